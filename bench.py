@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matrix product on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--workload c2|c1|c3...] [--impl reference]
+
+A step is one matmul of the workload's weight matrix with one batch of M
+synthetic token rows.  The default workload is the prefill GEMM the headline
+metric is quoted on: Q4_K W[17408, 5120] (0.02*N(0,1), quantized by the
+library's own quantizer) times bf16 X[M=2048, 5120] (rows of N(0,1) at RMS 1),
+fp32 accumulate; `--m 1 --workload c1` is the decode GEMV.  With --gpus N the
+weight rows are split over the ranks (one process per GPU), every rank
+multiplies its rows, and the slices are re-assembled on every rank with an
+NCCL all-gather: the total work is fixed (strong scaling).
+
+One JSON line is printed by rank 0.  `value` is measured with inputs resident
+in HBM; `e2e` goes through the public API from pinned host memory and back.
+`--impl reference` times the CPU restatement of the reference's own path
+(oracle/, all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (format, rows, cols, default M, activation dtype)
+    "c1": ("q4_k", 17408, 5120, 1, "f32"),      # decode GEMV, f32 activations
+    "c2": ("q4_k", 17408, 5120, 2048, "bf16"),  # prefill GEMM, bf16 activations
+    "c2_down": ("q4_k", 5120, 17408, 2048, "bf16"),
+    "c3_q6k": ("q6_k", 151936, 5120, 1, "f32"),
+    "c3_q8": ("q8_0", 5120, 5120, 1, "f32"),
+    "c3_attn": ("q4_k", 12288, 5120, 1, "f32"),
+}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, None
+
+    def __enter__(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            busy = sorted(sm)[len(sm) // 2:]          # the upper half: samples under load
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), samples=len(sm), reasons=sorted(reasons))
+        return out
+
+
+def make_inputs(fmt, rows, cols, m, act, seed_w=0, seed_x=2):
+    """W ~ 0.02*N(0,1) f32 (quantized later, on the device); X rows ~ N(0,1)
+    (scaled to RMS 1 and rounded to bf16 for the bf16 workloads)."""
+    w = 0.02 * np.random.default_rng(seed_w).standard_normal((rows, cols), dtype=np.float32)
+    x = np.random.default_rng(seed_x).standard_normal((m, cols), dtype=np.float32)
+    if act == "bf16":
+        x /= np.sqrt((x * x).mean(1, keepdims=True))
+        bits = ((x.view(np.uint32) + 0x7FFF + ((x.view(np.uint32) >> 16) & 1)) >> 16).astype(np.uint16)  # RNE
+        x = (bits.astype(np.uint32) << 16).view(np.float32)
+        return w, x, bits
+    return w, x, None
+
+
+def algorithmic_bytes(fmt, rows, cols, m):
+    from dwim_b200 import row_bytes
+    return rows * row_bytes(fmt, cols) + m * cols * 4 + m * rows * 4
+
+
+# ---------------------------------------------------------------------------------------
+def run_reference(args, fmt, rows, cols, m, act):
+    """The reference's CPU path (restated in oracle/) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    cores = oracle.threads()
+    w, x, _ = make_inputs(fmt, min(rows, 4096), cols, m, act)
+    blocks_all = oracle.quantize(fmt, w)
+    rb = oracle.row_bytes(fmt, cols)
+    # size the sample so that a step takes about a second
+    probe_rows = min(w.shape[0], max(cores * 4, 64))
+    t = time.perf_counter()
+    oracle.matmul(fmt, blocks_all[: probe_rows * rb], probe_rows, cols, x[: min(m, 16)])
+    per_row_token = (time.perf_counter() - t) / (probe_rows * min(m, 16))
+    sample_rows = int(max(cores, min(w.shape[0], rows, 1.0 / max(per_row_token * m, 1e-12))))
+    sample_rows = max(cores, sample_rows // cores * cores)
+    blocks = blocks_all[: sample_rows * rb]
+    for _ in range(max(1, args.warmup // 3)):
+        oracle.matmul(fmt, blocks, sample_rows, cols, x)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.matmul(fmt, blocks, sample_rows, cols, x)
+    dt = (time.perf_counter() - t) / args.steps
+    full = dt * rows / sample_rows                       # a whole step, scaled by rows
+    metric, unit, value = headline(fmt, rows, cols, m, full)
+    sample = f"{sample_rows} of {rows} weight rows x {m} tokens per step, time scaled by rows"
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(fmt, rows, cols, m, act, args.gpus),
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "tok_per_s": m / full,
+    }))
+
+
+def headline(fmt, rows, cols, m, seconds):
+    """The metric of a step: TFLOP/s for the GEMM sizes, GB/s for the GEMV sizes."""
+    if m > 16:
+        return "q4k_prefill_gemm_tflops" if fmt == "q4_k" else f"{fmt}_gemm_tflops", "TFLOP/s", 2.0 * m * rows * cols / seconds / 1e12
+    return ("q4k_decode_gemv_hbm_gbs" if fmt == "q4_k" else f"{fmt}_gemv_hbm_gbs"), "GB/s", algorithmic_bytes(fmt, rows, cols, m) / seconds / 1e9
+
+
+def workload_config(fmt, rows, cols, m, act, gpus):
+    return {"workload": f"{fmt.upper()} W[{rows},{cols}] x {act} X[{m},{cols}], fp32 accumulate",
+            "format": fmt, "rows": rows, "cols": cols, "tokens": m, "activations": act,
+            "sharding": f"rows/{gpus} + all-gather" if gpus > 1 else "none",
+            "l2": "weights rotate over copies totalling more than the 126 MB L2"}
+
+
+# ---------------------------------------------------------------------------------------
+def run_gpu(args, name, fmt, rows, cols, m, act):
+    import torch
+    from dwim_b200 import B200, Tensor, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = B200(local)
+    ext = torch.cuda.ExternalStream(dev.stream, device=local)
+
+    w, x, bits = make_inputs(fmt, rows, cols, m, act)
+    align = 16
+    r0, r1 = shard_rows(rows, rank, world, align)
+    my_rows = r1 - r0
+    part_rows = shard_rows(rows, 0, world, align)[1]
+    t_w = dev.quantize(fmt, w[r0:r1])
+    del w
+    # rotate over enough copies of the weights that a pass cannot be served from L2
+    wbytes = max(t_w.data.size, 1)
+    copies = int(min(16, max(2, -(-3 * L2_BYTES // wbytes))))
+    weights = [dev.upload(t_w) for _ in range(copies)]
+
+    xb = dev.alloc(m * cols)
+    (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
+    if world > 1:
+        if my_rows != part_rows:
+            raise SystemExit(f"{rows} rows do not split evenly over {world} ranks at multiples of {align}")
+        parts_t = torch.empty(world * m * part_rows, dtype=torch.float32, device="cuda")
+        mine_t = parts_t[rank * m * part_rows:(rank + 1) * m * part_rows]
+        out_local = dev.wrap(mine_t.data_ptr(), m * my_rows)
+        parts = dev.wrap(parts_t.data_ptr(), parts_t.numel())
+        out = dev.alloc(m * rows)
+    else:
+        out_local = out = dev.alloc(m * rows)
+
+    def step(i, fresh_input=True):
+        if fresh_input:
+            dev.resize(xb, m * cols)          # marks the input as rewritten: its 16-bit operand form is rebuilt
+        dev.matmul(out_local, weights[i % copies], xb)
+        if world > 1:
+            with torch.cuda.stream(ext):
+                dist.all_gather_into_tensor(parts_t, mine_t)
+            dev.gather_rows(out, parts, m, rows, world, align)
+
+    def timed(n_steps, fresh_input=True):
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        dev.sync()
+        launches0 = dev.launches
+        dev.timer_begin()
+        for i in range(n_steps):
+            step(i, fresh_input)
+        ms = dev.timer_end()
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / 1e3, dev.launches - launches0
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    with ClockSampler(local) as clocks:
+        seconds, launches = timed(args.steps)
+        # the dominant kernel alone (operand form cached): what the roofline is about
+        kernel_seconds, _ = timed(args.steps, fresh_input=False) if world == 1 else (seconds, 0)
+    per_step = seconds / args.steps
+    per_kernel = kernel_seconds / args.steps
+    metric, unit, value = headline(fmt, rows, cols, m, per_step)
+
+    # ---- end to end: pinned host memory -> device -> product -> pinned host memory ----
+    if bits is not None:
+        hx = torch.empty(m * cols, dtype=torch.uint16, pin_memory=True).numpy()
+        hx[:] = bits.ravel()
+    else:
+        hx = torch.empty(m * cols, dtype=torch.float32, pin_memory=True).numpy()
+        hx[:] = x.ravel()
+    hout = torch.empty(m * rows, dtype=torch.float32, pin_memory=True).numpy()
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step(i):
+        (dev.write_bf16(xb, hx) if bits is not None else dev.write(xb, hx))
+        step_no_resize(i)
+        dev.read(out, hout)
+
+    def step_no_resize(i):
+        dev.matmul(out_local, weights[i % copies], xb)
+        if world > 1:
+            with torch.cuda.stream(ext):
+                dist.all_gather_into_tensor(parts_t, mine_t)
+            dev.gather_rows(out, parts, m, rows, world, align)
+
+    for i in range(2):
+        e2e_step(i)
+    if dist:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    _, _, e2e_value = headline(fmt, rows, cols, m, e2e_s)
+
+    if rank == 0:
+        pk = peaks()
+        gemm = m > 16
+        if gemm:
+            flops = 2.0 * m * my_rows * cols
+            achieved = flops / per_kernel / 1e12
+            roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                    "frac_of_sustained": achieved / pk["tflops_sustained"] if pk["tflops_sustained"] else None}
+        else:
+            by = algorithmic_bytes(fmt, my_rows, cols, m)
+            achieved = by / per_kernel / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                    "frac_of_nominal_8tbs": achieved / 8000.0}
+        roof["kernel_us"] = per_kernel * 1e6
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 x int (exact) -> f32" if not gemm else "f16 -> f32", "data": "synthetic",
+            "config": workload_config(fmt, rows, cols, m, act, world),
+            "tok_per_s": m / per_step,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(hx.nbytes),
+                    "d2h_bytes_per_step": int(m * rows * 4), "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": roof,
+            "device": dev.name(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(fmt, rows, cols, m, act)
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(fmt, rows, cols, m, act):
+    """The oracle's matmul on the host cores, on a bounded sample (about 10 s)."""
+    import oracle
+    oracle.build()
+    cores = oracle.threads()
+    sample_w = min(rows, 2048)
+    w, x, _ = make_inputs(fmt, sample_w, cols, m, act)
+    blocks = oracle.quantize(fmt, w)
+    rb = oracle.row_bytes(fmt, cols)
+    probe = min(sample_w, max(4 * cores, 64))
+    t = time.perf_counter()
+    oracle.matmul(fmt, blocks[: probe * rb], probe, cols, x[: min(m, 8)])
+    unit_s = (time.perf_counter() - t) / (probe * min(m, 8))
+    sample_rows = int(min(sample_w, max(cores, 10.0 / max(unit_s * m, 1e-12))))
+    t = time.perf_counter()
+    reps = 0
+    while True:
+        oracle.matmul(fmt, blocks[: sample_rows * rb], sample_rows, cols, x)
+        reps += 1
+        if time.perf_counter() - t > 8.0 or reps >= 200:
+            break
+    dt = (time.perf_counter() - t) / reps * rows / sample_rows
+    _, unit, value = headline(fmt, rows, cols, m, dt)
+    return {"value": value, "unit": unit, "cores": cores, "kind": "port",
+            "sample": f"{sample_rows} of {rows} rows x {m} tokens, {reps} repeats, time scaled by rows",
+            "ms_per_step": dt * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--m", type=int, default=None, help="tokens per step (default: the workload's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    fmt, rows, cols, m, act = WORKLOADS[args.workload]
+    if args.m:
+        m = args.m
+    if args.impl == "reference":
+        run_reference(args, fmt, rows, cols, m, act)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if args.gpus > 1:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is {world})")
+    run_gpu(args, args.workload, fmt, rows, cols, m, act)
+
+
+if __name__ == "__main__":
+    main()

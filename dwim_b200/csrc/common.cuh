@@ -1,0 +1,106 @@
+// Handles behind the C ABI and the helpers every translation unit shares.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/dwim_b200.h"
+#include "formats.cuh"
+
+// Forms of an activation buffer's 16-bit shadow (cf. `Form`,
+// gpu/cuda/mod.rs:108-126: the reference keeps an f16 copy beside the f32 one
+// so that consecutive matmuls on one input convert it once).
+enum ShadowKind : int {
+    SHADOW_NONE = 0,
+    SHADOW_PANEL_NATURAL,   // small-M panels, k in order            (Q8_0, Q6_K)
+    SHADOW_PANEL_Q4K,       // small-M panels, k permuted + swizzled (Q4_K)
+    SHADOW_F16_ROWS         // [n][cols] f16, for the tensor-core GEMM
+};
+
+struct dwim_b200_buffer {
+    float *data = nullptr;
+    size_t len = 0, cap = 0;
+    bool owned = true;
+    bool bf16_exact = false;     // every value is exactly a bf16 (write_bf16)
+    // shadow
+    void *shadow = nullptr;
+    size_t shadow_cap = 0;       // bytes
+    int shadow_kind = SHADOW_NONE;
+    size_t shadow_cols = 0;      // K the shadow was built for
+    int shadow_split = 0;        // 1: hi/lo column pairs, 0: single f16
+};
+
+struct dwim_b200_weight {
+    dwim::WeightView v{};
+    void *quants_alloc = nullptr;
+    void *scales_alloc = nullptr;
+};
+
+struct dwim_b200_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    uint32_t *status = nullptr;      // device word: bounded waits report here
+    uint32_t *status_host = nullptr; // pinned
+    uint64_t launches = 0;
+    char name[256] = {0};
+    char err[512] = {0};
+    // the GEMM path's lazily created state
+    void *gemm_state = nullptr;
+};
+
+namespace dwim {
+
+inline int fail(dwim_b200_ctx *ctx, int code, const char *fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof ctx->err, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define DWIM_CUDA(ctx, expr)                                                                   \
+    do {                                                                                       \
+        cudaError_t e_ = (expr);                                                               \
+        if (e_ != cudaSuccess)                                                                 \
+            return dwim::fail(ctx, e_ == cudaErrorMemoryAllocation ? DWIM_B200_ENOMEM : DWIM_B200_ECUDA, \
+                              "%s: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+#define DWIM_LAUNCHED(ctx)                                                                     \
+    do {                                                                                       \
+        (ctx)->launches++;                                                                     \
+        cudaError_t e_ = cudaGetLastError();                                                   \
+        if (e_ != cudaSuccess)                                                                 \
+            return dwim::fail(ctx, DWIM_B200_ECUDA, "kernel launch: %s (%s:%d)",               \
+                              cudaGetErrorString(e_), __FILE__, __LINE__);                     \
+    } while (0)
+
+// codec.cu
+int repack_to_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const uint8_t *file_dev,
+                     uint8_t *quants, __half *scales);
+int dequantize_device(dwim_b200_ctx *ctx, const WeightView &w, float *out_dev);
+int quantize_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const float *w_dev, uint8_t *file_dev);
+
+// prologue.cu
+// Elements (f16) of one column's panel per 256 weights of K: 256 activations
+// and 16 entries of per-sub-block means (hi then lo halves).
+constexpr int PANEL_STRIDE = 272;
+size_t panel_bytes(size_t cols, int ncols);
+int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels);
+int build_f16_rows(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, __half *out);
+
+// gemv.cu
+enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+// One launch: tokens [t0, t0 + n_tokens) of a panel array holding ncols_total
+// columns, the launch's first at col0.  aux is the `up` product for EPI_SWIGLU.
+int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
+               size_t t0, int split, float *out, const float *aux, int epilogue);
+int gemv_max_tokens(int split);
+
+}  // namespace dwim

@@ -1,0 +1,656 @@
+// The small-M product (decode and speculative verify): out[t][r] = w[r] . x[t]
+// for up to 16 tokens, bound by how fast the packed weights stream from HBM.
+//
+// Replaces the reference's matmul_tile16_* / matmul_rows* kernels for few
+// tokens (matmul_tile.cu:94-258, matmul_rows.cu:29-184; dispatch at
+// gpu/cuda/mod.rs:1084-1131).
+//
+// Shape of the kernel
+//   - Persistent grid, one CTA per SM.  A CTA walks tiles of R = 16*RT weight
+//     rows; for each tile it streams the rows' packed blocks, K in chunks of
+//     `kc` units of 256 weights, through a ring of shared-memory stages.
+//   - One producer warp fills the ring with cp.async.bulk (the TMA engine's
+//     untiled copy): per stage one copy per weight row (the row's bytes for
+//     the chunk are contiguous in HBM), one per row of scales where the format
+//     keeps them apart, and one per unit for the activation panels.  Stages
+//     are handed over with mbarriers (full: transaction bytes; empty: one
+//     arrival per consumer warp).  Every wait is bounded.
+//   - RT*KS consumer warps.  Warp (rt, ks) owns row tile rt and every KS-th
+//     unit of a chunk.  It unpacks quants in registers to f16 *integers*
+//     (exact), multiplies them with the f16 activation columns on the tensor
+//     cores (mma.sync m16n8k16, fp32 accumulate: weight rows are the M side,
+//     activation columns the N side) and applies the f16/f32 block scales to
+//     the fp32 partial sums.  An f32 activation travels as two f16 columns
+//     (value and rounding remainder), so products are exact and the result
+//     differs from the CPU's only by fp32 summation order.
+//   - The K-split warps of a row tile are summed through shared memory in a
+//     fixed order (deterministic), then the epilogue stores, adds to, or
+//     SwiGLU-combines the output (modes after prelude.cu:29-35).
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace dwim {
+
+constexpr int MAX_STAGES = 8;
+constexpr int PANEL_BYTES = PANEL_STRIDE * 2;   // 544: 16 B multiple, 32 mod 128
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct GemvArgs {
+    WeightView w;
+    const uint8_t *panels;   // [units][ncols_total][PANEL_BYTES]
+    int ncols_total;         // columns in the panel array
+    int col0;                // first column of this launch
+    int ncols;               // columns of this launch (<= 8*NT)
+    int split;               // 1: columns are (hi, lo) pairs of a token
+    int n_tokens;            // tokens of this launch
+    size_t t0;               // first token's index in out
+    float *out;
+    const float *aux;        // EPI_SWIGLU: the `up` product, same layout as out
+    int epi;
+    int units;               // ceil(cols / 256)
+    int kc;                  // units per stage
+    int n_tiles;
+    int stages;
+    int q_stride;            // bytes between rows of a stage's quant region
+    int s_off, s_stride;     // scale region
+    int x_off;               // panel region
+    int stage_bytes;
+    uint32_t *status;
+};
+
+// ---------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for the barrier's phase, for at most WAIT_LIMIT_NS.  When the limit
+// runs out the kernel records `code` in the status word and carries on with
+// whatever the stage holds: control flow stays uniform, every later wait sees
+// the status and returns at once, the kernel ends, and the host reports the
+// failure at its next sync.
+__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
+    uint64_t start = globaltimer();
+    for (;;) {
+        if (mbar_try(bar, parity)) return;
+        if (*(volatile uint32_t *)status != 0) return;
+        if (globaltimer() - start > WAIT_LIMIT_NS) {
+            atomicOr(status, code);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
+    if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, status, code);
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;   // (a & mask) | orv
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));
+    return r;
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t hfma2(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmul2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ float h2f_lo(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v & 0xffff))); }
+__device__ __forceinline__ float h2f_hi(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v >> 16))); }
+
+// D += A (16 rows x 16 k, f16) * B (16 k x 8 columns, f16), fp32.
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr uint32_t H2_1024 = 0x64006400u;   // half2(1024, 1024)
+constexpr uint32_t H2_1056 = 0x64206420u;   // half2(1056, 1056)
+constexpr uint32_t H2_1152 = 0x64806480u;   // half2(1152, 1152)
+constexpr uint32_t H2_M1024 = 0xE400E400u;  // half2(-1024, -1024)
+constexpr uint32_t H2_M64 = 0xD400D400u;    // half2(-64, -64)
+constexpr uint32_t H2_SIXTEENTH = 0x2C002C00u;  // half2(1/16, 1/16)
+
+template <int FMT> struct Traits;
+template <> struct Traits<Q4_K> { static constexpr int UNIT_Q = 144; };
+template <> struct Traits<Q6_K> { static constexpr int UNIT_Q = 208; };
+template <> struct Traits<Q8_0> { static constexpr int UNIT_Q = 256; };
+
+// What a consumer lane needs to know about the stage it reads.
+struct Lane {
+    int g, c;                // row within the 8-row group; k-quarter
+    uint32_t row_a, row_b;   // shared addresses of rows g and g+8 (quant region)
+    uint32_t srow_a, srow_b; // shared addresses of the rows' scales
+    uint32_t x[2];           // shared address of this lane's column panel, per column group
+    bool xv[2];              // whether that column exists
+};
+
+// ---------------------------------------------------------------------------
+// Q4_K: one unit = one 144-byte block per row
+// ---------------------------------------------------------------------------
+// Lane c owns the 64 weights [64c, 64c+64) of each of its two rows: 32 bytes
+// whose low nibbles are sub-block 2c and high nibbles sub-block 2c+1.  The
+// 6-bit sub-block scale is folded into the f16 integers before the MMA
+// (sc*q <= 945 is exact in f16), so a whole block shares the f32 factor d.
+// The minimums go through one more MMA per block: A = the eight m_j, B = the
+// per-sub-block activation means (hi, lo); acc -= 32*dmin * that.
+struct Q4kScales {
+    uint32_t mul_lo, add_lo;   // low nibbles:  (1024+q)   * sc      - 1024*sc
+    uint32_t mul_hi, add_hi;   // high nibbles: (1024+16q) * (sc/16) - 64*sc
+    uint32_t mins;             // half2(m_2c, m_2c+1)
+    float d, dmin32;
+};
+__device__ __forceinline__ Q4kScales q4k_scales(const uint4 &hdr, int c) {
+    int sh = (c & 1) * 16;
+    uint32_t y = (hdr.y >> sh) & 0xffffu, z = (hdr.z >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
+    uint32_t sc2 = c < 2 ? (y & 0x3f3fu) : ((w & 0x0f0fu) | ((y >> 2) & 0x3030u));
+    uint32_t m2 = c < 2 ? (z & 0x3f3fu) : (((w >> 4) & 0x0f0fu) | ((z >> 2) & 0x3030u));
+    // bytes (a, b) -> half2(a, b): put 0x64 above each byte (1024 + v), take 1024 off
+    uint32_t scp = hsub2(prmt(sc2, 0x00006464u, 0x5140u), H2_1024);
+    uint32_t mp = hsub2(prmt(m2, 0x00006464u, 0x5140u), H2_1024);
+    uint32_t sa = prmt(scp, scp, 0x1010u);   // half2(sc_a, sc_a)
+    uint32_t sb = prmt(scp, scp, 0x3232u);   // half2(sc_b, sc_b)
+    Q4kScales s;
+    s.mul_lo = sa;
+    s.add_lo = hmul2(sa, H2_M1024);
+    s.mul_hi = hmul2(sb, H2_SIXTEENTH);
+    s.add_hi = hmul2(sb, H2_M64);
+    s.mins = mp;
+    s.d = h2f_lo(hdr.x);
+    s.dmin32 = h2f_hi(hdr.x) * 32.0f;
+    return s;
+}
+
+template <int NT>
+__device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int ncols, const uint32_t (&xo)[4],
+                                         float (&acc)[NT][4]) {
+    const uint32_t ba = L.row_a + ul * 144, bb = L.row_b + ul * 144;
+    const uint4 ha = lds128(ba), hb = lds128(bb);
+    uint32_t qa[8], qb[8];
+    {
+        uint4 t0 = lds128(ba + 16 + 32 * L.c), t1 = lds128(ba + 32 + 32 * L.c);
+        qa[0] = t0.x; qa[1] = t0.y; qa[2] = t0.z; qa[3] = t0.w;
+        qa[4] = t1.x; qa[5] = t1.y; qa[6] = t1.z; qa[7] = t1.w;
+        uint4 u0 = lds128(bb + 16 + 32 * L.c), u1 = lds128(bb + 32 + 32 * L.c);
+        qb[0] = u0.x; qb[1] = u0.y; qb[2] = u0.z; qb[3] = u0.w;
+        qb[4] = u1.x; qb[5] = u1.y; qb[6] = u1.z; qb[7] = u1.w;
+    }
+    const Q4kScales sa = q4k_scales(ha, L.c), sb = q4k_scales(hb, L.c);
+    float c1[NT][4], c2[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) c1[nt][i] = c2[nt][i] = 0.0f;
+    uint32_t xb[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 128 * L.c;
+
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const uint32_t wa = qa[j], wb = qb[j], was = wa >> 8, wbs = wb >> 8;
+        // bytes (0,2) and (1,3) of the word, low then high nibbles
+        const uint32_t a_le = hfma2(lop3_and_or(wa, 0x000f000fu, H2_1024), sa.mul_lo, sa.add_lo);
+        const uint32_t a_lo = hfma2(lop3_and_or(was, 0x000f000fu, H2_1024), sa.mul_lo, sa.add_lo);
+        const uint32_t a_he = hfma2(lop3_and_or(wa, 0x00f000f0u, H2_1024), sa.mul_hi, sa.add_hi);
+        const uint32_t a_ho = hfma2(lop3_and_or(was, 0x00f000f0u, H2_1024), sa.mul_hi, sa.add_hi);
+        const uint32_t b_le = hfma2(lop3_and_or(wb, 0x000f000fu, H2_1024), sb.mul_lo, sb.add_lo);
+        const uint32_t b_lo = hfma2(lop3_and_or(wbs, 0x000f000fu, H2_1024), sb.mul_lo, sb.add_lo);
+        const uint32_t b_he = hfma2(lop3_and_or(wb, 0x00f000f0u, H2_1024), sb.mul_hi, sb.add_hi);
+        const uint32_t b_ho = hfma2(lop3_and_or(wbs, 0x00f000f0u, H2_1024), sb.mul_hi, sb.add_hi);
+        const uint32_t off = 8 * (j & 4) + xo[j & 3];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
+            if (L.xv[nt]) {
+                x0 = lds64(xb[nt] + off);        // sub-block 2c   (low nibbles)
+                x1 = lds64(xb[nt] + 64 + off);   // sub-block 2c+1 (high nibbles)
+            }
+            mma16816(c1[nt], a_le, b_le, a_lo, b_lo, x0.x, x0.y);
+            mma16816(c1[nt], a_he, b_he, a_ho, b_ho, x1.x, x1.y);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        uint2 xm = make_uint2(0, 0);
+        if (L.xv[nt]) xm = lds64(L.x[nt] + ul * ncols * PANEL_BYTES + 512 + 8 * L.c);
+        mma16816(c2[nt], sa.mins, sb.mins, sa.mins, sb.mins, xm.x, xm.y);
+        acc[nt][0] += sa.d * c1[nt][0] - sa.dmin32 * c2[nt][0];
+        acc[nt][1] += sa.d * c1[nt][1] - sa.dmin32 * c2[nt][1];
+        acc[nt][2] += sb.d * c1[nt][2] - sb.dmin32 * c2[nt][2];
+        acc[nt][3] += sb.d * c1[nt][3] - sb.dmin32 * c2[nt][3];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Q8_0: one unit = eight 32-weight blocks per row (256 quant bytes, 8 scales)
+// ---------------------------------------------------------------------------
+// Lane c owns bytes [8c, 8c+8) of each block: two words, one per MMA.
+__device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t &p01, uint32_t &p23) {
+    w ^= 0x80808080u;                                    // q + 128, unsigned
+    p01 = hsub2(prmt(w, 0x64646464u, 0x5140u), H2_1152); // 1024 + 128 + q - 1152
+    p23 = hsub2(prmt(w, 0x64646464u, 0x5342u), H2_1152);
+}
+
+template <int NT>
+__device__ __forceinline__ void unit_q8_0(const Lane &L, int ul, int ncols, float (&acc)[NT][4]) {
+    const uint32_t qa = L.row_a + ul * 256 + 8 * L.c, qb = L.row_b + ul * 256 + 8 * L.c;
+    const uint4 sa = lds128(L.srow_a + ul * 16), sb = lds128(L.srow_b + ul * 16);
+    const uint32_t sca[4] = {sa.x, sa.y, sa.z, sa.w}, scb[4] = {sb.x, sb.y, sb.z, sb.w};
+    uint32_t xb[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 16 * L.c;
+#pragma unroll
+    for (int blk = 0; blk < 8; blk++) {
+        const uint2 wa = lds64(qa + 32 * blk), wb = lds64(qb + 32 * blk);
+        uint32_t a0, a2, a1, a3, e0, e2, e1, e3;
+        s8x4_to_h2(wa.x, a0, a2);
+        s8x4_to_h2(wb.x, a1, a3);
+        s8x4_to_h2(wa.y, e0, e2);
+        s8x4_to_h2(wb.y, e1, e3);
+        const float da = (blk & 1) ? h2f_hi(sca[blk >> 1]) : h2f_lo(sca[blk >> 1]);
+        const float db = (blk & 1) ? h2f_hi(scb[blk >> 1]) : h2f_lo(scb[blk >> 1]);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            uint4 xv = make_uint4(0, 0, 0, 0);
+            if (L.xv[nt]) xv = lds128(xb[nt] + 64 * blk);
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            mma16816(c, a0, a1, a2, a3, xv.x, xv.y);
+            mma16816(c, e0, e1, e2, e3, xv.z, xv.w);
+            acc[nt][0] += da * c[0];
+            acc[nt][1] += da * c[1];
+            acc[nt][2] += db * c[2];
+            acc[nt][3] += db * c[3];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Q6_K: one unit = one 208-byte device block per row (+ its f16 d)
+// ---------------------------------------------------------------------------
+// One MMA per 16-weight scale group: lane c holds weights 4c..4c+3 of the
+// group.  For (half, lh) the lane reads two ql words and one qh word and
+// makes the four groups k = 0..3 from them.
+__device__ __forceinline__ float s8_byte_to_f32(uint32_t word_xor80, int b) {
+    // 0x4B000000 | (s + 128) is 8388608 + s + 128 as a float
+    return __uint_as_float(prmt(word_xor80, 0x4B000000u, 0x7540u + b)) - 8388736.0f;
+}
+
+template <int NT>
+__device__ __forceinline__ void unit_q6k(const Lane &L, int ul, int ncols, int d_index, float (&acc)[NT][4]) {
+    const uint32_t ba = L.row_a + ul * 208, bb = L.row_b + ul * 208;
+    uint4 ta = lds128(ba + 192), tb = lds128(bb + 192);
+    const uint32_t sca[4] = {ta.x ^ 0x80808080u, ta.y ^ 0x80808080u, ta.z ^ 0x80808080u, ta.w ^ 0x80808080u};
+    const uint32_t scb[4] = {tb.x ^ 0x80808080u, tb.y ^ 0x80808080u, tb.z ^ 0x80808080u, tb.w ^ 0x80808080u};
+    const float da = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_a + 2 * d_index)));
+    const float db = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_b + 2 * d_index)));
+    float part[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) part[nt][i] = 0.0f;
+    uint32_t xb[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 8 * L.c;
+
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+        for (int lh = 0; lh < 2; lh++) {
+            const uint32_t o = 64 * hf + 16 * lh + 4 * L.c, oh = 128 + 32 * hf + 16 * lh + 4 * L.c;
+            const uint32_t la0 = lds32(ba + o), la1 = lds32(ba + o + 32), hha = lds32(ba + oh);
+            const uint32_t lb0 = lds32(bb + o), lb1 = lds32(bb + o + 32), hhb = lds32(bb + oh);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t la = (k & 1) ? la1 : la0, lb = (k & 1) ? lb1 : lb0;
+                const uint32_t lowa = ((k >> 1) ? (la >> 4) : la) & 0x0f0f0f0fu;
+                const uint32_t lowb = ((k >> 1) ? (lb >> 4) : lb) & 0x0f0f0f0fu;
+                const uint32_t ha = (k == 0 ? hha << 4 : k == 1 ? hha << 2 : k == 2 ? hha : hha >> 2) & 0x30303030u;
+                const uint32_t hb = (k == 0 ? hhb << 4 : k == 1 ? hhb << 2 : k == 2 ? hhb : hhb >> 2) & 0x30303030u;
+                const uint32_t qa = lowa | ha, qb = lowb | hb;   // bytes: q + 32
+                const uint32_t a0 = hsub2(prmt(qa, 0x64646464u, 0x5140u), H2_1056);
+                const uint32_t a2 = hsub2(prmt(qa, 0x64646464u, 0x5342u), H2_1056);
+                const uint32_t a1 = hsub2(prmt(qb, 0x64646464u, 0x5140u), H2_1056);
+                const uint32_t a3 = hsub2(prmt(qb, 0x64646464u, 0x5342u), H2_1056);
+                const int sidx = 8 * hf + 2 * k + lh;
+                const float fa = s8_byte_to_f32(sca[sidx >> 2], sidx & 3);
+                const float fb = s8_byte_to_f32(scb[sidx >> 2], sidx & 3);
+                const uint32_t koff = 2 * (128 * hf + 32 * k + 16 * lh);
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    uint2 xv = make_uint2(0, 0);
+                    if (L.xv[nt]) xv = lds64(xb[nt] + koff);
+                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    mma16816(c, a0, a1, a2, a3, xv.x, xv.y);
+                    part[nt][0] += fa * c[0];
+                    part[nt][1] += fa * c[1];
+                    part[nt][2] += fb * c[2];
+                    part[nt][3] += fb * c[3];
+                }
+            }
+        }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        acc[nt][0] += da * part[nt][0];
+        acc[nt][1] += da * part[nt][1];
+        acc[nt][2] += db * part[nt][2];
+        acc[nt][3] += db * part[nt][3];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    // gpu/cpu.rs:238-242, 425-427: g * (1 / (1 + exp(-g))) * u
+    return g * (1.0f / (1.0f + expf(-g))) * u;
+}
+
+__device__ __forceinline__ void emit(const GemvArgs &a, size_t t, size_t r, float v) {
+    if (r >= a.w.rows) return;
+    size_t i = (a.t0 + t) * a.w.rows + r;
+    if (a.epi == EPI_ADD) v += a.out[i];
+    else if (a.epi == EPI_SWIGLU) v = silu_mul(v, a.aux[i]);
+    a.out[i] = v;
+}
+
+template <int FMT, int NT, int RT, int KS>
+__global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvArgs a) {
+    constexpr int NW = RT * KS;
+    constexpr int R = RT * 16;
+    constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
+    constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NT * 4 * 32 : 0;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);          // full[MAX_STAGES], empty[MAX_STAGES]
+    float *red = reinterpret_cast<float *>(smem + 128);
+    uint8_t *stages = smem + 128 + ((RED_FLOATS * 4 + 127) & ~127);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = a.stages;
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, NW);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int n_chunks = (a.units + a.kc - 1) / a.kc;
+    const uint32_t stage0 = smem_u32(stages);
+
+    if (warp == NW) {
+        // ------------------------------ producer ------------------------------
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+            const size_t row0 = (size_t)tile * R;
+            const int nrows = (int)min((size_t)R, a.w.rows - row0);
+            for (int ch = 0; ch < n_chunks; ch++, it++) {
+                const int s = it % S;
+                const uint32_t ph = (it / S) & 1;
+                mbar_wait(empty0 + 8 * s, ph ^ 1, a.status, 0x1u);
+                const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
+                const uint32_t qbytes = UNIT_Q * kcc;
+                uint32_t sbytes = 0;
+                size_t s_first = 0;   // first f16 of the row's scales to copy
+                if (FMT == Q8_0) { sbytes = 16 * kcc; s_first = (size_t)8 * u0; }
+                if (FMT == Q6_K) {
+                    s_first = (size_t)(u0 & ~7);
+                    size_t s_end = min((size_t)pad8(u0 + kcc), a.w.srow);
+                    sbytes = (uint32_t)(s_end - s_first) * 2;
+                }
+                const uint32_t xbytes = (uint32_t)a.ncols * PANEL_BYTES;
+                const uint32_t bar = full0 + 8 * s;
+                if (lane == 0) mbar_expect_tx(bar, nrows * (qbytes + sbytes) + kcc * xbytes);
+                __syncwarp();
+                const uint32_t st = stage0 + s * a.stage_bytes;
+                for (int r = lane; r < nrows; r += 32) {
+                    bulk_g2s(st + r * a.q_stride, a.w.quants + (row0 + r) * a.w.qrow + (size_t)u0 * UNIT_Q, qbytes, bar);
+                    if (FMT != Q4_K)
+                        bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
+                }
+                for (int u = lane; u < kcc; u += 32)
+                    bulk_g2s(st + a.x_off + u * xbytes,
+                             a.panels + ((size_t)(u0 + u) * a.ncols_total + a.col0) * PANEL_BYTES, xbytes, bar);
+            }
+        }
+        // Drain: the copies this warp issued must have landed before the CTA's
+        // shared memory is given up.  Normally the consumers have already
+        // waited on every stage and this returns at once.
+        if (*(volatile uint32_t *)a.status != 0) {
+            uint64_t start = globaltimer();
+            uint32_t first = it > (uint32_t)S ? it - S : 0;
+            for (uint32_t i = first; i < it; i++) {
+                while (!mbar_try(full0 + 8 * (i % S), (i / S) & 1))
+                    if (globaltimer() - start > WAIT_LIMIT_NS) break;
+            }
+        }
+        return;
+    }
+
+    // -------------------------------- consumers --------------------------------
+    const int rt = warp % RT, ks = warp / RT;
+    Lane L;
+    L.g = lane >> 2;
+    L.c = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) L.xv[nt] = nt < NT && (nt * 8 + L.g) < a.ncols;
+    uint32_t xo[4];
+#pragma unroll
+    for (int v = 0; v < 4; v++) xo[v] = 8 * (v ^ L.c);
+
+    uint32_t it = 0;
+    int tile_parity = 0;
+    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, tile_parity ^= 1) {
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+
+        for (int ch = 0; ch < n_chunks; ch++, it++) {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1;
+            mbar_wait(full0 + 8 * s, ph, a.status, 0x2u);
+            const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
+            const uint32_t st = stage0 + s * a.stage_bytes;
+            L.row_a = st + (rt * 16 + L.g) * a.q_stride;
+            L.row_b = L.row_a + 8 * a.q_stride;
+            L.srow_a = st + a.s_off + (rt * 16 + L.g) * a.s_stride;
+            L.srow_b = L.srow_a + 8 * a.s_stride;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) L.x[nt] = st + a.x_off + (nt * 8 + L.g) * PANEL_BYTES;
+            for (int ul = ks; ul < kcc; ul += KS) {
+                if (FMT == Q4_K) unit_q4k<NT>(L, ul, a.ncols, xo, acc);
+                else if (FMT == Q8_0) unit_q8_0<NT>(L, ul, a.ncols, acc);
+                else unit_q6k<NT>(L, ul, a.ncols, (u0 & 7) + ul, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+
+        // ---- sum the K-split warps of this row tile, in warp order ----
+        if (KS > 1) {
+            float *buf = red + tile_parity * (KS * RT * NT * 128);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) buf[(((ks * RT + rt) * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+            if (ks != 0) continue;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int k2 = 0; k2 < KS; k2++) v += buf[(((k2 * RT + rt) * NT + nt) * 4 + i) * 32 + lane];
+                    acc[nt][i] = v;
+                }
+        }
+
+        // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
+        const size_t r0 = (size_t)tile * R + rt * 16 + L.g, r1 = r0 + 8;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            if (a.split) {
+                const int t = nt * 4 + L.c;   // columns 2t (hi), 2t+1 (lo)
+                if (t < a.n_tokens) {
+                    emit(a, t, r0, acc[nt][0] + acc[nt][1]);
+                    emit(a, t, r1, acc[nt][2] + acc[nt][3]);
+                }
+            } else {
+                const int t = nt * 8 + 2 * L.c;
+                if (t < a.n_tokens) { emit(a, t, r0, acc[nt][0]); emit(a, t, r1, acc[nt][2]); }
+                if (t + 1 < a.n_tokens) { emit(a, t + 1, r0, acc[nt][1]); emit(a, t + 1, r1, acc[nt][3]); }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+int gemv_max_tokens(int split) { return split ? 8 : 16; }
+
+template <int FMT, int NT, int RT, int KS>
+static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
+    constexpr int R = RT * 16;
+    constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
+    constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NT * 4 * 32 * 4 + 127) & ~127) : 0;
+    // K per stage: a multiple of KS units, about 1024 weights per warp-visit
+    a.kc = KS * (FMT == Q8_0 ? 1 : 1);
+    if (a.kc > a.units) a.kc = a.units;
+    int qs = UNIT_Q * a.kc;
+    if ((qs / 16) % 2 == 0) qs += 16;   // an odd number of 16-byte steps between rows: no bank conflicts
+    a.q_stride = qs;
+    a.s_off = R * qs;
+    a.s_stride = FMT == Q8_0 ? 16 * a.kc + 16 : FMT == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
+    a.x_off = a.s_off + R * a.s_stride;
+    a.stage_bytes = (a.x_off + a.kc * a.ncols * PANEL_BYTES + 127) & ~127;
+    a.n_tiles = (int)((a.w.rows + R - 1) / R);
+    const int fixed = 128 + RED_BYTES;
+    int stages = (227 * 1024 - fixed) / a.stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: a stage of %d bytes does not fit", a.stage_bytes);
+    a.stages = stages;
+    const int smem = fixed + stages * a.stage_bytes;
+    auto kern = gemv_kernel<FMT, NT, RT, KS>;
+    static bool configured[64] = {false};   // per instantiation, per device
+    if (!configured[ctx->device & 63]) {
+        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        configured[ctx->device & 63] = true;
+    }
+    int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
+    kern<<<grid, (RT * KS + 1) * 32, smem, ctx->stream>>>(a);
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}
+
+template <int FMT, int NT>
+static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
+    // Many rows: 32-row tiles, four K-split warps each; few rows: 16-row tiles
+    // and eight K-split warps, so that every SM still gets tiles.
+    const size_t tiles32 = (a.w.rows + 31) / 32;
+    if (tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 4>(ctx, a);
+    return launch<FMT, NT, 1, 8>(ctx, a);
+}
+
+int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
+               size_t t0, int split, float *out, const float *aux, int epilogue) {
+    if (w.rows == 0 || n_tokens == 0) return 0;
+    GemvArgs a{};
+    a.w = w;
+    a.panels = reinterpret_cast<const uint8_t *>(panels);
+    a.ncols_total = ncols_total;
+    a.col0 = col0;
+    a.ncols = n_tokens * (split ? 2 : 1);
+    a.split = split;
+    a.n_tokens = n_tokens;
+    a.t0 = t0;
+    a.out = out;
+    a.aux = aux;
+    a.epi = epilogue;
+    a.units = (int)((w.cols + 255) / 256);
+    a.status = ctx->status;
+    if (a.ncols > 16) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: %d columns", a.ncols);
+    const bool two = a.ncols > 8;
+    switch (w.fmt) {
+    case Q4_K: return two ? launch_shape<Q4_K, 2>(ctx, a) : launch_shape<Q4_K, 1>(ctx, a);
+    case Q6_K: return two ? launch_shape<Q6_K, 2>(ctx, a) : launch_shape<Q6_K, 1>(ctx, a);
+    case Q8_0: return two ? launch_shape<Q8_0, 2>(ctx, a) : launch_shape<Q8_0, 1>(ctx, a);
+    default: return fail(ctx, DWIM_B200_EFORMAT, "unknown weight format %d", w.fmt);
+    }
+}
+
+}  // namespace dwim

@@ -1,0 +1,116 @@
+// Activation prologue: f32 activations -> the 16-bit operand forms the matmul
+// kernels read.  The reference does the same with its f16 shadow buffers
+// (`halves`, gpu/cuda/mod.rs:313-384; to_f16.cu:6-18): convert once, reuse for
+// every matmul that takes the same input.
+//
+// Panels (small-M kernel).  K is cut in units of 256 weights.  For unit u and
+// column c the panel is PANEL_STRIDE = 272 halves:
+//     [0, 256)   the column's activations for k in [256u, 256u+256)
+//     [256, 272) per-32-weight means of those activations (Q4_K only),
+//                each as a hi and a lo half: entry 4p+{0,1} = hi of sub-blocks
+//                2p, 2p+1; entry 4p+{2,3} = their lo parts
+// laid out [unit][column][272].  A "column" is one token (single mode) or one
+// half of a token: with split = 1 token t owns columns 2t (x rounded to f16)
+// and 2t+1 (the rounding's remainder, again as f16), so that hi + lo carries
+// 22 bits of the f32 activation and the tensor-core products stay exact.
+//
+// Order of k inside [0, 256):
+//   natural (Q8_0, Q6_K): position = k.
+//   Q4_K: the kernel's lane c (0..3) owns the 64 weights [64c, 64c+64) and
+//   unpacks bytes (0, 2) and (1, 3) of each 32-bit word together, so each run
+//   of four k is stored in the order (0, 2, 1, 3); and the 8-byte runs are
+//   XOR-swizzled by c so that the four lanes of a row hit different banks:
+//     run  = 16c + 8*nib + (j ^ c)      k = 64c + 32*nib + 4j + e
+//     position = 4*run + {0,2,1,3}[e]
+#include "common.cuh"
+
+namespace dwim {
+
+size_t panel_bytes(size_t cols, int ncols) {
+    size_t units = (cols + 255) / 256;
+    return units * (size_t)ncols * PANEL_STRIDE * sizeof(__half);
+}
+
+__device__ __forceinline__ int panel_pos_q4k(int k) {
+    int c = k >> 6, nib = (k >> 5) & 1, j = (k >> 2) & 7, e = k & 3;
+    int run = 16 * c + 8 * nib + (j ^ c);
+    int pe = ((e & 1) << 1) | (e >> 1);   // 0,1,2,3 -> 0,2,1,3
+    return 4 * run + pe;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// grid (units, tokens), 256 threads: thread k converts x[t][256u + k].
+template <bool Q4K>
+__global__ void __launch_bounds__(256) panel_kernel(const float *__restrict__ x, size_t cols, int ncols, int split,
+                                                    __half *__restrict__ panels) {
+    int u = blockIdx.x, t = blockIdx.y, k = threadIdx.x;
+    size_t kk = (size_t)u * 256 + k;
+    float v = kk < cols ? x[(size_t)t * cols + kk] : 0.0f;
+    __half hi = to_f16_clamped(v);
+    float rem = v - __half2float(hi);
+    __half lo = to_f16_clamped(rem);
+    int pos = Q4K ? panel_pos_q4k(k) : k;
+    int col = split ? 2 * t : t;
+    __half *p = panels + ((size_t)u * ncols + col) * PANEL_STRIDE;
+    p[pos] = hi;
+    if (split) p[PANEL_STRIDE + pos] = lo;
+    // means of the 32 activations of each sub-block (a warp = a sub-block)
+    float mh = 0.0f, ml = 0.0f;
+    if (Q4K) {
+        mh = warp_sum(__half2float(hi)) * (1.0f / 32.0f);
+        ml = warp_sum(__half2float(lo)) * (1.0f / 32.0f);
+    }
+    if ((k & 31) == 0) {
+        int j = k >> 5;
+        int e = 256 + 4 * (j >> 1) + (j & 1);
+        __half a = to_f16_clamped(mh);
+        p[e] = a;
+        p[e + 2] = to_f16_clamped(mh - __half2float(a));
+        if (split) {
+            __half b = to_f16_clamped(ml);
+            p[PANEL_STRIDE + e] = b;
+            p[PANEL_STRIDE + e + 2] = to_f16_clamped(ml - __half2float(b));
+        }
+    }
+}
+
+int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels) {
+    if (n == 0 || cols == 0) return 0;
+    size_t units = (cols + 255) / 256;
+    if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one panel build: %zu", n);
+    dim3 grid((unsigned)units, (unsigned)n);
+    int ncols = (int)n * (split ? 2 : 1);
+    if (kind == SHADOW_PANEL_Q4K) panel_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, cols, ncols, split, panels);
+    else panel_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, cols, ncols, split, panels);
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}
+
+// Plain f16 rows for the tensor-core GEMM: out[t][k] = f16(x[t][k]), clamped
+// to +-65504 as the reference's to_f16 kernel does (prelude.cu:121-132).
+__global__ void f16_rows_kernel(const float4 *__restrict__ x, size_t n4, uint2 *__restrict__ out) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 v = x[i];
+        uint32_t a = to_f16_bits(v.x) | ((uint32_t)to_f16_bits(v.y) << 16);
+        uint32_t b = to_f16_bits(v.z) | ((uint32_t)to_f16_bits(v.w) << 16);
+        out[i] = make_uint2(a, b);
+    }
+}
+
+int build_f16_rows(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, __half *out) {
+    size_t total = n * cols;
+    if (total == 0) return 0;
+    if (total % 4) return fail(ctx, DWIM_B200_EINVAL, "f16 rows: length %zu is not a multiple of 4", total);
+    size_t n4 = total / 4;
+    unsigned grid = (unsigned)((n4 + 255) / 256 < (size_t)ctx->sm_count * 8 ? (n4 + 255) / 256 : (size_t)ctx->sm_count * 8);
+    f16_rows_kernel<<<grid, 256, 0, ctx->stream>>>((const float4 *)x, n4, (uint2 *)out);
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}
+
+}  // namespace dwim

@@ -1,0 +1,193 @@
+"""``B200``: the engine's ``Device`` operator interface (gpu/mod.rs:176-401)
+for the quantized matrix product, over the C ABI of ``libdwim_b200.so``.
+
+Method names, argument order and meaning follow the trait: ``upload``,
+``alloc``, ``resize``, ``read``, ``write``, ``matmul``, ``matmul_add``,
+``swiglu``, ``name``, ``memory``, ``batch``.  Where the trait's methods panic
+(a bad shape, a driver error) these raise ``DeviceError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import weakref
+
+import numpy as np
+
+from . import _lib
+from .tensor import Tensor, format_id, row_bytes
+
+
+class DeviceError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_lib.ERROR_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+class Buffer:
+    """A vector of f32 activations in device memory (``Device::Buffer``)."""
+
+    def __init__(self, dev: "B200", handle: int):
+        self._dev, self._h = dev, handle
+        self._fin = weakref.finalize(self, dev._free_buffer, handle)
+
+    def __len__(self) -> int:
+        return int(self._dev._L.dwim_b200_buffer_len(self._h))
+
+    @property
+    def ptr(self) -> int:
+        """Device address of the data."""
+        return int(self._dev._L.dwim_b200_buffer_ptr(self._h) or 0)
+
+
+class Weight:
+    """A weight matrix in device memory (``Device::Weight``)."""
+
+    def __init__(self, dev: "B200", handle: int, fmt: int, shape):
+        self._dev, self._h, self.fmt, self.shape = dev, handle, fmt, tuple(shape)
+        self._fin = weakref.finalize(self, dev._free_weight, handle)
+
+
+class B200:
+    def __init__(self, device: int = 0):
+        self._L = _lib.lib()
+        h = C.c_void_p()
+        rc = self._L.dwim_b200_open(device, C.byref(h))
+        if rc != 0:
+            raise DeviceError(rc, (self._L.dwim_b200_last_error(None) or b"").decode())
+        self._ctx = h.value
+        self._closed = False
+        self._fin = weakref.finalize(self, self._L.dwim_b200_close, self._ctx)
+
+    # -- plumbing ---------------------------------------------------------
+    def _check(self, rc: int):
+        if rc != 0:
+            raise DeviceError(rc, (self._L.dwim_b200_last_error(self._ctx) or b"").decode())
+
+    def _free_buffer(self, handle):
+        if not self._closed:
+            self._L.dwim_b200_buffer_free(self._ctx, handle)
+
+    def _free_weight(self, handle):
+        if not self._closed:
+            self._L.dwim_b200_weight_free(self._ctx, handle)
+
+    def close(self):
+        if not self._closed:
+            self._closed = True
+            self._fin()
+
+    # -- the trait ----------------------------------------------------------
+    def name(self) -> str:
+        buf = C.create_string_buffer(256)
+        self._check(self._L.dwim_b200_name(self._ctx, buf, 256))
+        return buf.value.decode()
+
+    def memory(self) -> int:
+        free = C.c_uint64()
+        self._check(self._L.dwim_b200_memory(self._ctx, C.byref(free)))
+        return free.value
+
+    def batch(self) -> int:
+        return int(self._L.dwim_b200_batch(self._ctx))
+
+    def upload(self, tensor: Tensor) -> Weight:
+        h = C.c_void_p()
+        data = tensor.data
+        self._check(self._L.dwim_b200_upload(self._ctx, tensor.fmt, tensor.rows, tensor.cols,
+                                             data.ctypes.data, data.size, C.byref(h)))
+        return Weight(self, h.value, tensor.fmt, tensor.shape)
+
+    def alloc(self, length: int) -> Buffer:
+        h = C.c_void_p()
+        self._check(self._L.dwim_b200_alloc(self._ctx, length, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def wrap(self, device_ptr: int, length: int) -> Buffer:
+        """A buffer over device memory the caller owns (e.g. a torch tensor)."""
+        h = C.c_void_p()
+        self._check(self._L.dwim_b200_wrap(self._ctx, device_ptr, length, C.byref(h)))
+        return Buffer(self, h.value)
+
+    def resize(self, buf: Buffer, length: int) -> None:
+        self._check(self._L.dwim_b200_resize(self._ctx, buf._h, length))
+
+    def read(self, buf: Buffer, out: np.ndarray | None = None) -> np.ndarray:
+        n = len(buf)
+        if out is None:
+            out = np.empty(n, np.float32)
+        assert out.dtype == np.float32 and out.size == n and out.flags.c_contiguous
+        self._check(self._L.dwim_b200_read(self._ctx, buf._h, out.ctypes.data, n))
+        return out
+
+    def write(self, buf: Buffer, data) -> None:
+        data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        self._check(self._L.dwim_b200_write(self._ctx, buf._h, data.ctypes.data, data.size))
+
+    def write_bf16(self, buf: Buffer, bits) -> None:
+        """Writes bf16 bit patterns (uint16); the buffer holds their f32 values."""
+        bits = np.ascontiguousarray(bits, dtype=np.uint16).reshape(-1)
+        self._check(self._L.dwim_b200_write_bf16(self._ctx, buf._h, bits.ctypes.data, bits.size))
+
+    def buffer(self, data) -> Buffer:
+        """alloc + write, as the reference tests' helper (gpu/tests.rs:142-146)."""
+        data = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
+        buf = self.alloc(data.size)
+        self.write(buf, data)
+        return buf
+
+    def matmul(self, out: Buffer, w: Weight, x: Buffer) -> None:
+        self._check(self._L.dwim_b200_matmul(self._ctx, out._h, w._h, x._h))
+
+    def matmul_add(self, x: Buffer, w: Weight, input: Buffer, scratch: Buffer | None = None) -> None:
+        self._check(self._L.dwim_b200_matmul_add(self._ctx, x._h, w._h, input._h, scratch._h if scratch else None))
+
+    def swiglu(self, out: Buffer, gate: Weight, up: Weight, x: Buffer, scratch: Buffer) -> None:
+        self._check(self._L.dwim_b200_swiglu(self._ctx, out._h, gate._h, up._h, x._h, scratch._h))
+
+    # -- beside the trait -----------------------------------------------------
+    def sync(self) -> None:
+        self._check(self._L.dwim_b200_sync(self._ctx))
+
+    def dequantize(self, w: Weight) -> np.ndarray:
+        """``Tensor::dequantize`` (gpu/mod.rs:138-168), computed on the device."""
+        out = np.empty(w.shape, np.float32)
+        self._check(self._L.dwim_b200_dequantize(self._ctx, w._h, out.ctypes.data, out.size))
+        return out
+
+    def quantize(self, fmt, weights) -> Tensor:
+        """Quantizes an f32 ``[rows, cols]`` matrix to GGUF blocks on the device."""
+        fmt = format_id(fmt)
+        weights = np.ascontiguousarray(weights, dtype=np.float32)
+        rows, cols = weights.shape
+        out = np.empty(rows * row_bytes(fmt, cols), np.uint8)
+        self._check(self._L.dwim_b200_quantize(self._ctx, fmt, rows, cols, weights.ctypes.data,
+                                               out.ctypes.data, out.size))
+        return Tensor(fmt, (rows, cols), out)
+
+    def gather_rows(self, out: Buffer, parts: Buffer, n: int, rows: int, world: int, align: int) -> None:
+        self._check(self._L.dwim_b200_gather_rows(self._ctx, out._h, parts._h, n, rows, world, align))
+
+    @property
+    def stream(self) -> int:
+        return int(self._L.dwim_b200_stream(self._ctx) or 0)
+
+    @property
+    def launches(self) -> int:
+        return int(self._L.dwim_b200_launches(self._ctx))
+
+    def timer_begin(self) -> None:
+        self._check(self._L.dwim_b200_timer_begin(self._ctx))
+
+    def timer_end(self) -> float:
+        ms = C.c_float()
+        self._check(self._L.dwim_b200_timer_end(self._ctx, C.byref(ms)))
+        return ms.value
+
+
+def shard_rows(rows: int, rank: int, world: int, align: int = 16):
+    """Rows [begin, end) of rank ``rank`` when a matrix is split by output rows."""
+    b, e = C.c_size_t(), C.c_size_t()
+    rc = _lib.lib().dwim_b200_shard_rows(rows, rank, world, align, C.byref(b), C.byref(e))
+    if rc != 0:
+        raise DeviceError(rc, "bad shard arguments")
+    return b.value, e.value

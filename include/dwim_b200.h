@@ -1,0 +1,173 @@
+/*
+ * dwim_b200 — the block-quantized matrix product of the dwim inference engine,
+ * hand-written for NVIDIA B200 (sm_100a), behind a flat C ABI.
+ *
+ * The entry points map one to one onto the hot-path methods of the engine's
+ * `trait Device` (gpu/mod.rs:176-401): a Rust `impl Device for B200` binds
+ * them with `extern "C"` and nothing else.  Each declaration names the trait
+ * method or reference function it replaces.
+ *
+ * Conventions
+ *   - Every function returns 0 on success and a negative DWIM_B200_E* code on
+ *     failure; the message is kept per context (dwim_b200_last_error).  No
+ *     exception crosses this boundary and nothing aborts.  (The trait's
+ *     methods are infallible and panic on misuse, gpu/cuda/mod.rs:485-500: a
+ *     binding turns a non-zero code into a panic.)
+ *   - A context is driven by one host thread at a time, as the reference's
+ *     device is (gpu/cuda/mod.rs:5-9).  All work of a context runs in order
+ *     on one CUDA stream; only read, sync, dequantize and quantize wait.
+ *   - Weights are GGUF blocks, row-major: rows * dwim_b200_row_bytes(fmt,
+ *     cols) bytes.  Activations are f32, one row of `cols` per token;
+ *     results are token-major, out[t * rows + r] (gpu/cpu.rs:144-148).
+ *   - There is no CPU fallback: without a CUDA device dwim_b200_open fails.
+ */
+#ifndef DWIM_B200_H
+#define DWIM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DWIM_B200_API __attribute__((visibility("default")))
+#else
+#define DWIM_B200_API
+#endif
+
+/* Weight formats, numbered as GGUF numbers its tensor types
+ * (inference/gguf.rs:28-33 knows 8 and 14; 12 is new to the engine). */
+enum {
+    DWIM_B200_Q8_0 = 8,  /* 32 weights: f16 d, 32 x i8            (34 B)  */
+    DWIM_B200_Q4_K = 12, /* 256 weights: f16 d, dmin, 12 B of 6-bit scales/mins, 128 B of nibbles (144 B) */
+    DWIM_B200_Q6_K = 14  /* 256 weights: ql[128] qh[64] i8 scales[16] f16 d (210 B) */
+};
+
+enum {
+    DWIM_B200_OK = 0,
+    DWIM_B200_EINVAL = -1,  /* a null handle, a bad shape or a bad length */
+    DWIM_B200_EFORMAT = -2, /* an unknown weight format, or cols not whole blocks */
+    DWIM_B200_ENOMEM = -3,  /* out of device memory */
+    DWIM_B200_ECUDA = -4,   /* the CUDA runtime reported an error */
+    DWIM_B200_ENODEV = -5,  /* no usable device (not sm_100) */
+    DWIM_B200_ETIMEOUT = -6 /* a bounded device-side wait gave up; see dwim_b200_status */
+};
+
+typedef struct dwim_b200_ctx dwim_b200_ctx;
+typedef struct dwim_b200_buffer dwim_b200_buffer;
+typedef struct dwim_b200_weight dwim_b200_weight;
+
+/* ---- the device ------------------------------------------------------- */
+
+/* Cuda::new (gpu/cuda/mod.rs:210-238): opens device `device`, creates the
+ * context's stream.  Fails with ENODEV on anything but compute capability 10.x. */
+DWIM_B200_API int dwim_b200_open(int device, dwim_b200_ctx **out);
+DWIM_B200_API int dwim_b200_close(dwim_b200_ctx *ctx);
+
+/* The message of the last failure on this context ("" if none).  With a null
+ * context: the last failure of dwim_b200_open on this thread. */
+DWIM_B200_API const char *dwim_b200_last_error(const dwim_b200_ctx *ctx);
+
+/* Device::name (gpu/mod.rs:188-189). */
+DWIM_B200_API int dwim_b200_name(const dwim_b200_ctx *ctx, char *buf, size_t cap);
+/* Device::memory (gpu/mod.rs:191-194): bytes free on the device. */
+DWIM_B200_API int dwim_b200_memory(const dwim_b200_ctx *ctx, uint64_t *free_bytes);
+/* Device::batch (gpu/mod.rs:196-204; 512 for the reference's CUDA device,
+ * gpu/cuda/mod.rs:47-48): most tokens one matmul should be given. */
+DWIM_B200_API size_t dwim_b200_batch(const dwim_b200_ctx *ctx);
+/* Waits for everything queued on the context (the reference has no such
+ * method: reading a buffer is its only wait, gpu/cuda/mod.rs:995-1000).
+ * Returns ETIMEOUT if a kernel's bounded wait gave up since the last call. */
+DWIM_B200_API int dwim_b200_sync(dwim_b200_ctx *ctx);
+/* The context's cudaStream_t, for callers that record their own events. */
+DWIM_B200_API void *dwim_b200_stream(const dwim_b200_ctx *ctx);
+/* The status word kernels write when a bounded wait runs out: 0 = none. */
+DWIM_B200_API int dwim_b200_status(dwim_b200_ctx *ctx, uint32_t *status);
+/* Number of kernels this context has launched since it was opened. */
+DWIM_B200_API uint64_t dwim_b200_launches(const dwim_b200_ctx *ctx);
+
+/* Timing on the context's own stream: begin records an event, end records a
+ * second one, waits for it and returns the milliseconds between them. */
+DWIM_B200_API int dwim_b200_timer_begin(dwim_b200_ctx *ctx);
+DWIM_B200_API int dwim_b200_timer_end(dwim_b200_ctx *ctx, float *ms);
+
+/* ---- activations -------------------------------------------------------- */
+
+/* Device::alloc (gpu/mod.rs:209-210): a zeroed buffer of `len` f32. */
+DWIM_B200_API int dwim_b200_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out);
+/* A buffer over device memory the caller owns (`len` f32 at `device_ptr`),
+ * e.g. the receive side of an NCCL collective.  Freeing the handle leaves
+ * the memory alone.  No counterpart in the reference (it is single-GPU). */
+DWIM_B200_API int dwim_b200_wrap(dwim_b200_ctx *ctx, float *device_ptr, size_t len, dwim_b200_buffer **out);
+/* Device::resize (gpu/mod.rs:216-219; gpu/cuda/mod.rs:986-993): sets the
+ * length, up to the allocated one; never reallocates. */
+DWIM_B200_API int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t len);
+/* Device::write (gpu/mod.rs:224-225): `len` must equal the buffer's length. */
+DWIM_B200_API int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len);
+/* As write, from bf16 bits (gpu/float.rs:5-8): the buffer holds the same
+ * values as f32 and remembers that they are exact in 16 bits. */
+DWIM_B200_API int dwim_b200_write_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const uint16_t *data, size_t len);
+/* Device::read (gpu/mod.rs:221-222): waits for the queued work. */
+DWIM_B200_API int dwim_b200_read(dwim_b200_ctx *ctx, const dwim_b200_buffer *buf, float *out, size_t len);
+DWIM_B200_API int dwim_b200_buffer_free(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
+DWIM_B200_API size_t dwim_b200_buffer_len(const dwim_b200_buffer *buf);
+/* The device address of the buffer's f32 data. */
+DWIM_B200_API float *dwim_b200_buffer_ptr(const dwim_b200_buffer *buf);
+
+/* ---- weights ------------------------------------------------------------ */
+
+/* Bytes of one row of `cols` weights in GGUF layout, 0 if the format is
+ * unknown or cols is not whole blocks (inference/gguf.rs:36-53). */
+DWIM_B200_API size_t dwim_b200_row_bytes(int fmt, size_t cols);
+
+/* Device::upload (gpu/mod.rs:206-207; gpu/cuda/mod.rs:905-951): copies a
+ * [rows, cols] matrix of GGUF blocks to the device; the host memory is not
+ * kept.  `bytes` must be rows * row_bytes. */
+DWIM_B200_API int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols,
+                                   const void *blocks, size_t bytes, dwim_b200_weight **out);
+DWIM_B200_API int dwim_b200_weight_free(dwim_b200_ctx *ctx, dwim_b200_weight *w);
+DWIM_B200_API int dwim_b200_weight_shape(const dwim_b200_weight *w, int *fmt, size_t *rows, size_t *cols);
+
+/* Tensor::dequantize (gpu/mod.rs:138-168), run on the device: `len` =
+ * rows * cols f32, row-major, to host memory.  Bit-exact with the reference's
+ * decoders (inference/quants.rs:59-104) — the tests' ground truth. */
+DWIM_B200_API int dwim_b200_dequantize(dwim_b200_ctx *ctx, const dwim_b200_weight *w, float *out, size_t len);
+
+/* Quantizes a host f32 [rows, cols] matrix to GGUF blocks in host memory, on
+ * the device.  Q8_0 follows quantize_q8_0_row (gpu/quant.rs:31-46, 154-180);
+ * the Q4_K and Q6_K quantizers have no reference counterpart. */
+DWIM_B200_API int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols,
+                                     const float *weights, void *blocks, size_t bytes);
+
+/* ---- the product -------------------------------------------------------- */
+
+/* Device::matmul (gpu/mod.rs:251-254): out[t] = w . x[t] for each of the
+ * n = len(x)/cols rows of x; len(out) must be n * rows. */
+DWIM_B200_API int dwim_b200_matmul(dwim_b200_ctx *ctx, dwim_b200_buffer *out,
+                                   const dwim_b200_weight *w, dwim_b200_buffer *x);
+/* Device::matmul_add (gpu/mod.rs:256-268): x += w . input.  `scratch` is as
+ * long as x and is left undefined (it may be null: the sum is fused). */
+DWIM_B200_API int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, const dwim_b200_weight *w,
+                                       dwim_b200_buffer *input, dwim_b200_buffer *scratch);
+/* Device::swiglu (gpu/mod.rs:270-285): out = silu(gate . x) * (up . x).
+ * `scratch` is as long as out and is left undefined. */
+DWIM_B200_API int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *gate,
+                                   const dwim_b200_weight *up, dwim_b200_buffer *x, dwim_b200_buffer *scratch);
+
+/* ---- sharding across GPUs (no counterpart in the reference) -------------- */
+
+/* The rows rank `rank` of `world` holds when a matrix is split by output
+ * rows at multiples of `align`: [*begin, *end). */
+DWIM_B200_API int dwim_b200_shard_rows(size_t rows, int rank, int world, size_t align,
+                                       size_t *begin, size_t *end);
+/* Re-assembles an all-gathered result: `parts` holds, for each rank in turn,
+ * that rank's [n, rows_of_rank] slice; `out` gets the token-major [n, rows]. */
+DWIM_B200_API int dwim_b200_gather_rows(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *parts,
+                                        size_t n, size_t rows, int world, size_t align);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DWIM_B200_H */

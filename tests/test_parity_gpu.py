@@ -1,0 +1,343 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Modelled on the reference's generic device suite (gpu/tests.rs): the same
+deterministic generator, the same shape lists, the same two error checks —
+plus bit-exact checks of the decoders and quantizers, the committed golden
+cases, and the stricter "max relative error 1e-3" bar.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from conftest import close, close_batch, max_rel_err
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+KATS = json.load(open(os.path.join(HERE, "golden", "reference_kats.json")))
+FORMATS = ("q4_k", "q6_k", "q8_0")
+
+# max |got - want| / max(|want|, rms(want)); the matmul bar
+TOL = 1e-3
+
+
+def kcols(fmt, cols):
+    """The reference's shapes with cols made whole blocks of the format."""
+    per = 32 if fmt == "q8_0" else 256
+    return (cols + per - 1) // per * per
+
+
+def lcg_weights(oracle, rng, fmt, rows, cols):
+    """Rng::q8_0-style (gpu/tests.rs:87-103): a row of LCG floats at a time, quantized."""
+    w = rng.floats(rows * cols).reshape(rows, cols)
+    return oracle.quantize(fmt, w)
+
+
+def upload(dev, fmt, rows, cols, blocks):
+    from dwim_b200 import Tensor
+    return dev.upload(Tensor(fmt, (rows, cols), blocks))
+
+
+# ---- device plumbing (gpu/tests.rs:166-186, 962-975) --------------------------------
+def test_write_and_read_round_trip(dev, oracle):
+    data = oracle.Lcg(1).floats(100_003)
+    assert np.array_equal(dev.read(dev.buffer(data)), data)
+
+
+def test_alloc_is_zeroed_and_resize_keeps_capacity(dev):
+    from dwim_b200 import DeviceError
+    buf = dev.alloc(1000)
+    assert not dev.read(buf).any()
+    dev.write(buf, np.arange(1000, dtype=np.float32))
+    dev.resize(buf, 10)
+    assert np.array_equal(dev.read(buf), np.arange(10, dtype=np.float32))
+    dev.resize(buf, 1000)
+    assert np.array_equal(dev.read(buf)[:10], np.arange(10, dtype=np.float32))
+    with pytest.raises(DeviceError):
+        dev.resize(buf, 1001)
+    assert len(dev.read(dev.alloc(0))) == 0
+
+
+def test_device_reports_itself(dev):
+    assert "B200" in dev.name()
+    assert dev.memory() > 1 << 30
+    assert dev.batch() == 2048
+
+
+# ---- decoders: bit-exact -----------------------------------------------------------------
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_dequantize_is_bit_exact(dev, oracle, fmt):
+    rng = np.random.default_rng(21)
+    for rows, cols in [(1, 256), (37, 1024), (300, 5120)]:
+        w = (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)
+        blocks = oracle.quantize(fmt, w)
+        got = dev.dequantize(upload(dev, fmt, rows, cols, blocks))
+        want = oracle.dequantize(fmt, blocks, rows, cols)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_dequantize_random_bit_patterns_is_bit_exact(dev, oracle, fmt):
+    """Every field at arbitrary values, not only what a quantizer emits."""
+    from dwim_b200 import row_bytes
+    rng = np.random.default_rng(22)
+    rows, cols = 64, 1024
+    blocks = rng.integers(0, 256, rows * row_bytes(fmt, cols), dtype=np.uint8)
+    # keep the f16 scales finite (inf/nan scales are not weights)
+    size = {"q4_k": 144, "q6_k": 210, "q8_0": 34}[fmt]
+    b = blocks.reshape(-1, size)
+    for off in {"q4_k": (1, 3), "q6_k": (209,), "q8_0": (1,)}[fmt]:
+        b[:, off] &= 0x3B          # exponent below 0x1f
+    got = dev.dequantize(upload(dev, fmt, rows, cols, blocks))
+    want = oracle.dequantize(fmt, blocks, rows, cols)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_q6_k_known_answers_on_the_device(dev, oracle):
+    # inference/quants.rs:236-275, decoded by the device
+    block = np.zeros(210, np.uint8)
+    block[37], block[128 + 5], block[192 + 2] = 0b1010, 0b1100, 3
+    block[208:210] = np.frombuffer(oracle.to_f16([0.25]).tobytes(), np.uint8)
+    out = dev.dequantize(upload(dev, "q6_k", 1, 256, block))[0]
+    assert out[37] == 19.5 and all(out[i] == -24.0 for i in range(32, 48) if i != 37)
+    assert not out[:32].any() and not out[48:].any()
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_quantize_is_byte_exact(dev, oracle, fmt):
+    rng = np.random.default_rng(23)
+    w = (0.02 * rng.standard_normal((96, 2048))).astype(np.float32)
+    w[0, :256] = 0.0
+    w[1, 7] = 5.0
+    w[2, :64] = np.float32(1e-30)
+    w[3, 300] = -65536.0
+    assert np.array_equal(dev.quantize(fmt, w).data, oracle.quantize(fmt, w))
+    lcg = oracle.Lcg(5).floats(64 * 512).reshape(64, 512)
+    assert np.array_equal(dev.quantize(fmt, lcg).data, oracle.quantize(fmt, lcg))
+
+
+# ---- matmul ---------------------------------------------------------------------------
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_block_matmul_matches_cpu(dev, oracle, fmt):
+    """block_matmul_matches_cpu (gpu/tests.rs:219-262): the reference's shapes, its
+    generator (weights Rng(80) shape after shape, x = Rng(rows + n)), its checks."""
+    rng = oracle.Lcg(80)
+    for rows, cols, n in KATS["matmul_shapes"]["shapes"]:
+        cols = kcols(fmt, cols)
+        blocks = lcg_weights(oracle, rng, fmt, rows, cols)
+        x = oracle.Lcg(rows + n).floats(n * cols)
+        want = oracle.matmul(fmt, blocks, rows, cols, x)
+        out = dev.alloc(n * rows)
+        dev.matmul(out, upload(dev, fmt, rows, cols, blocks), dev.buffer(x))
+        got = dev.read(out).reshape(n, rows)
+        what = f"{fmt} {rows}x{cols} n={n}"
+        if n == 1:
+            close(got, want, 1e-4)
+        close_batch(got, want, what)
+        assert max_rel_err(got, want) <= TOL, what
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n", [1, 2, 4, 5, 8, 9, 15, 16, 17])
+def test_matmul_token_counts_at_model_width(dev, oracle, fmt, n):
+    rng = np.random.default_rng(31 + n)
+    rows, cols = 333, 5120
+    blocks = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    out = dev.alloc(n * rows)
+    dev.matmul(out, upload(dev, fmt, rows, cols, blocks), dev.buffer(x))
+    got, want = dev.read(out).reshape(n, rows), oracle.matmul(fmt, blocks, rows, cols, x)
+    assert max_rel_err(got, want) <= TOL
+    # the small-M kernel keeps products exact: expect fp32-summation noise only
+    assert max_rel_err(got, want) <= 2e-5
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_matmul_bf16_activations(dev, oracle, fmt):
+    """Config 2's inputs: rows of N(0,1) scaled to RMS 1, rounded to bf16."""
+    rng = np.random.default_rng(41)
+    rows, cols = 1000, 5120
+    blocks = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    weight = upload(dev, fmt, rows, cols, blocks)
+    for n in (1, 7, 16):
+        x = rng.standard_normal((n, cols)).astype(np.float32)
+        x /= np.sqrt((x * x).mean(1, keepdims=True))
+        bits = oracle.to_bf16(x)
+        xb = dev.alloc(n * cols)
+        dev.write_bf16(xb, bits)
+        assert np.array_equal(dev.read(xb), oracle.bf16(bits))
+        out = dev.alloc(n * rows)
+        dev.matmul(out, weight, xb)
+        want = oracle.matmul(fmt, blocks, rows, cols, oracle.bf16(bits))
+        assert max_rel_err(dev.read(out).reshape(n, rows), want) <= 2e-5
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_matmul_golden_cases(dev, fmt):
+    """The committed oracle outputs (tests/golden/oracle_cases.npz)."""
+    g = np.load(os.path.join(HERE, "golden", "oracle_cases.npz"))
+    w, x, blocks = g[f"{fmt}_w"], g[f"{fmt}_x"], g[f"{fmt}_blocks"]
+    rows, cols = w.shape
+    n = x.shape[0]
+    assert np.array_equal(dev.quantize(fmt, w).data, blocks)
+    weight = upload(dev, fmt, rows, cols, blocks)
+    assert np.array_equal(dev.dequantize(weight).view(np.uint32), g[f"{fmt}_dequant"].view(np.uint32))
+    out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
+    dev.matmul(out, weight, dev.buffer(x))
+    assert max_rel_err(dev.read(out), g[f"{fmt}_matmul"]) <= 2e-5
+    dev.swiglu(out, weight, upload(dev, fmt, rows, cols, g[f"{fmt}_up_blocks"]), dev.buffer(x), scratch)
+    assert max_rel_err(dev.read(out), g[f"{fmt}_swiglu"]) <= 1e-4
+
+
+def test_shadow_is_rebuilt_after_a_write(dev, oracle):
+    """One input buffer reused: across formats (different operand layouts) and
+    after being overwritten."""
+    rng = np.random.default_rng(43)
+    rows, cols = 64, 512
+    w = (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)
+    xb, out = dev.alloc(2 * cols), dev.alloc(2 * rows)
+    for trial in range(2):
+        x = rng.standard_normal((2, cols)).astype(np.float32)
+        dev.write(xb, x)
+        for fmt in FORMATS:
+            blocks = oracle.quantize(fmt, w)
+            dev.matmul(out, upload(dev, fmt, rows, cols, blocks), xb)
+            assert max_rel_err(dev.read(out), oracle.matmul(fmt, blocks, rows, cols, x)) <= 2e-5
+
+
+# ---- fused operators (gpu/tests.rs:816-871) ---------------------------------------------
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_swiglu_matches_cpu(dev, oracle, fmt):
+    rng = oracle.Lcg(22)
+    for rows, cols, n in KATS["fused_shapes"]["shapes"]:
+        cols = kcols(fmt, cols)
+        gate, up = lcg_weights(oracle, rng, fmt, rows, cols), lcg_weights(oracle, rng, fmt, rows, cols)
+        x = rng.floats(n * cols)
+        want = oracle.swiglu(fmt, gate, up, rows, cols, x)
+        out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
+        dev.swiglu(out, upload(dev, fmt, rows, cols, gate), upload(dev, fmt, rows, cols, up), dev.buffer(x), scratch)
+        got = dev.read(out)
+        close_batch(got, want, f"{fmt} {rows}x{cols} n={n}")
+        assert max_rel_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+def test_matmul_add_matches_cpu(dev, oracle, fmt):
+    rng = oracle.Lcg(23)
+    for rows, cols, n in KATS["fused_shapes"]["shapes"]:
+        cols = kcols(fmt, cols)
+        blocks = lcg_weights(oracle, rng, fmt, rows, cols)
+        inp, x = rng.floats(n * cols), rng.floats(n * rows)
+        want = oracle.matmul_add(fmt, blocks, rows, cols, inp, x).ravel()
+        out, scratch = dev.buffer(x), dev.alloc(n * rows)
+        dev.matmul_add(out, upload(dev, fmt, rows, cols, blocks), dev.buffer(inp), scratch)
+        got = dev.read(out)
+        # what was added, which is what a batch's error is a part of
+        close_batch(got - x, want - x, f"{fmt} {rows}x{cols} n={n}")
+        assert max_rel_err(got - x, want - x) <= TOL
+
+
+# ---- misuse is an error code, never a fault (the trait's panics) ------------------------------
+def test_misuse_is_reported(dev, oracle):
+    from dwim_b200 import DeviceError, Tensor
+    rng = np.random.default_rng(47)
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((32, 512))).astype(np.float32))
+    w = upload(dev, "q4_k", 32, 512, blocks)
+    with pytest.raises(DeviceError):               # x is not rows of cols
+        dev.matmul(dev.alloc(32), w, dev.alloc(500))
+    with pytest.raises(DeviceError):               # out has the wrong length
+        dev.matmul(dev.alloc(33), w, dev.alloc(512))
+    with pytest.raises(DeviceError):               # write of the wrong length
+        dev.write(dev.alloc(8), np.zeros(9, np.float32))
+    with pytest.raises(DeviceError):               # gate and up differ
+        w2 = upload(dev, "q4_k", 16, 512, blocks[: 16 * 288])
+        dev.swiglu(dev.alloc(32), w, w2, dev.alloc(512), dev.alloc(32))
+    L = dev._L
+    import ctypes as C
+    h = C.c_void_p()
+    assert L.dwim_b200_upload(dev._ctx, 12, 32, 512, blocks.ctypes.data, blocks.size - 1, C.byref(h)) == -1   # truncated
+    assert L.dwim_b200_upload(dev._ctx, 2, 32, 512, blocks.ctypes.data, blocks.size, C.byref(h)) == -2        # Q4_0: unknown here
+    assert L.dwim_b200_upload(dev._ctx, 12, 32, 500, blocks.ctypes.data, blocks.size, C.byref(h)) == -2       # not whole blocks
+    assert b"blocks" in L.dwim_b200_last_error(dev._ctx)
+    # the device still works afterwards
+    out = dev.alloc(32)
+    x = rng.standard_normal(512).astype(np.float32)
+    dev.matmul(out, w, dev.buffer(x))
+    assert max_rel_err(dev.read(out), oracle.matmul("q4_k", blocks, 32, 512, x)) <= 2e-5
+    dev.sync()
+
+
+def test_empty_inputs(dev, oracle):
+    blocks = oracle.quantize("q8_0", np.ones((4, 64), np.float32))
+    w = upload(dev, "q8_0", 4, 64, blocks)
+    dev.matmul(dev.alloc(0), w, dev.alloc(0))       # no tokens
+    w0 = upload(dev, "q8_0", 0, 64, np.zeros(0, np.uint8))
+    dev.matmul(dev.alloc(0), w0, dev.alloc(64))     # no rows
+    dev.sync()
+
+
+# ---- BASELINE's full sizes: oracle on a row sample + size-independent properties ------------------
+def full_size_case(dev, oracle, fmt, rows, cols, n, seed, bf16=False):
+    rng = np.random.default_rng(seed)
+    w = (0.02 * rng.standard_normal((rows, cols), dtype=np.float32)).astype(np.float32)
+    t = dev.quantize(fmt, w)
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    weight = dev.upload(t)
+    xb = dev.alloc(n * cols)
+    if bf16:
+        bits = oracle.to_bf16(x)
+        x = oracle.bf16(bits).reshape(n, cols)
+        dev.write_bf16(xb, bits)
+    else:
+        dev.write(xb, x)
+    out = dev.alloc(n * rows)
+    dev.matmul(out, weight, xb)
+    got = dev.read(out).reshape(n, rows)
+    # (1) the oracle on every row
+    want = oracle.matmul(fmt, t.data, rows, cols, x)
+    assert max_rel_err(got, want) <= TOL
+    # (2) the device quantizer wrote the oracle's bytes (a row sample) and decodes them bit-exactly
+    sample = rng.choice(rows, 64, replace=False)
+    assert np.array_equal(t.select_rows(sample).data, oracle.quantize(fmt, w[sample]))
+    # (3) linearity: W.(2x) = 2 W.x (a power of two scales every term; only
+    # f16-subnormal remainders of tiny activations can round differently)
+    dev.write(xb, 2.0 * x)
+    out2 = dev.alloc(n * rows)
+    dev.matmul(out2, weight, xb)
+    assert max_rel_err(dev.read(out2).reshape(n, rows), 2.0 * got) <= 1e-6
+    # (4) a second run gives the same bits (fixed summation order)
+    dev.write(xb, x)
+    dev.matmul(out2, weight, xb)
+    assert np.array_equal(dev.read(out2).reshape(n, rows), got)
+    return got, want
+
+
+def test_config1_q4_k_gemv_full_size(dev, oracle):
+    """BASELINE config 1: Q4_K [17408, 5120] . x[1, 5120], W seed 0, x seed 1."""
+    w = (0.02 * np.random.default_rng(0).standard_normal((17408, 5120), dtype=np.float32))
+    x = np.random.default_rng(1).standard_normal((1, 5120)).astype(np.float32)
+    t = dev.quantize("q4_k", w)
+    assert t.data.size == 50_135_040
+    weight = dev.upload(t)
+    assert np.array_equal(dev.dequantize(weight).view(np.uint32),
+                          oracle.dequantize("q4_k", t.data, 17408, 5120).view(np.uint32))
+    out = dev.alloc(17408)
+    dev.matmul(out, weight, dev.buffer(x))
+    got, want = dev.read(out), oracle.matmul("q4_k", t.data, 17408, 5120, x).ravel()
+    close(got, want, 1e-4)
+    assert max_rel_err(got, want) <= 2e-5
+    # against the unquantized product: within quantization noise (a sanity check on the format itself)
+    exact = (w.astype(np.float64) @ x[0].astype(np.float64))
+    assert np.sqrt(np.mean((got - exact) ** 2)) < 0.12 * np.sqrt(np.mean(exact ** 2))
+
+
+@pytest.mark.parametrize("fmt,rows,cols,n", [
+    ("q4_k", 12288, 5120, 8), ("q8_0", 5120, 5120, 8), ("q4_k", 5120, 17408, 4), ("q6_k", 151936, 5120, 1)])
+def test_config3_shapes_full_size(dev, oracle, fmt, rows, cols, n):
+    full_size_case(dev, oracle, fmt, rows, cols, n, seed=3)
+
+
+def test_config2_q4_k_m16_bf16_full_size(dev, oracle):
+    full_size_case(dev, oracle, "q4_k", 17408, 5120, 16, seed=2, bf16=True)
