@@ -273,15 +273,19 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
     w->v.rows = rows;
     w->v.cols = cols;
     w->v.qrow = dev_quant_row_bytes(fmt, cols);
+    w->v.qpitch = dev_quant_pitch(fmt, cols);
     w->v.srow = dev_scale_row_elems(fmt, cols);
     uint8_t *staging = nullptr;
-    cudaError_t e = cudaMalloc(&w->quants_alloc, rows * w->v.qrow + WEIGHT_SLACK);
+    cudaError_t e = cudaMalloc(&w->quants_alloc, rows * w->v.qpitch + WEIGHT_SLACK);
+    // the padding between rows is read by the bulk copies: keep it defined
+    if (e == cudaSuccess && w->v.qpitch != w->v.qrow)
+        e = cudaMemsetAsync(w->quants_alloc, 0, rows * w->v.qpitch, ctx->stream);
     if (e == cudaSuccess && w->v.srow) e = cudaMalloc(&w->scales_alloc, rows * w->v.srow * sizeof(__half) + WEIGHT_SLACK);
-    if (e == cudaSuccess) e = cudaMemsetAsync((uint8_t *)w->quants_alloc + rows * w->v.qrow, 0, WEIGHT_SLACK, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync((uint8_t *)w->quants_alloc + rows * w->v.qpitch, 0, WEIGHT_SLACK, ctx->stream);
     int rc = 0;
     if (e == cudaSuccess && bytes) {
         if (fmt == Q4_K) {
-            e = cudaMemcpyAsync(w->quants_alloc, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
+            e = cudaMemcpy2DAsync(w->quants_alloc, w->v.qpitch, blocks, rb, rb, rows, cudaMemcpyHostToDevice, ctx->stream);
         } else {
             e = cudaMalloc(&staging, bytes);
             if (e == cudaSuccess) e = cudaMemcpyAsync(staging, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
@@ -407,8 +411,8 @@ static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b2
     size_t n = x->len / v.cols;
     REQUIRE(ctx, out_len == n * v.rows, DWIM_B200_EINVAL, "%s: output of %zu floats for %zu tokens of %zu rows", what,
             out_len, n, v.rows);
-    REQUIRE(ctx, out != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
     if (n == 0 || v.rows == 0) return 0;
+    REQUIRE(ctx, out != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
     if (n > SMALL_M_MAX && gemm_available()) {
         int rc = ensure_shadow(ctx, x, SHADOW_F16_ROWS, v.cols, 0);
         if (rc) return rc;

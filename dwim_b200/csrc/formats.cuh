@@ -13,6 +13,10 @@
 //   Q8_0: quants [rows][cols] i8                scales [rows][pad8(cols/32)] f16
 //   Q6_K: quants [rows][cols/256][208]          scales [rows][pad8(cols/256)] f16
 //         (208 = ql 128 | qh 64 | sub-scales 16)
+// Rows of every quant array sit `qpitch` bytes apart: the row's bytes rounded
+// up to an odd number of 16-byte steps.  A tile of consecutive rows is then
+// one contiguous run of HBM (one bulk copy into shared memory) and, once
+// there, the eight rows a warp reads together fall in different banks.
 #pragma once
 #include <cuda_fp16.h>
 #include <stdint.h>
@@ -45,6 +49,10 @@ __host__ __device__ inline size_t dev_quant_row_bytes(int fmt, size_t cols) {
     default: return cols / 256 * Q6_K_DEV;
     }
 }
+__host__ __device__ inline size_t dev_quant_pitch(int fmt, size_t cols) {
+    size_t b = dev_quant_row_bytes(fmt, cols);
+    return (b / 16) % 2 == 0 ? b + 16 : b;
+}
 __host__ __device__ inline size_t dev_scale_row_elems(int fmt, size_t cols) {
     switch (fmt) {
     case Q8_0: return pad8(cols / 32);
@@ -57,22 +65,27 @@ __host__ __device__ inline size_t dev_scale_row_elems(int fmt, size_t cols) {
 struct WeightView {
     int fmt;
     size_t rows, cols;
-    const uint8_t *quants;   // [rows][qrow]
+    const uint8_t *quants;   // [rows][qpitch]
     const __half *scales;    // [rows][srow] (null for Q4_K)
-    size_t qrow;             // bytes per row of quants
+    size_t qrow;             // bytes of quants in a row
+    size_t qpitch;           // bytes from one row to the next
     size_t srow;             // f16 per row of scales
 };
 
 // ---- f16 ------------------------------------------------------------------
 // gpu/float.rs:38-48: exact.
-__device__ __forceinline__ float from_f16_bits(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ float from_f16_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 // gpu/float.rs:13-28: nearest even, clamped to +-65504 instead of overflowing.
-__device__ __forceinline__ uint16_t to_f16_bits(float x) {
+// The conversion goes through PTX and comes back as a 32-bit integer: with
+// the 16-bit intrinsic types the compiler was seen to drop the low byte of
+// the result when it was stored a byte at a time.
+__device__ __forceinline__ uint32_t to_f16_bits(float x) {
     float a = fminf(fabsf(x), 65504.0f);
-    uint16_t h = __half_as_ushort(__float2half_rn(a));
-    return h | (uint16_t)((__float_as_uint(x) >> 16) & 0x8000u);
+    uint32_t h;
+    asm("{\n\t.reg .b16 t;\n\tcvt.rn.f16.f32 t, %1;\n\tmov.b32 %0, {t, t};\n\t}" : "=r"(h) : "f"(a));
+    return (h & 0x7fffu) | ((__float_as_uint(x) >> 16) & 0x8000u);
 }
-__device__ __forceinline__ __half to_f16_clamped(float x) { return __ushort_as_half(to_f16_bits(x)); }
+__device__ __forceinline__ __half to_f16_clamped(float x) { return __ushort_as_half((unsigned short)to_f16_bits(x)); }
 
 // ---- Q4_K -----------------------------------------------------------------
 // The 6-bit scale and minimum of sub-block j from the block's 12 bytes.

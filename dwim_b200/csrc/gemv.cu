@@ -27,6 +27,7 @@
 //     fixed order (deterministic), then the epilogue stores, adds to, or
 //     SwiGLU-combines the output (modes after prelude.cu:29-35).
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -54,10 +55,25 @@ struct GemvArgs {
     int stages;
     int q_stride;            // bytes between rows of a stage's quant region
     int s_off, s_stride;     // scale region
-    int x_off;               // panel region
+    int x_off;               // panel region (when the panels travel with the stages)
     int stage_bytes;
+    int whole_rows;          // 1: a stage holds whole rows (kc == units): one copy for the tile's quants, one for its scales
+    int x_resident;          // 1: the launch's panels sit in shared memory for the CTA's whole life
+    int xres_bytes;
     uint32_t *status;
+    unsigned long long *trace;   // debugging only: clock stamps of CTA 0 (null in normal use)
 };
+
+// Debug trace: (clock, tag, iteration) stamps of CTA 0, 200 slots per warp.
+#define TRACE_SLOTS 200
+__device__ __forceinline__ void trace(const GemvArgs &a, int &n, int tag, uint32_t it) {
+    if (a.trace && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && n < TRACE_SLOTS) {
+        unsigned long long *p = a.trace + 2 * ((threadIdx.x >> 5) * TRACE_SLOTS + n);
+        p[0] = clock64();
+        p[1] = ((unsigned long long)tag << 32) | it;
+        n++;
+    }
+}
 
 // ---------------------------------------------------------------------------
 // PTX helpers
@@ -73,11 +89,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Non-blocking test of a barrier phase.  (mbarrier.try_wait may suspend the
+// thread, and on this part a suspended waiter is only woken on a coarse timer
+// tick of about 2 us: kernels built on it ran in multiples of 2.048 us.)
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -97,7 +116,8 @@ __device__ __forceinline__ uint64_t globaltimer() {
 __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
     uint64_t start = globaltimer();
     for (;;) {
-        if (mbar_try(bar, parity)) return;
+        for (int i = 0; i < 256; i++)
+            if (mbar_try(bar, parity)) return;
         if (*(volatile uint32_t *)status != 0) return;
         if (globaltimer() - start > WAIT_LIMIT_NS) {
             atomicOr(status, code);
@@ -106,7 +126,10 @@ __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, uint3
     }
 }
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
-    if (!mbar_try(bar, parity)) mbar_wait_slow(bar, parity, status, code);
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+        if (mbar_try(bar, parity)) return;
+    mbar_wait_slow(bar, parity, status, code);
 }
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -167,7 +190,7 @@ __device__ __forceinline__ float h2f_hi(uint32_t v) { return __half2float(__usho
 // D += A (16 rows x 16 k, f16) * B (16 k x 8 columns, f16), fp32.
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -231,7 +254,7 @@ __device__ __forceinline__ Q4kScales q4k_scales(const uint4 &hdr, int c) {
 }
 
 template <int NT>
-__device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int ncols, const uint32_t (&xo)[4],
+__device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int xu, int ncols, const uint32_t (&xo)[4],
                                          float (&acc)[NT][4]) {
     const uint32_t ba = L.row_a + ul * 144, bb = L.row_b + ul * 144;
     const uint4 ha = lds128(ba), hb = lds128(bb);
@@ -245,14 +268,15 @@ __device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int ncols, const
         qb[4] = u1.x; qb[5] = u1.y; qb[6] = u1.z; qb[7] = u1.w;
     }
     const Q4kScales sa = q4k_scales(ha, L.c), sb = q4k_scales(hb, L.c);
-    float c1[NT][4], c2[NT][4];
+    // two independent accumulator chains (low / high nibbles) keep the tensor pipe busy
+    float c1[NT][4], c1h[NT][4], c2[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) c1[nt][i] = c2[nt][i] = 0.0f;
+        for (int i = 0; i < 4; i++) c1[nt][i] = c1h[nt][i] = c2[nt][i] = 0.0f;
     uint32_t xb[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 128 * L.c;
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 128 * L.c;
 
 #pragma unroll
     for (int j = 0; j < 8; j++) {
@@ -275,18 +299,18 @@ __device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int ncols, const
                 x1 = lds64(xb[nt] + 64 + off);   // sub-block 2c+1 (high nibbles)
             }
             mma16816(c1[nt], a_le, b_le, a_lo, b_lo, x0.x, x0.y);
-            mma16816(c1[nt], a_he, b_he, a_ho, b_ho, x1.x, x1.y);
+            mma16816(c1h[nt], a_he, b_he, a_ho, b_ho, x1.x, x1.y);
         }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
         uint2 xm = make_uint2(0, 0);
-        if (L.xv[nt]) xm = lds64(L.x[nt] + ul * ncols * PANEL_BYTES + 512 + 8 * L.c);
+        if (L.xv[nt]) xm = lds64(L.x[nt] + xu * ncols * PANEL_BYTES + 512 + 8 * L.c);
         mma16816(c2[nt], sa.mins, sb.mins, sa.mins, sb.mins, xm.x, xm.y);
-        acc[nt][0] += sa.d * c1[nt][0] - sa.dmin32 * c2[nt][0];
-        acc[nt][1] += sa.d * c1[nt][1] - sa.dmin32 * c2[nt][1];
-        acc[nt][2] += sb.d * c1[nt][2] - sb.dmin32 * c2[nt][2];
-        acc[nt][3] += sb.d * c1[nt][3] - sb.dmin32 * c2[nt][3];
+        acc[nt][0] += sa.d * (c1[nt][0] + c1h[nt][0]) - sa.dmin32 * c2[nt][0];
+        acc[nt][1] += sa.d * (c1[nt][1] + c1h[nt][1]) - sa.dmin32 * c2[nt][1];
+        acc[nt][2] += sb.d * (c1[nt][2] + c1h[nt][2]) - sb.dmin32 * c2[nt][2];
+        acc[nt][3] += sb.d * (c1[nt][3] + c1h[nt][3]) - sb.dmin32 * c2[nt][3];
     }
 }
 
@@ -301,13 +325,13 @@ __device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t &p01, uint32_t &
 }
 
 template <int NT>
-__device__ __forceinline__ void unit_q8_0(const Lane &L, int ul, int ncols, float (&acc)[NT][4]) {
+__device__ __forceinline__ void unit_q8_0(const Lane &L, int ul, int xu, int ncols, float (&acc)[NT][4]) {
     const uint32_t qa = L.row_a + ul * 256 + 8 * L.c, qb = L.row_b + ul * 256 + 8 * L.c;
     const uint4 sa = lds128(L.srow_a + ul * 16), sb = lds128(L.srow_b + ul * 16);
     const uint32_t sca[4] = {sa.x, sa.y, sa.z, sa.w}, scb[4] = {sb.x, sb.y, sb.z, sb.w};
     uint32_t xb[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 16 * L.c;
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 16 * L.c;
 #pragma unroll
     for (int blk = 0; blk < 8; blk++) {
         const uint2 wa = lds64(qa + 32 * blk), wb = lds64(qb + 32 * blk);
@@ -345,7 +369,7 @@ __device__ __forceinline__ float s8_byte_to_f32(uint32_t word_xor80, int b) {
 }
 
 template <int NT>
-__device__ __forceinline__ void unit_q6k(const Lane &L, int ul, int ncols, int d_index, float (&acc)[NT][4]) {
+__device__ __forceinline__ void unit_q6k(const Lane &L, int ul, int xu, int ncols, int d_index, float (&acc)[NT][4]) {
     const uint32_t ba = L.row_a + ul * 208, bb = L.row_b + ul * 208;
     uint4 ta = lds128(ba + 192), tb = lds128(bb + 192);
     const uint32_t sca[4] = {ta.x ^ 0x80808080u, ta.y ^ 0x80808080u, ta.z ^ 0x80808080u, ta.w ^ 0x80808080u};
@@ -359,7 +383,7 @@ __device__ __forceinline__ void unit_q6k(const Lane &L, int ul, int ncols, int d
         for (int i = 0; i < 4; i++) part[nt][i] = 0.0f;
     uint32_t xb[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + ul * ncols * PANEL_BYTES + 8 * L.c;
+    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 8 * L.c;
 
 #pragma unroll
     for (int hf = 0; hf < 2; hf++)
@@ -430,35 +454,45 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
     constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NT * 4 * 32 : 0;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);          // full[MAX_STAGES], empty[MAX_STAGES]
-    float *red = reinterpret_cast<float *>(smem + 128);
-    uint8_t *stages = smem + 128 + ((RED_FLOATS * 4 + 127) & ~127);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);   // full[MAX_STAGES], empty[MAX_STAGES], panels
+    float *red = reinterpret_cast<float *>(smem + 256);
+    uint8_t *xres = smem + 256 + ((RED_FLOATS * 4 + 127) & ~127);
+    uint8_t *stages = xres + a.xres_bytes;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = a.stages;
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES), xbar = smem_u32(bars + 2 * MAX_STAGES);
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, NW);
         }
+        mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     const int n_chunks = (a.units + a.kc - 1) / a.kc;
     const uint32_t stage0 = smem_u32(stages);
+    int tn = 0;   // trace slots used by this warp
 
     if (warp == NW) {
         // ------------------------------ producer ------------------------------
         uint32_t it = 0;
+        if (a.x_resident && lane == 0 && (int)blockIdx.x < a.n_tiles) {
+            // the launch's panels are one contiguous run: [units][ncols][PANEL_BYTES]
+            mbar_expect_tx(xbar, a.xres_bytes);
+            bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);
+        }
         for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
             const size_t row0 = (size_t)tile * R;
             const int nrows = (int)min((size_t)R, a.w.rows - row0);
             for (int ch = 0; ch < n_chunks; ch++, it++) {
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
+                trace(a, tn, 1, it);
                 mbar_wait(empty0 + 8 * s, ph ^ 1, a.status, 0x1u);
+                trace(a, tn, 2, it);
                 const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
                 const uint32_t qbytes = UNIT_Q * kcc;
                 uint32_t sbytes = 0;
@@ -469,19 +503,32 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                     size_t s_end = min((size_t)pad8(u0 + kcc), a.w.srow);
                     sbytes = (uint32_t)(s_end - s_first) * 2;
                 }
-                const uint32_t xbytes = (uint32_t)a.ncols * PANEL_BYTES;
+                const uint32_t xbytes = a.x_resident ? 0u : (uint32_t)a.ncols * PANEL_BYTES;
                 const uint32_t bar = full0 + 8 * s;
-                if (lane == 0) mbar_expect_tx(bar, nrows * (qbytes + sbytes) + kcc * xbytes);
+                if (a.whole_rows) {
+                    if (lane == 0)
+                        mbar_expect_tx(bar, nrows * (uint32_t)(a.w.qpitch + (FMT != Q4_K ? a.w.srow * 2 : 0)) + kcc * xbytes);
+                } else if (lane == 0) {
+                    mbar_expect_tx(bar, nrows * (qbytes + sbytes) + kcc * xbytes);
+                }
                 __syncwarp();
                 const uint32_t st = stage0 + s * a.stage_bytes;
-                for (int r = lane; r < nrows; r += 32) {
-                    bulk_g2s(st + r * a.q_stride, a.w.quants + (row0 + r) * a.w.qrow + (size_t)u0 * UNIT_Q, qbytes, bar);
-                    if (FMT != Q4_K)
-                        bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
+                if (a.whole_rows) {
+                    // consecutive rows are one contiguous run (rows sit qpitch apart, and so do the stage's)
+                    if (lane == 0) bulk_g2s(st, a.w.quants + row0 * a.w.qpitch, nrows * (uint32_t)a.w.qpitch, bar);
+                    if (FMT != Q4_K && lane == 1)
+                        bulk_g2s(st + a.s_off, a.w.scales + row0 * a.w.srow, nrows * (uint32_t)a.w.srow * 2, bar);
+                } else {
+                    for (int r = lane; r < nrows; r += 32) {
+                        bulk_g2s(st + r * a.q_stride, a.w.quants + (row0 + r) * a.w.qpitch + (size_t)u0 * UNIT_Q, qbytes, bar);
+                        if (FMT != Q4_K)
+                            bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
+                    }
                 }
-                for (int u = lane; u < kcc; u += 32)
+                for (int u = lane; u < kcc && !a.x_resident; u += 32)
                     bulk_g2s(st + a.x_off + u * xbytes,
                              a.panels + ((size_t)(u0 + u) * a.ncols_total + a.col0) * PANEL_BYTES, xbytes, bar);
+                trace(a, tn, 3, it);
             }
         }
         // Drain: the copies this warp issued must have landed before the CTA's
@@ -511,6 +558,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 
     uint32_t it = 0;
     int tile_parity = 0;
+    if (a.x_resident && (int)blockIdx.x < a.n_tiles) mbar_wait(xbar, 0, a.status, 0x4u);
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, tile_parity ^= 1) {
         float acc[NT][4];
 #pragma unroll
@@ -521,7 +569,9 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         for (int ch = 0; ch < n_chunks; ch++, it++) {
             const int s = it % S;
             const uint32_t ph = (it / S) & 1;
+            trace(a, tn, 4, it);
             mbar_wait(full0 + 8 * s, ph, a.status, 0x2u);
+            trace(a, tn, 5, it);
             const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
             const uint32_t st = stage0 + s * a.stage_bytes;
             L.row_a = st + (rt * 16 + L.g) * a.q_stride;
@@ -529,14 +579,19 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
             L.srow_a = st + a.s_off + (rt * 16 + L.g) * a.s_stride;
             L.srow_b = L.srow_a + 8 * a.s_stride;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) L.x[nt] = st + a.x_off + (nt * 8 + L.g) * PANEL_BYTES;
-            for (int ul = ks; ul < kcc; ul += KS) {
-                if (FMT == Q4_K) unit_q4k<NT>(L, ul, a.ncols, xo, acc);
-                else if (FMT == Q8_0) unit_q8_0<NT>(L, ul, a.ncols, acc);
-                else unit_q6k<NT>(L, ul, a.ncols, (u0 & 7) + ul, acc);
+            for (int nt = 0; nt < NT; nt++)
+                L.x[nt] = (a.x_resident ? smem_u32(xres) : st + a.x_off) + (nt * 8 + L.g) * PANEL_BYTES;
+            const int xu0 = a.x_resident ? u0 : 0;
+            // units are dealt to the K-split warps round-robin over the whole row,
+            // so every warp gets the same number whatever the chunking
+            for (int ul = (ks + KS - u0 % KS) % KS; ul < kcc; ul += KS) {
+                if (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
+                else if (FMT == Q8_0) unit_q8_0<NT>(L, ul, xu0 + ul, a.ncols, acc);
+                else unit_q6k<NT>(L, ul, xu0 + ul, a.ncols, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
+            trace(a, tn, 6, it);
         }
 
         // ---- sum the K-split warps of this row tile, in warp order ----
@@ -559,6 +614,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                 }
         }
 
+        trace(a, tn, 7, it);
         // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
         const size_t r0 = (size_t)tile * R + rt * 16 + L.g, r1 = r0 + 8;
 #pragma unroll
@@ -583,46 +639,127 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 // ---------------------------------------------------------------------------
 int gemv_max_tokens(int split) { return split ? 8 : 16; }
 
+// DWIM_B200_GEMV_TUNE="rt,ks,kc,stages" overrides the launch shape (0 = keep
+// the default), for sweeps on the device.  Read once.
+struct Tune { int rt = 0, ks = 0, kc = 0, stages = 0; };
+static const Tune &tune() {
+    static Tune t = [] {
+        Tune v;
+        if (const char *e = getenv("DWIM_B200_GEMV_TUNE")) sscanf(e, "%d,%d,%d,%d", &v.rt, &v.ks, &v.kc, &v.stages);
+        return v;
+    }();
+    return t;
+}
+
 template <int FMT, int NT, int RT, int KS>
 static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
     constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NT * 4 * 32 * 4 + 127) & ~127) : 0;
-    // K per stage: a multiple of KS units, about 1024 weights per warp-visit
-    a.kc = KS * (FMT == Q8_0 ? 1 : 1);
-    if (a.kc > a.units) a.kc = a.units;
-    int qs = UNIT_Q * a.kc;
-    if ((qs / 16) % 2 == 0) qs += 16;   // an odd number of 16-byte steps between rows: no bank conflicts
-    a.q_stride = qs;
-    a.s_off = R * qs;
-    a.s_stride = FMT == Q8_0 ? 16 * a.kc + 16 : FMT == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
-    a.x_off = a.s_off + R * a.s_stride;
-    a.stage_bytes = (a.x_off + a.kc * a.ncols * PANEL_BYTES + 127) & ~127;
+    constexpr int SMEM_MAX = 227 * 1024;
+    const int fixed = 256 + RED_BYTES;
+    // Panels stay resident when the launch covers the whole panel array (one
+    // contiguous run) and it is small next to the ring.
+    const int xall = a.units * a.ncols * PANEL_BYTES;
+    a.x_resident = a.col0 == 0 && a.ncols == a.ncols_total && xall <= 80 * 1024;
+    a.xres_bytes = a.x_resident ? xall : 0;
+    // K per stage.  Whole rows when two stages of them fit: the tile is then one
+    // contiguous run of HBM and moves with a single bulk copy (issuing a bulk
+    // copy costs the producer on the order of a hundred cycles, so a stage
+    // made of one copy per row starves the consumers).  Longer rows are cut in
+    // even chunks, one copy per row and chunk.
+    const int budget = SMEM_MAX - fixed - a.xres_bytes;
+    const int srow_bytes = (int)a.w.srow * 2;
+    auto whole_stage = [&]() {
+        return (int)((R * (a.w.qpitch + srow_bytes) + (a.x_resident ? 0 : a.units * a.ncols * PANEL_BYTES) + 127) & ~127);
+    };
+    a.whole_rows = tune().kc <= 0 && 2 * whole_stage() <= budget;
+    if (a.whole_rows) {
+        a.kc = a.units;
+        a.q_stride = (int)a.w.qpitch;
+        a.s_off = R * a.q_stride;
+        a.s_stride = srow_bytes;
+        a.x_off = a.s_off + R * a.s_stride;
+        a.stage_bytes = whole_stage();
+        a.stages = budget / a.stage_bytes;
+    } else {
+        int chunks = 2;
+        for (;; chunks++) {
+            a.kc = (a.units + chunks - 1) / chunks;
+            if (tune().kc > 0) a.kc = tune().kc < a.units ? tune().kc : a.units;
+            int qs = UNIT_Q * a.kc;
+            if ((qs / 16) % 2 == 0) qs += 16;   // an odd number of 16-byte steps between rows: no bank conflicts
+            a.q_stride = qs;
+            a.s_off = R * qs;
+            a.s_stride = FMT == Q8_0 ? 16 * a.kc + 16 : FMT == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
+            a.x_off = a.s_off + R * a.s_stride;
+            a.stage_bytes = (a.x_off + (a.x_resident ? 0 : a.kc * a.ncols * PANEL_BYTES) + 127) & ~127;
+            a.stages = budget / a.stage_bytes;
+            if (a.stages >= 2 || a.kc == 1 || tune().kc > 0) break;
+        }
+    }
+    if (a.stages > MAX_STAGES) a.stages = MAX_STAGES;
+    if (tune().stages > 0 && tune().stages < a.stages) a.stages = tune().stages;
+    if (a.stages < 2) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: a stage of %d bytes does not fit", a.stage_bytes);
     a.n_tiles = (int)((a.w.rows + R - 1) / R);
-    const int fixed = 128 + RED_BYTES;
-    int stages = (227 * 1024 - fixed) / a.stage_bytes;
-    if (stages > MAX_STAGES) stages = MAX_STAGES;
-    if (stages < 2) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: a stage of %d bytes does not fit", a.stage_bytes);
-    a.stages = stages;
-    const int smem = fixed + stages * a.stage_bytes;
+    const int smem = fixed + a.xres_bytes + a.stages * a.stage_bytes;
     auto kern = gemv_kernel<FMT, NT, RT, KS>;
     static bool configured[64] = {false};   // per instantiation, per device
     if (!configured[ctx->device & 63]) {
-        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX));
         configured[ctx->device & 63] = true;
     }
     int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
-    kern<<<grid, (RT * KS + 1) * 32, smem, ctx->stream>>>(a);
+    static unsigned long long *tbuf = nullptr;
+    static int traced = 0;
+    const bool tracing = getenv("DWIM_B200_GEMV_TRACE") != nullptr;
+    const int nwarps = RT * KS + 1;
+    if (tracing) {
+        if (!tbuf) cudaMallocManaged(&tbuf, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
+        cudaStreamSynchronize(ctx->stream);
+        memset(tbuf, 0, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
+        a.trace = tbuf;
+    }
+    kern<<<grid, nwarps * 32, smem, ctx->stream>>>(a);
     DWIM_LAUNCHED(ctx);
+    if (tracing) {
+        cudaStreamSynchronize(ctx->stream);
+        if (++traced == atoi(getenv("DWIM_B200_GEMV_TRACE"))) {
+            unsigned long long t0 = ~0ull;
+            for (int i = 0; i < nwarps * TRACE_SLOTS; i++)
+                if (tbuf[2 * i + 1] && tbuf[2 * i] < t0) t0 = tbuf[2 * i];
+            fprintf(stderr, "TRACE rt=%d ks=%d stages=%d kc=%d whole=%d stage_bytes=%d tiles=%d grid=%d xres=%d\n", RT, KS, a.stages,
+                    a.kc, a.whole_rows, a.stage_bytes, a.n_tiles, grid, a.xres_bytes);
+            for (int w = 0; w < nwarps; w++)
+                for (int i = 0; i < TRACE_SLOTS; i++) {
+                    unsigned long long v = tbuf[2 * (w * TRACE_SLOTS + i) + 1];
+                    if (v) fprintf(stderr, "TRACE %llu tag=%llu warp=%d it=%llu\n", tbuf[2 * (w * TRACE_SLOTS + i)] - t0, v >> 32, w, v & 0xffffffffull);
+                }
+        }
+    }
     return 0;
 }
 
 template <int FMT, int NT>
 static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
-    // Many rows: 32-row tiles, four K-split warps each; few rows: 16-row tiles
-    // and eight K-split warps, so that every SM still gets tiles.
+    // Row tiles per CTA (RT) x K-split warps per row tile (KS).  KS should
+    // divide the row's units so that every warp gets the same share.
+    // Measured on B200 at the model's shapes: Q4_K runs best with 32-row tiles
+    // when there are rows enough for two tiles per SM, the wider formats with
+    // 16-row tiles (their stages are larger); eight K-split warps throughout.
     const size_t tiles32 = (a.w.rows + 31) / 32;
-    if (tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 4>(ctx, a);
+    int rt = FMT == Q4_K && tiles32 >= (size_t)2 * ctx->sm_count ? 2 : 1;
+    int ks = 8;
+    if (tune().rt > 0) rt = tune().rt;
+    if (tune().ks > 0) ks = tune().ks;
+    if (NT == 2 && rt == 2 && ks >= 8) ks /= 2;   // 17+ warps of the two-group kernel would spill registers
+    if (rt == 2 && ks == 10) return launch<FMT, NT, 2, 10>(ctx, a);
+    if (rt == 2 && ks == 8) return launch<FMT, NT, 2, 8>(ctx, a);
+    if (rt == 2 && ks == 5) return launch<FMT, NT, 2, 5>(ctx, a);
+    if (rt == 2 && ks == 4) return launch<FMT, NT, 2, 4>(ctx, a);
+    if (rt == 1 && ks == 10) return launch<FMT, NT, 1, 10>(ctx, a);
+    if (rt == 1 && ks == 5) return launch<FMT, NT, 1, 5>(ctx, a);
+    if (rt == 1 && ks == 4) return launch<FMT, NT, 1, 4>(ctx, a);
     return launch<FMT, NT, 1, 8>(ctx, a);
 }
 

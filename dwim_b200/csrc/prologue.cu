@@ -96,8 +96,8 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
 __global__ void f16_rows_kernel(const float4 *__restrict__ x, size_t n4, uint2 *__restrict__ out) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         float4 v = x[i];
-        uint32_t a = to_f16_bits(v.x) | ((uint32_t)to_f16_bits(v.y) << 16);
-        uint32_t b = to_f16_bits(v.z) | ((uint32_t)to_f16_bits(v.w) << 16);
+        uint32_t a = to_f16_bits(v.x) | (to_f16_bits(v.y) << 16);
+        uint32_t b = to_f16_bits(v.z) | (to_f16_bits(v.w) << 16);
         out[i] = make_uint2(a, b);
     }
 }

@@ -455,7 +455,7 @@ ORC_API void orc_quantize_q4_k(const float *x, size_t cols, uint8_t *row) {
         for (int j = 0; j < 8; j++) {
             float mn = 0.0f, mx = 0.0f;
             for (int i = 0; i < 32; i++) { mn = fminf(mn, xb[j * 32 + i]); mx = fmaxf(mx, xb[j * 32 + i]); }
-            low[j] = -mn;                                  /* >= 0 */
+            low[j] = 0.0f - mn;                            /* >= 0, and +0 (not -0) when mn is 0 */
             step[j] = (mx - mn) * (1.0f / 15.0f);
             top_step = fmaxf(top_step, step[j]);
             top_low = fmaxf(top_low, low[j]);
