@@ -23,6 +23,7 @@ static constexpr size_t SMALL_M_MAX = 16;
 namespace dwim {
 // gemm.cu
 bool gemm_available();
+bool gemm_supports(const WeightView &w);
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *x16, size_t n, float *out, const float *aux,
                int epilogue);
 void gemm_release(dwim_b200_ctx *ctx);
@@ -413,7 +414,9 @@ static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b2
             out_len, n, v.rows);
     if (n == 0 || v.rows == 0) return 0;
     REQUIRE(ctx, out != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
-    if (n > SMALL_M_MAX && gemm_available()) {
+    // f32 activations would lose 2^-12 per value going to one f16 operand; they
+    // stay on the exact small-M path until the GEMM carries them as hi/lo pairs.
+    if (n > SMALL_M_MAX && x->bf16_exact && gemm_available() && gemm_supports(v)) {
         int rc = ensure_shadow(ctx, x, SHADOW_F16_ROWS, v.cols, 0);
         if (rc) return rc;
         return gemm_large(ctx, v, (const __half *)x->shadow, n, out, aux, epilogue);
