@@ -24,8 +24,8 @@ namespace dwim {
 // gemm.cu
 bool gemm_available();
 bool gemm_supports(const WeightView &w);
-int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *x16, size_t n, float *out, const float *aux,
-               int epilogue);
+int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+               const float *aux, int epilogue);
 void gemm_release(dwim_b200_ctx *ctx);
 }  // namespace dwim
 
@@ -384,7 +384,7 @@ int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, co
 static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size_t cols, int split) {
     if (x->shadow_kind == kind && x->shadow_cols == cols && x->shadow_split == split) return 0;
     size_t n = x->len / cols;
-    size_t need = kind == SHADOW_F16_ROWS ? x->len * sizeof(__half) : panel_bytes(cols, (int)n * (split ? 2 : 1));
+    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n * (split ? 2 : 1)) : panel_bytes(cols, (int)n * (split ? 2 : 1));
     if (need > x->shadow_cap) {
         if (x->shadow) {
             DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -396,7 +396,7 @@ static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size
         x->shadow_cap = need;
     }
     x->shadow_kind = SHADOW_NONE;
-    int rc = kind == SHADOW_F16_ROWS ? build_f16_rows(ctx, x->data, n, cols, (__half *)x->shadow)
+    int rc = kind == SHADOW_GEMM ? build_gemm_operand(ctx, x->data, n, cols, split, (__half *)x->shadow)
                                      : build_panels(ctx, x->data, n, cols, kind, split, (__half *)x->shadow);
     if (rc) return rc;
     x->shadow_kind = kind;
@@ -414,12 +414,13 @@ static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b2
             out_len, n, v.rows);
     if (n == 0 || v.rows == 0) return 0;
     REQUIRE(ctx, out != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
-    // f32 activations would lose 2^-12 per value going to one f16 operand; they
-    // stay on the exact small-M path until the GEMM carries them as hi/lo pairs.
-    if (n > SMALL_M_MAX && x->bf16_exact && gemm_available() && gemm_supports(v)) {
-        int rc = ensure_shadow(ctx, x, SHADOW_F16_ROWS, v.cols, 0);
+    // bf16 activations are exact in one f16 column; f32 ones travel as two
+    // (value and rounding remainder), summed again in the epilogue.
+    if (n > SMALL_M_MAX && gemm_available() && gemm_supports(v)) {
+        int split = x->bf16_exact ? 0 : 1;
+        int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
         if (rc) return rc;
-        return gemm_large(ctx, v, (const __half *)x->shadow, n, out, aux, epilogue);
+        return gemm_large(ctx, v, (const __half *)x->shadow, n, split, out, aux, epilogue);
     }
     // bf16 activations are exact in one f16 column; f32 ones travel as two.
     int split = x->bf16_exact ? 0 : 1;

@@ -16,7 +16,7 @@ enum ShadowKind : int {
     SHADOW_NONE = 0,
     SHADOW_PANEL_NATURAL,   // small-M panels, k in order            (Q8_0, Q6_K)
     SHADOW_PANEL_Q4K,       // small-M panels, k permuted + swizzled (Q4_K)
-    SHADOW_F16_ROWS         // [n][cols] f16, for the tensor-core GEMM
+    SHADOW_GEMM             // f16 rows + sub-block means, for the tensor-core GEMM
 };
 
 struct dwim_b200_buffer {
@@ -93,7 +93,8 @@ int quantize_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const
 constexpr int PANEL_STRIDE = 272;
 size_t panel_bytes(size_t cols, int ncols);
 int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels);
-int build_f16_rows(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, __half *out);
+size_t gemm_operand_bytes(size_t cols, size_t ncols);
+int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out);
 
 // gemv.cu
 enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };

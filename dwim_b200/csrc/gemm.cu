@@ -1,28 +1,37 @@
-// The large-M product (prefill, long verify batches): a dense contraction on
-// the 5th-generation tensor cores.  Replaces the reference's matmul_tile64_*
-// kernels (matmul_tile.cu:94-258; host side gpu/cuda/mod.rs:402-442).
+// The large-M product (prefill, long verify batches) for Q4_K: a dense
+// contraction on the 5th-generation tensor cores whose products are exact.
+// Replaces the reference's matmul_tile64_* kernels (matmul_tile.cu:94-258;
+// host side gpu/cuda/mod.rs:402-442).
 //
-// out[t][r] = sum_k W[r][k] * X[t][k].  A CTA owns a tile of 128 weight rows
-// (the MMA's M side, one TMEM lane per row) by BN tokens (the N side, one TMEM
-// column per token) and walks K in blocks of 64:
+// out[t][r] = sum_k W[r][k] x[t][k], with W[r][k] = d*(sc_j*q) - dmin*m_j
+// (d, dmin per 256-weight unit and row; sc_j, m_j per 32-weight sub-block).
+// The integer sc_j*q <= 945 is exact in f16, so for every unit u of K
+//     S1_u[r][t] = sum_k (sc*q)[r][k] * x[t][k]          16 MMAs of K=16
+//     S2_u[r][t] = sum_j m_j[r] * mean_j(x[t])            1 MMA of K=16
+// are sums of exact products in the tensor cores' fp32 accumulators, and
+//     out[r][t] = sum_u  d_u[r]*S1_u - 32*dmin_u[r]*S2_u
+// is applied by CUDA cores in fp32.  (The reference's tile kernel rounds every
+// dequantized weight to f16 instead, matmul_tile.cu:66-74: 2e-4 of rms error.)
+// An f32 activation travels as two f16 columns, value and rounding remainder,
+// which the epilogue adds up again; a bf16 one is exact in one column.
 //
-//   warp 0       TMA producer.  Per 256 weights of K one tiled tensor copy
-//                brings the tile's packed blocks ([128 rows][144 B] for Q4_K)
-//                into a raw ring; per K block one tensor copy brings the
-//                activations' f16 tile ([BN][64], 128-byte swizzle).
-//   warps 6-13   dequantizers.  Thread (row, half) decodes 32 weights of its
-//                row from the raw ring in fp32 — fma(d*sc, q, -dmin*m), the
-//                reference's order — rounds once to f16 (as the reference's
-//                tile kernel does, matmul_tile.cu:66-74) and stores them into
-//                the stage's A tile in the canonical K-major 128-byte-swizzled
-//                layout the MMA's shared-memory descriptor expects.
-//   warp 1       MMA issuer: one thread issues four tcgen05.mma (M=128, N=BN,
-//                K=16, f16 x f16 -> f32 in TMEM) per K block and commits the
-//                stage back to the producers.
-//   warps 2-5    epilogue: tcgen05.ld the accumulators (32 lanes x 32 columns
-//                per warp and instruction), apply the operator's mode
-//                (store / add / SwiGLU) and write out[t][r], coalesced over r.
-//
+// A CTA owns 128 weight rows (one TMEM lane each) by BN columns:
+//   warp 0        TMA producer: per unit the tile's packed blocks
+//                 ([128 rows][144 B]) into a raw ring and the means operand;
+//                 per 64 of K the activations' f16 tile ([BN][64], 128-byte
+//                 swizzle).
+//   warp 1        MMA issuer (one thread): tcgen05.mma M=128 N=BN K=16 into
+//                 S1 and S2 of the unit's accumulator buffer (two buffers, so
+//                 unit u+1 multiplies while unit u drains).
+//   warps 2-9     drain: tcgen05.ld S1 and S2, acc += d*S1 - 32*dmin*S2 in
+//                 registers (thread = weight row, 64 columns per warp at
+//                 BN=128); after the last unit the operator's epilogue
+//                 (store / add / SwiGLU) and the store, coalesced over rows.
+//   warps 10-17   dequantizers: thread (row, half) turns 32 nibbles into
+//                 sc*q halves (lop3 magic number + one HFMA2 per two weights)
+//                 and stores them into the stage's A tile in the K-major
+//                 128-byte-swizzled layout of the MMA's descriptor; once per
+//                 unit it writes the row's eight m_j and (d, 32*dmin).
 // Every mbarrier wait is bounded (ptx.cuh); a kernel that gave up says so in
 // the context's status word.
 #include <cuda.h>
@@ -36,12 +45,20 @@ namespace {
 
 constexpr int TILE_M = 128;   // weight rows per CTA
 constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of f16
+constexpr int KSTAGES = 4;    // = K blocks per unit: stage index == K block within the unit
 constexpr int RAW_STAGES = 3;
-constexpr int N_DEQ_WARPS = 8;
-constexpr int GEMM_THREADS = (6 + N_DEQ_WARPS) * 32;
+constexpr int MIN_STAGES = 2;
+constexpr int SCALE_SLOTS = 4;
+constexpr int N_DEQ_WARPS = 8, N_DRAIN_WARPS = 8;
+constexpr int GEMM_THREADS = (2 + N_DRAIN_WARPS + N_DEQ_WARPS) * 32;
+constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // 18 KB
+constexpr int A_BYTES = TILE_M * BK * 2;                           // 16 KB
+constexpr int AMIN_BYTES = TILE_M * 16 * 2;                        // 4 KB: [k half][row][16 B]
+constexpr int BAR_BYTES = 1024;
 
 struct GemmArgs {
-    size_t rows, n, units;   // weight rows, tokens, 256-weight units of K
+    size_t rows, n, ncols, units;   // weight rows, tokens, operand columns, 256-weight units of K
+    int split;                      // 1: columns 2t, 2t+1 are token t's hi and lo halves
     float *out;
     const float *aux;
     int epi;
@@ -49,14 +66,15 @@ struct GemmArgs {
 };
 
 template <int BN> struct Cfg {
-    static constexpr int STAGES = BN >= 256 ? 3 : 4;
-    static constexpr int A_BYTES = TILE_M * BK * 2;            // 16 KB
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // Q4_K: 18 KB
-    static constexpr int BAR_BYTES = 1024;
-    static constexpr int SMEM = BAR_BYTES + STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + 1024;   // + alignment slack
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [k half][column][16 B]
+    static constexpr int MIN_BYTES = AMIN_BYTES + ((BMIN_BYTES + 1023) / 1024) * 1024;
+    static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 8;   // (d, 32*dmin) per row
+    static constexpr int SMEM = BAR_BYTES + KSTAGES * STAGE_BYTES + MIN_STAGES * MIN_BYTES + RAW_STAGES * RAW_BYTES +
+                                SCALE_BYTES + 1024;                // + alignment slack
+    static constexpr int TMEM_COLS = 4 * BN < 32 ? 32 : 4 * BN;    // S1 x2, S2 x2
+    static constexpr int DRAIN_COLS = BN / 2;                      // columns per drain warp
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -84,27 +102,29 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
-// (64 f16), 128-byte swizzled, eight-row groups 1024 bytes apart:
-//   [0,14) address >> 4   [16,30) leading offset >> 4 (unused for swizzled
-//   K-major: 1)   [32,46) stride between eight-row groups >> 4 (64)
-//   [46,48) descriptor version 1   [61,64) layout 2 = 128-byte swizzle
+// Shared-memory matrix descriptors (K-major operands).
+//   [0,14) address >> 4   [16,30) leading byte offset >> 4   [32,46) stride
+//   byte offset >> 4   [46,48) version 1   [61,64) layout
+// 128-byte swizzle: rows are 128 bytes (64 f16), eight-row groups 1024 bytes
+// apart (stride offset); the leading offset is not used.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// No swizzle: 8 rows x 16 bytes are contiguous (128 bytes); eight-row groups
+// 128 bytes apart (stride offset); the second 8 of K `lbo` bytes further on.
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3ffffu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | (8ull << 32) | (1ull << 46);
 }
 // Instruction descriptor: f32 accumulate (bits 4-5 = 1), f16 A and B (0),
 // both K-major (0), N >> 3 at bit 17, M >> 4 at bit 24.
@@ -115,73 +135,90 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n) {
 __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
-__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
-    uint32_t r;   // cvt packs its first source into the upper half
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
+__device__ __forceinline__ void sts64f(uint32_t a, float x, float y) {
+    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(x), "f"(y) : "memory");
 }
-
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-// ---- Q4_K dequantizer: 32 weights of one row ---------------------------------------
-// Thread (row, h) of K block `g` (0..3 inside the 256-weight unit) decodes
-// sub-block 2g + h: nibble h of the 32 bytes of group g.
-__device__ __forceinline__ void dequant_q4k_32(uint32_t raw_row, int g, int h, uint32_t a_row, int row7) {
-    const uint4 hdr = lds128(raw_row);
+constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_M64 = 0xD400D400u, H2_SIXTEENTH = 0x2C002C00u;
+
+// ---- dequantizer: 32 weights of one row as exact sc*q halves ----------------------------
+// Thread (row, h) of K block g (0..3 inside the unit) owns sub-block 2g + h:
+// nibble h of the 32 bytes of group g.  A word's bytes come out in the order
+// (0, 2, 1, 3); the activations are stored in the same order.
+__device__ __forceinline__ void dequant_q4k_32(const uint4 &hdr, uint32_t raw_row, int g, int h, uint32_t a_row, int row7) {
     const uint4 q0 = lds128(raw_row + 16 + 32 * g), q1 = lds128(raw_row + 32 + 32 * g);
-    // the 6-bit scale and minimum of sub-blocks 2g, 2g+1 as two bytes each (see gemv.cu: q4k_scales)
     const int sh = (g & 1) * 16;
-    const uint32_t y = (hdr.y >> sh) & 0xffffu, z = (hdr.z >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
+    const uint32_t y = (hdr.y >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
     const uint32_t sc2 = g < 2 ? (y & 0x3f3fu) : ((w & 0x0f0fu) | ((y >> 2) & 0x3030u));
-    const uint32_t m2 = g < 2 ? (z & 0x3f3fu) : (((w >> 4) & 0x0f0fu) | ((z >> 2) & 0x3030u));
-    const float sc = (float)((sc2 >> (8 * h)) & 0xffu), m = (float)((m2 >> (8 * h)) & 0xffu);
-    const float ds = __fmul_rn(h2f_lo(hdr.x), sc), ndm = -__fmul_rn(h2f_hi(hdr.x), m);
+    const uint32_t sc = (sc2 >> (8 * h)) & 0xffu;
+    const uint32_t scp = hsub2(0x64006400u | sc | (sc << 16), H2_1024);   // half2(sc, sc)
+    // low nibbles: (1024 + q)*sc - 1024*sc; high nibbles: (1024 + 16q)*(sc/16) - 64*sc
+    const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu;
+    const uint32_t mul = h ? hmul2(scp, H2_SIXTEENTH) : scp;
+    const uint32_t add = hmul2(scp, h ? H2_M64 : H2_M1024);
     const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
     for (int c = 0; c < 4; c++) {   // 16-byte chunk c of this half: weights 8c .. 8c+7
-        uint32_t o[4];
-#pragma unroll
-        for (int p = 0; p < 2; p++) {
-            const uint32_t nib = (words[2 * c + p] >> (4 * h)) & 0x0f0f0f0fu;
-            // byte b of nib -> 8388608 + q as a float, then q, then ds*q - dm in one rounding
-            const float f0 = __uint_as_float(prmt(nib, 0x4B000000u, 0x7540u)) - 8388608.0f;
-            const float f1 = __uint_as_float(prmt(nib, 0x4B000000u, 0x7541u)) - 8388608.0f;
-            const float f2 = __uint_as_float(prmt(nib, 0x4B000000u, 0x7542u)) - 8388608.0f;
-            const float f3 = __uint_as_float(prmt(nib, 0x4B000000u, 0x7543u)) - 8388608.0f;
-            o[2 * p] = pack_f16x2(fmaf(ds, f0, ndm), fmaf(ds, f1, ndm));
-            o[2 * p + 1] = pack_f16x2(fmaf(ds, f2, ndm), fmaf(ds, f3, ndm));
-        }
-        sts128(a_row + (((4 * h + c) ^ row7) << 4), o[0], o[1], o[2], o[3]);
+        const uint32_t w0 = words[2 * c], w1 = words[2 * c + 1];
+        const uint32_t o0 = hfma2(lop3_and_or(w0, mask, H2_1024), mul, add);        // bytes 0, 2
+        const uint32_t o1 = hfma2(lop3_and_or(w0 >> 8, mask, H2_1024), mul, add);   // bytes 1, 3
+        const uint32_t o2 = hfma2(lop3_and_or(w1, mask, H2_1024), mul, add);
+        const uint32_t o3 = hfma2(lop3_and_or(w1 >> 8, mask, H2_1024), mul, add);
+        sts128(a_row + (((4 * h + c) ^ row7) << 4), o0, o1, o2, o3);
     }
+}
+
+// The row's eight 6-bit minimums as eight halves (16 bytes).
+__device__ __forceinline__ void mins_q4k(const uint4 &hdr, uint32_t (&o)[4]) {
+    const uint32_t lo4 = hdr.z & 0x3f3f3f3fu;                                          // m_0..m_3
+    const uint32_t hi4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);  // m_4..m_7
+    o[0] = hsub2(prmt(lo4, 0x64646464u, 0x5140u), H2_1024);
+    o[1] = hsub2(prmt(lo4, 0x64646464u, 0x5342u), H2_1024);
+    o[2] = hsub2(prmt(hi4, 0x64646464u, 0x5140u), H2_1024);
+    o[3] = hsub2(prmt(hi4, 0x64646464u, 0x5342u), H2_1024);
 }
 
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                const __grid_constant__ CUtensorMap tmap_m, const GemmArgs a) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment for the swizzled tiles
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base;                       // 8-byte barriers
-    const uint32_t full0 = bars, empty0 = bars + 64, rawfull0 = bars + 128, rawempty0 = bars + 192, accbar = bars + 256;
-    const uint32_t tmem_slot = bars + 320;
-    const uint32_t stage0 = base + C::BAR_BYTES;
-    const uint32_t raw0 = stage0 + C::STAGES * C::STAGE_BYTES;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzled tiles want 1024-byte alignment
+    // barriers, 8 bytes each
+    const uint32_t full0 = base, empty0 = base + 32, minfull0 = base + 64, minempty0 = base + 80;
+    const uint32_t rawfull0 = base + 96, rawempty0 = base + 128, accfull0 = base + 160, accempty0 = base + 176;
+    const uint32_t tmem_slot = base + 192;
+    const uint32_t stage0 = base + BAR_BYTES;
+    const uint32_t min0 = stage0 + KSTAGES * C::STAGE_BYTES;
+    const uint32_t raw0 = min0 + MIN_STAGES * C::MIN_BYTES;
+    const uint32_t scale0 = raw0 + RAW_STAGES * RAW_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * TILE_M, tok0 = blockIdx.y * BN;
-    const int n_kb = (int)a.units * 4;
+    const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
+    const int units = (int)a.units;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) {
+        for (int s = 0; s < KSTAGES; s++) {
             mbar_init(full0 + 8 * s, 1 + N_DEQ_WARPS);   // the producer's expect_tx arrival + one per dequant warp
             mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
+        }
+        for (int s = 0; s < MIN_STAGES; s++) {
+            mbar_init(minfull0 + 8 * s, 1 + N_DEQ_WARPS);
+            mbar_init(minempty0 + 8 * s, 1);
+            mbar_init(accfull0 + 8 * s, 1);
+            mbar_init(accempty0 + 8 * s, N_DRAIN_WARPS);
         }
         for (int s = 0; s < RAW_STAGES; s++) {
             mbar_init(rawfull0 + 8 * s, 1);
             mbar_init(rawempty0 + 8 * s, N_DEQ_WARPS);
         }
-        mbar_init(accbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -196,71 +233,135 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            for (int kb = 0; kb < n_kb; kb++) {
-                if ((kb & 3) == 0) {
-                    const int u = kb >> 2, rs = u % RAW_STAGES;
-                    mbar_wait(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
-                    mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
-                    tma_load_2d(raw0 + rs * C::RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
+            for (int u = 0; u < units; u++) {
+                const int rs = u % RAW_STAGES, ms = u & 1;
+                const uint32_t par = (u & 1) ^ 1;   // K stage g is used once per unit
+                mbar_wait(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
+                mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
+                tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
+                for (int g = 0; g < 4; g++) {
+                    mbar_wait(empty0 + 8 * g, par, a.status, 0x20u);
+                    mbar_expect_tx(full0 + 8 * g, C::B_BYTES);
+                    tma_load_2d(stage0 + g * C::STAGE_BYTES + A_BYTES, &tmap_x, (4 * u + g) * BK, col0, full0 + 8 * g);
                 }
-                const int s = kb % C::STAGES;
-                mbar_wait(empty0 + 8 * s, ((kb / C::STAGES) & 1) ^ 1, a.status, 0x20u);
-                mbar_expect_tx(full0 + 8 * s, C::B_BYTES);
-                tma_load_2d(stage0 + s * C::STAGE_BYTES + C::A_BYTES, &tmap_x, kb * BK, tok0, full0 + 8 * s);
+                mbar_wait(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);
+                mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
+                const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
+                tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // hi parts: K 0..7
+                tma_load_2d(bm + BN * 16, &tmap_m, u * 16 + 8, col0, minfull0 + 8 * ms);   // lo parts: K 8..15
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
-        for (int kb = 0; kb < n_kb; kb++) {
-            const int s = kb % C::STAGES;
-            mbar_wait(full0 + 8 * s, (kb / C::STAGES) & 1, a.status, 0x40u);
+        for (int u = 0; u < units; u++) {
+            const int ab = u & 1;
+            const uint32_t s1 = tmem_base + ab * BN, s2 = tmem_base + 2 * BN + ab * BN;
+            mbar_wait(accempty0 + 8 * ab, ((u >> 1) & 1) ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
+            tc_fence_after();
+            for (int g = 0; g < 4; g++) {
+                mbar_wait(full0 + 8 * g, u & 1, a.status, 0x100u);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_addr = stage0 + g * C::STAGE_BYTES;
+                    const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)   // 32 bytes further along the swizzled row per K=16
+                        umma_f16(s1, ad + 2 * k, bd + 2 * k, idesc, (g | k) != 0);
+                    umma_commit(empty0 + 8 * g);        // the stage may be refilled once these finish
+                }
+                __syncwarp();
+            }
+            mbar_wait(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x200u);
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t a_addr = stage0 + s * C::STAGE_BYTES, b_addr = a_addr + C::A_BYTES;
-                const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(b_addr);
-#pragma unroll
-                for (int k = 0; k < BK / 16; k++)   // 32 bytes further along the swizzled row per K=16
-                    umma_f16(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (kb | k) != 0);
-                umma_commit(empty0 + 8 * s);                  // the stage may be refilled once these finish
-                if (kb == n_kb - 1) umma_commit(accbar);      // and the accumulators are complete
+                const uint32_t am = min0 + ab * C::MIN_BYTES;
+                umma_f16(s2, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(am + AMIN_BYTES, BN * 16), idesc, 0);
+                umma_commit(minempty0 + 8 * ab);
+                umma_commit(accfull0 + 8 * ab);         // both sums of the unit are complete
             }
             __syncwarp();
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 2 + N_DRAIN_WARPS) {
         // ------------------------------ dequantizers ------------------------------
-        const int dt = threadIdx.x - 6 * 32;      // 0..255
+        const int dt = threadIdx.x - (2 + N_DRAIN_WARPS) * 32;   // 0..255
         const int r = dt >> 1, h = dt & 1;
-        for (int kb = 0; kb < n_kb; kb++) {
-            const int u = kb >> 2, g = kb & 3, rs = u % RAW_STAGES, s = kb % C::STAGES;
-            if (g == 0) mbar_wait(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x80u);
-            mbar_wait(empty0 + 8 * s, ((kb / C::STAGES) & 1) ^ 1, a.status, 0x100u);
-            dequant_q4k_32(raw0 + rs * C::RAW_BYTES + r * 144, g, h, stage0 + s * C::STAGE_BYTES + r * 128, r & 7);
-            fence_async_smem();      // the tensor core reads shared memory through the async proxy
+        for (int u = 0; u < units; u++) {
+            const int rs = u % RAW_STAGES, ms = u & 1;
+            mbar_wait(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
+            const uint32_t raw_row = raw0 + rs * RAW_BYTES + r * 144;
+            const uint4 hdr = lds128(raw_row);
+            for (int g = 0; g < 4; g++) {
+                mbar_wait(empty0 + 8 * g, (u & 1) ^ 1, a.status, 0x800u);
+                dequant_q4k_32(hdr, raw_row, g, h, stage0 + g * C::STAGE_BYTES + r * 128, r & 7);
+                fence_async_smem();      // the tensor core reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * g);
+            }
+            mbar_wait(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);
+            uint32_t m8[4];
+            mins_q4k(hdr, m8);
+            // A' = [m_0..m_7 | m_0..m_7]: K half h of row r
+            sts128(min0 + ms * C::MIN_BYTES + h * (TILE_M * 16) + r * 16, m8[0], m8[1], m8[2], m8[3]);
+            if (h == 0) sts64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + r) * 8, h2f_lo(hdr.x), 32.0f * h2f_hi(hdr.x));
+            fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(full0 + 8 * s);
-                if (g == 3) mbar_arrive(rawempty0 + 8 * rs);
+                mbar_arrive(minfull0 + 8 * ms);
+                mbar_arrive(rawempty0 + 8 * rs);
             }
         }
     } else {
-        // ------------------------------ epilogue (warps 2-5) ------------------------------
-        const int quad = warp & 3;                 // the TMEM lanes this warp may read: 32*quad ..
-        const size_t row = (size_t)row0 + quad * 32 + lane;
-        mbar_wait(accbar, 0, a.status, 0x200u);
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; c++) {
-            uint32_t v[32];
-            tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c * 32, v);
-            tmem_ld_wait();
-            if (row < a.rows) {
+        // ------------------------------ drain + epilogue (warps 2-9) ------------------------------
+        const int quad = warp & 3;                      // the TMEM lanes this warp may read: 32*quad ..
+        const int chalf = (warp - 2) >> 2;              // which half of the tile's columns
+        const int rl = quad * 32 + lane;                // row within the tile = TMEM lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * C::DRAIN_COLS;
+        float acc[C::DRAIN_COLS];
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const size_t t = (size_t)tok0 + c * 32 + j;
+        for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] = 0.0f;
+        for (int u = 0; u < units; u++) {
+            const int ab = u & 1;
+            mbar_wait(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x2000u);    // the row scales are written
+            mbar_wait(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);    // the unit's sums are complete
+            tc_fence_after();
+            const float2 sc = lds64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 8);
+#pragma unroll
+            for (int c = 0; c < C::DRAIN_COLS / 16; c++) {
+                uint32_t v1[16], v2[16];
+                tmem_ld16(lane_addr + ab * BN + c * 16, v1);
+                tmem_ld16(lane_addr + 2 * BN + ab * BN + c * 16, v2);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j++)
+                    acc[c * 16 + j] += sc.x * __uint_as_float(v1[j]) - sc.y * __uint_as_float(v2[j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
+        }
+        const size_t row = (size_t)row0 + rl;
+        if (row < a.rows) {
+            const size_t cbase = (size_t)col0 + chalf * C::DRAIN_COLS;
+            if (a.split) {
+#pragma unroll
+                for (int j = 0; j < C::DRAIN_COLS; j += 2) {
+                    const size_t t = (cbase + j) >> 1;
                     if (t < a.n) {
                         const size_t i = t * a.rows + row;
-                        float x = __uint_as_float(v[j]);
+                        float x = acc[j] + acc[j + 1];
+                        if (a.epi == EPI_ADD) x += a.out[i];
+                        else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
+                        a.out[i] = x;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < C::DRAIN_COLS; j++) {
+                    const size_t t = cbase + j;
+                    if (t < a.n) {
+                        const size_t i = t * a.rows + row;
+                        float x = acc[j];
                         if (a.epi == EPI_ADD) x += a.out[i];
                         else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
                         a.out[i] = x;
@@ -291,37 +392,46 @@ EncodeTiled encode_fn() {
     return fn;
 }
 
-template <int BN>
-int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *x16, size_t n, float *out, const float *aux, int epi) {
-    using C = Cfg<BN>;
+int encode_2d(dwim_b200_ctx *ctx, CUtensorMap *map, CUtensorMapDataType type, const void *ptr, uint64_t inner, uint64_t outer,
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle, const char *what) {
     EncodeTiled enc = encode_fn();
     if (!enc) return fail(ctx, DWIM_B200_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    CUtensorMap tw, tx;
-    {   // packed weights as bytes: [rows][qpitch], box [128 rows][144 bytes]
-        cuuint64_t dims[2] = {w.qpitch, w.rows}, strides[1] = {w.qpitch};
-        cuuint32_t box[2] = {144, TILE_M}, es[2] = {1, 1};
-        CUresult r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w.quants, dims, strides, box, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(ctx, DWIM_B200_ECUDA, "encoding the weight tensor map failed (%d)", (int)r);
-    }
-    {   // activations as f16: [n][cols], box [BN tokens][64], 128-byte swizzle; rows past n read as zero
-        cuuint64_t dims[2] = {w.cols, n}, strides[1] = {w.cols * 2};
-        cuuint32_t box[2] = {BK, BN}, es[2] = {1, 1};
-        CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)x16, dims, strides, box, es,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return fail(ctx, DWIM_B200_ECUDA, "encoding the activation tensor map failed (%d)", (int)r);
-    }
-    GemmArgs a{w.rows, n, w.cols / 256, out, aux, epi, ctx->status};
+    cuuint64_t dims[2] = {inner, outer}, strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer}, es[2] = {1, 1};
+    CUresult r = enc(map, type, 2, const_cast<void *>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, DWIM_B200_ECUDA, "encoding the %s tensor map failed (%d)", what, (int)r);
+    return 0;
+}
+
+template <int BN>
+int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+                const float *aux, int epi) {
+    using C = Cfg<BN>;
+    const size_t ncols = n * (split ? 2 : 1), units = w.cols / 256;
+    CUtensorMap tw, tx, tm;
+    int rc;
+    // packed weights as bytes: [rows][qpitch], box [128 rows][144 bytes]; rows past the end read as zero blocks
+    if ((rc = encode_2d(ctx, &tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.quants, w.qpitch, w.rows, w.qpitch, 144, TILE_M,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, "weight")))
+        return rc;
+    // activations: [ncols][K] f16, box [BN][64], 128-byte swizzle; columns past the end read as zero
+    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, BN,
+                        CU_TENSOR_MAP_SWIZZLE_128B, "activation")))
+        return rc;
+    // sub-block means: [ncols][units*16] f16, box [BN][8]
+    if ((rc = encode_2d(ctx, &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand + ncols * w.cols, units * 16, ncols, units * 32, 8,
+                        BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
+        return rc;
+    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status};
     auto kern = gemm_q4k_kernel<BN>;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured[ctx->device & 63] = true;
     }
-    dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((n + BN - 1) / BN));
-    kern<<<grid, GEMM_THREADS, C::SMEM, ctx->stream>>>(tw, tx, a);
+    dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
+    kern<<<grid, GEMM_THREADS, C::SMEM, ctx->stream>>>(tw, tx, tm, a);
     DWIM_LAUNCHED(ctx);
     return 0;
 }
@@ -330,17 +440,17 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *x16, size
 
 bool gemm_available() { return true; }
 
-// Formats and shapes the tensor-core kernel takes; the rest goes through the
-// small-M kernel in groups of tokens.
+// Formats the tensor-core kernel takes; the rest goes through the small-M
+// kernel in groups of tokens.
 bool gemm_supports(const WeightView &w) { return w.fmt == Q4_K && w.cols % 256 == 0; }
 
-int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *x16, size_t n, float *out, const float *aux,
-               int epilogue) {
+int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+               const float *aux, int epilogue) {
     if (!gemm_supports(w)) return fail(ctx, DWIM_B200_EFORMAT, "the tensor-core GEMM does not take format %d", w.fmt);
-    if (n <= 32) return launch_gemm<32>(ctx, w, x16, n, out, aux, epilogue);
-    if (n <= 64) return launch_gemm<64>(ctx, w, x16, n, out, aux, epilogue);
-    if (n <= 128) return launch_gemm<128>(ctx, w, x16, n, out, aux, epilogue);
-    return launch_gemm<256>(ctx, w, x16, n, out, aux, epilogue);
+    const size_t ncols = n * (split ? 2 : 1);
+    if (ncols <= 32) return launch_gemm<32>(ctx, w, operand, n, split, out, aux, epilogue);
+    if (ncols <= 64) return launch_gemm<64>(ctx, w, operand, n, split, out, aux, epilogue);
+    return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
 }
 
 void gemm_release(dwim_b200_ctx *) {}

@@ -91,24 +91,56 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
     return 0;
 }
 
-// Plain f16 rows for the tensor-core GEMM: out[t][k] = f16(x[t][k]), clamped
-// to +-65504 as the reference's to_f16 kernel does (prelude.cu:121-132).
-__global__ void f16_rows_kernel(const float4 *__restrict__ x, size_t n4, uint2 *__restrict__ out) {
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        float4 v = x[i];
-        uint32_t a = to_f16_bits(v.x) | (to_f16_bits(v.y) << 16);
-        uint32_t b = to_f16_bits(v.z) | (to_f16_bits(v.w) << 16);
-        out[i] = make_uint2(a, b);
+// Operands of the tensor-core GEMM (Q4_K).  Two arrays, one row per column
+// (a column is a token, or with split = 1 a token's hi or lo half, columns 2t
+// and 2t+1):
+//   x16   [ncols][K] f16      the activations; each run of four k is stored in
+//                             the order (0, 2, 1, 3), the order the dequantizer
+//                             produces weights in (it unpacks bytes 0,2 and 1,3
+//                             of a word together)
+//   means [ncols][K/256][16]  per 32-weight sub-block the mean of the column's
+//                             f16 values, as a hi half (entries 0-7) and the
+//                             remainder (entries 8-15): the operand the
+//                             sub-block minimums are multiplied with
+size_t gemm_operand_bytes(size_t cols, size_t ncols) {
+    return ncols * cols * sizeof(__half) + ncols * (cols / 256) * 16 * sizeof(__half);
+}
+
+// grid (units, tokens), 256 threads.
+__global__ void __launch_bounds__(256) gemm_operand_kernel(const float *__restrict__ x, size_t cols, size_t units, int split,
+                                                           __half *__restrict__ x16, __half *__restrict__ means) {
+    const int u = blockIdx.x, t = blockIdx.y, k = threadIdx.x;
+    const float v = x[(size_t)t * cols + (size_t)u * 256 + k];
+    const __half hi = to_f16_clamped(v);
+    const __half lo = to_f16_clamped(v - __half2float(hi));
+    const int e = k & 3, pos = (k & ~3) | ((e & 1) << 1) | (e >> 1);
+    const size_t col = split ? 2 * (size_t)t : (size_t)t;
+    x16[col * cols + (size_t)u * 256 + pos] = hi;
+    if (split) x16[(col + 1) * cols + (size_t)u * 256 + pos] = lo;
+    const float mh = warp_sum(__half2float(hi)) * (1.0f / 32.0f);
+    const float ml = split ? warp_sum(__half2float(lo)) * (1.0f / 32.0f) : 0.0f;
+    if ((k & 31) == 0) {
+        const int j = k >> 5;
+        __half *m = means + (col * units + u) * 16;
+        const __half a = to_f16_clamped(mh);
+        m[j] = a;
+        m[8 + j] = to_f16_clamped(mh - __half2float(a));
+        if (split) {
+            __half *m2 = m + units * 16;
+            const __half b = to_f16_clamped(ml);
+            m2[j] = b;
+            m2[8 + j] = to_f16_clamped(ml - __half2float(b));
+        }
     }
 }
 
-int build_f16_rows(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, __half *out) {
-    size_t total = n * cols;
-    if (total == 0) return 0;
-    if (total % 4) return fail(ctx, DWIM_B200_EINVAL, "f16 rows: length %zu is not a multiple of 4", total);
-    size_t n4 = total / 4;
-    unsigned grid = (unsigned)((n4 + 255) / 256 < (size_t)ctx->sm_count * 8 ? (n4 + 255) / 256 : (size_t)ctx->sm_count * 8);
-    f16_rows_kernel<<<grid, 256, 0, ctx->stream>>>((const float4 *)x, n4, (uint2 *)out);
+int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out) {
+    if (n == 0 || cols == 0) return 0;
+    if (cols % 256) return fail(ctx, DWIM_B200_EINVAL, "GEMM operand: %zu columns are not whole 256-weight units", cols);
+    if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one operand build: %zu", n);
+    const size_t units = cols / 256, ncols = n * (split ? 2 : 1);
+    dim3 grid((unsigned)units, (unsigned)n);
+    gemm_operand_kernel<<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
     DWIM_LAUNCHED(ctx);
     return 0;
 }
