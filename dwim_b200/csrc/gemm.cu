@@ -35,6 +35,7 @@
 // Every mbarrier wait is bounded (ptx.cuh); a kernel that gave up says so in
 // the context's status word.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -63,7 +64,19 @@ struct GemmArgs {
     const float *aux;
     int epi;
     uint32_t *status;
+    unsigned long long *trace;   // debugging only: clock stamps of CTA (0,0), null in normal use
 };
+
+// Debug trace: (clock, tag, index) stamps, 400 slots per warp.
+#define GEMM_TRACE_SLOTS 400
+__device__ __forceinline__ void gtrace(const GemmArgs &a, int &n, int tag, int idx) {
+    if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && n < GEMM_TRACE_SLOTS) {
+        unsigned long long *p = a.trace + 2 * ((threadIdx.x >> 5) * GEMM_TRACE_SLOTS + n);
+        p[0] = clock64();
+        p[1] = ((unsigned long long)tag << 32) | (unsigned)idx;
+        n++;
+    }
+}
 
 template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
@@ -203,6 +216,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
     const int units = (int)a.units;
+    int tn = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < KSTAGES; s++) {
@@ -236,15 +250,16 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             for (int u = 0; u < units; u++) {
                 const int rs = u % RAW_STAGES, ms = u & 1;
                 const uint32_t par = (u & 1) ^ 1;   // K stage g is used once per unit
-                mbar_wait(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
+                mbar_wait_parked(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
                 mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
                 tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
                 for (int g = 0; g < 4; g++) {
-                    mbar_wait(empty0 + 8 * g, par, a.status, 0x20u);
+                    mbar_wait_parked(empty0 + 8 * g, par, a.status, 0x20u);
+                    gtrace(a, tn, 1, 4 * u + g);
                     mbar_expect_tx(full0 + 8 * g, C::B_BYTES);
                     tma_load_2d(stage0 + g * C::STAGE_BYTES + A_BYTES, &tmap_x, (4 * u + g) * BK, col0, full0 + 8 * g);
                 }
-                mbar_wait(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);
+                mbar_wait_parked(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);
                 mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
                 const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
                 tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // hi parts: K 0..7
@@ -257,10 +272,12 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         for (int u = 0; u < units; u++) {
             const int ab = u & 1;
             const uint32_t s1 = tmem_base + ab * BN, s2 = tmem_base + 2 * BN + ab * BN;
-            mbar_wait(accempty0 + 8 * ab, ((u >> 1) & 1) ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
+            mbar_wait_parked(accempty0 + 8 * ab, ((u >> 1) & 1) ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
             tc_fence_after();
             for (int g = 0; g < 4; g++) {
-                mbar_wait(full0 + 8 * g, u & 1, a.status, 0x100u);
+                gtrace(a, tn, 2, 4 * u + g);
+                mbar_wait_parked(full0 + 8 * g, u & 1, a.status, 0x100u);
+                gtrace(a, tn, 3, 4 * u + g);
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t a_addr = stage0 + g * C::STAGE_BYTES;
@@ -272,7 +289,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 }
                 __syncwarp();
             }
-            mbar_wait(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x200u);
+            mbar_wait_parked(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x200u);
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t am = min0 + ab * C::MIN_BYTES;
@@ -284,21 +301,35 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
     } else if (warp >= 2 + N_DRAIN_WARPS) {
         // ------------------------------ dequantizers ------------------------------
-        const int dt = threadIdx.x - (2 + N_DRAIN_WARPS) * 32;   // 0..255
-        const int r = dt >> 1, h = dt & 1;
+        // warp w decodes half h = w / 4 of rows 32*(w % 4) + lane: 32 different
+        // rows per store instruction, which the swizzle spreads over all banks
+        const int dw = warp - (2 + N_DRAIN_WARPS);
+        const int r = (dw & 3) * 32 + lane, h = dw >> 2;
         for (int u = 0; u < units; u++) {
             const int rs = u % RAW_STAGES, ms = u & 1;
-            mbar_wait(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
+            mbar_wait_parked(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
             const uint32_t raw_row = raw0 + rs * RAW_BYTES + r * 144;
             const uint4 hdr = lds128(raw_row);
-            for (int g = 0; g < 4; g++) {
-                mbar_wait(empty0 + 8 * g, (u & 1) ^ 1, a.status, 0x800u);
+            // two K blocks per hand-over: the fixed cost (barrier wait, proxy fence,
+            // arrive) is paid once per 128 of K and the two decodes overlap
+#pragma unroll
+            for (int g = 0; g < 4; g += 2) {
+                gtrace(a, tn, 4, 4 * u + g);
+                mbar_wait_parked(empty0 + 8 * g, (u & 1) ^ 1, a.status, 0x800u);
+                mbar_wait_parked(empty0 + 8 * (g + 1), (u & 1) ^ 1, a.status, 0x800u);
+                gtrace(a, tn, 5, 4 * u + g);
                 dequant_q4k_32(hdr, raw_row, g, h, stage0 + g * C::STAGE_BYTES + r * 128, r & 7);
+                dequant_q4k_32(hdr, raw_row, g + 1, h, stage0 + (g + 1) * C::STAGE_BYTES + r * 128, r & 7);
+                gtrace(a, tn, 6, 4 * u + g);
                 fence_async_smem();      // the tensor core reads shared memory through the async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * g);
+                if (lane == 0) {
+                    mbar_arrive(full0 + 8 * g);
+                    mbar_arrive(full0 + 8 * (g + 1));
+                }
+                gtrace(a, tn, 7, 4 * u + g);
             }
-            mbar_wait(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);
+            mbar_wait_parked(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);
             uint32_t m8[4];
             mins_q4k(hdr, m8);
             // A' = [m_0..m_7 | m_0..m_7]: K half h of row r
@@ -322,8 +353,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] = 0.0f;
         for (int u = 0; u < units; u++) {
             const int ab = u & 1;
-            mbar_wait(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x2000u);    // the row scales are written
-            mbar_wait(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);    // the unit's sums are complete
+            mbar_wait_parked(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x2000u);    // the row scales are written
+            gtrace(a, tn, 8, u);
+            mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);    // the unit's sums are complete
+            gtrace(a, tn, 9, u);
             tc_fence_after();
             const float2 sc = lds64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 8);
 #pragma unroll
@@ -339,6 +372,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
+            gtrace(a, tn, 10, u);
         }
         const size_t row = (size_t)row0 + rl;
         if (row < a.rows) {
@@ -423,7 +457,15 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     if ((rc = encode_2d(ctx, &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand + ncols * w.cols, units * 16, ncols, units * 32, 8,
                         BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
         return rc;
-    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status};
+    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status, nullptr};
+    static unsigned long long *tbuf = nullptr;
+    static int traced = 0;
+    const char *tenv = getenv("DWIM_B200_GEMM_TRACE");
+    if (tenv) {
+        if (!tbuf) cudaMalloc(&tbuf, 2 * 32 * GEMM_TRACE_SLOTS * sizeof(unsigned long long));
+        cudaMemsetAsync(tbuf, 0, 2 * 32 * GEMM_TRACE_SLOTS * sizeof(unsigned long long), ctx->stream);
+        a.trace = tbuf;
+    }
     auto kern = gemm_q4k_kernel<BN>;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
@@ -433,6 +475,19 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     kern<<<grid, GEMM_THREADS, C::SMEM, ctx->stream>>>(tw, tx, tm, a);
     DWIM_LAUNCHED(ctx);
+    if (tenv && ++traced == atoi(tenv)) {
+        static unsigned long long host[2 * 32 * GEMM_TRACE_SLOTS];
+        cudaStreamSynchronize(ctx->stream);
+        cudaMemcpy(host, tbuf, sizeof host, cudaMemcpyDeviceToHost);
+        unsigned long long t0 = ~0ull;
+        for (int i = 0; i < 32 * GEMM_TRACE_SLOTS; i++)
+            if (host[2 * i + 1] && host[2 * i] < t0) t0 = host[2 * i];
+        for (int wv = 0; wv < 32; wv++)
+            for (int i = 0; i < GEMM_TRACE_SLOTS; i++) {
+                unsigned long long v = host[2 * (wv * GEMM_TRACE_SLOTS + i) + 1];
+                if (v) fprintf(stderr, "GTRACE %llu tag=%llu warp=%d idx=%llu\n", host[2 * (wv * GEMM_TRACE_SLOTS + i)] - t0, v >> 32, wv, v & 0xffffffffull);
+            }
+    }
     return 0;
 }
 

@@ -33,6 +33,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Blocking form: the hardware may park the thread until the phase completes
+// (or a time limit passes), which leaves the issue slots to the warps that
+// have work.  For waits that are expected to be long.
+__device__ __forceinline__ bool mbar_try_suspend(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ uint64_t globaltimer() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -54,6 +68,14 @@ static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity
             return;
         }
     }
+}
+// Bounded wait built on the blocking form.
+__device__ __forceinline__ void mbar_wait_parked(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
+    if (mbar_try(bar, parity)) return;
+#pragma unroll 1
+    for (int i = 0; i < 4096; i++)
+        if (mbar_try_suspend(bar, parity)) return;
+    mbar_wait_slow(bar, parity, status, code);
 }
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint32_t *status, uint32_t code) {
 #pragma unroll 1
