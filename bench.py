@@ -295,23 +295,35 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     if rank == 0:
         pk = peaks()
         gemm = m > 16
+        # DRAM bytes per launch of the dominant kernel from the ncu captures summarised under
+        # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None where no capture exists.
+        traffic, traffic_note = None, None
+        if world == 1 and (fmt, rows, cols) == ("q4_k", 17408, 5120):
+            if m == 1:
+                traffic, traffic_note = 50.47e6, "profiles/gemv_kernel_q4k_c1.md"
+            elif gemm:
+                # captured at M=512 (76.6 MB); weights fixed, the rest in proportion to M
+                traffic = 50.1e6 + 26.5e6 * m / 512
+                traffic_note = "profiles/gemm_q4k_kernel_c2.md, captured at M=512 and scaled by M"
         if gemm:
             flops = 2.0 * m * my_rows * cols
             achieved = flops / per_kernel / 1e12
             roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"],
+                    "frac": achieved / pk["tflops"], "traffic": traffic, "traffic_source": traffic_note,
+                    "peak_source": pk["source"],
                     "frac_of_sustained": achieved / pk["tflops_sustained"] if pk["tflops_sustained"] else None}
         else:
             by = algorithmic_bytes(fmt, my_rows, cols, m)
             achieved = by / per_kernel / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                    "frac": achieved / pk["hbm_gbs"], "traffic": traffic, "traffic_source": traffic_note,
+                    "peak_source": pk["source"],
                     "frac_of_nominal_8tbs": achieved / 8000.0}
         roof["kernel_us"] = per_kernel * 1e6
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16 x int (exact) -> f32" if not gemm else "f16 -> f32", "data": "synthetic",
+            "dtype": "f16 (exact integer weights x f16 activations), f32 accumulate", "data": "synthetic",
             "config": workload_config(fmt, rows, cols, m, act, world),
             "tok_per_s": m / per_step,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(hx.nbytes),

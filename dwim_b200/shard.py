@@ -1,0 +1,92 @@
+"""Row sharding of a weight matrix over the GPUs of one node.
+
+The reference engine is single-GPU (gpu/cuda/mod.rs:230 opens device 0 and
+nothing else); this is new.  Output rows of ``out[t] = W . x[t]`` are
+independent, so rank ``r`` of ``world`` holds rows ``[begin_r, end_r)`` of W —
+cut at multiples of ``align`` rows, blocks untouched — multiplies them, and one
+all-gather re-assembles the token-major result on every rank:
+
+    rank r:   part_r[t, :] = W[begin_r:end_r] . x[t]            (its own GPU)
+    exchange: parts = all_gather(part_r)       [world, n, part_rows]
+    assemble: out[t, begin_r:end_r] = parts[r, t, :end_r-begin_r]
+
+``plan`` and ``assemble`` are the host-side statement of that layout (the
+device does ``assemble`` with ``B200.gather_rows``); ``RowSharded`` runs it
+with one process per GPU over ``torch.distributed`` (NCCL).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .device import B200, shard_rows
+from .tensor import Tensor
+
+
+def plan(rows: int, world: int, align: int = 16):
+    """[(begin, end)] per rank; rank 0 holds the most rows."""
+    return [shard_rows(rows, r, world, align) for r in range(world)]
+
+
+def part_rows(rows: int, world: int, align: int = 16) -> int:
+    """Rows of the common (padded) slice every rank contributes to the all-gather."""
+    b, e = shard_rows(rows, 0, world, align)
+    return e - b
+
+
+def assemble(parts: np.ndarray, n: int, rows: int, world: int, align: int = 16) -> np.ndarray:
+    """Token-major [n, rows] from the gathered [world, n, part_rows] slices."""
+    pr = part_rows(rows, world, align)
+    parts = np.asarray(parts).reshape(world, n, pr)
+    out = np.empty((n, rows), parts.dtype)
+    for r, (b, e) in enumerate(plan(rows, world, align)):
+        out[:, b:e] = parts[r, :, : e - b]
+    return out
+
+
+class RowSharded:
+    """A weight matrix split by output rows over the ranks of a process group.
+
+    Every rank constructs it with the same host ``Tensor`` (or only its own
+    slice via ``local=``) and calls ``matmul`` with the same activations; each
+    call leaves the full result in ``out`` on every rank.
+    """
+
+    def __init__(self, dev: B200, tensor: Tensor | None, rank: int, world: int, align: int = 16, group=None,
+                 local: Tensor | None = None, shape=None):
+        import torch
+        self.dev, self.rank, self.world, self.align, self.group = dev, rank, world, align, group
+        self.rows, self.cols = tensor.shape if tensor is not None else shape
+        self.begin, self.end = shard_rows(self.rows, rank, world, align)
+        self.part_rows = part_rows(self.rows, world, align)
+        mine = local if local is not None else tensor.slice_rows(self.begin, self.end)
+        assert mine.shape == (self.end - self.begin, self.cols)
+        self.weight = dev.upload(mine)
+        self._torch = torch
+        self._stream = torch.cuda.ExternalStream(dev.stream)
+        self._parts = None      # torch tensor [world * n * part_rows], and its device views
+        self._views = None
+
+    def _buffers(self, n: int):
+        if self._parts is None or self._parts.numel() != self.world * n * self.part_rows:
+            t = self._torch
+            self._parts = t.zeros(self.world * n * self.part_rows, dtype=t.float32, device="cuda")
+            mine = self._parts[self.rank * n * self.part_rows:(self.rank + 1) * n * self.part_rows]
+            my_rows = self.end - self.begin
+            # a short last shard computes into a buffer of its own and is padded into the common slice
+            local = self.dev.wrap(mine.data_ptr(), n * my_rows) if my_rows == self.part_rows else self.dev.alloc(n * my_rows)
+            self._views = (mine, local, self.dev.wrap(self._parts.data_ptr(), self._parts.numel()))
+        return self._views
+
+    def matmul(self, out, x) -> None:
+        """out[t] = W . x[t] on every rank; ``out`` has n * rows floats."""
+        import torch.distributed as dist
+        n = len(x) // self.cols
+        mine, local, parts = self._buffers(n)
+        self.dev.matmul(local, self.weight, x)
+        my_rows = self.end - self.begin
+        with self._torch.cuda.stream(self._stream):
+            if my_rows != self.part_rows:
+                src = self._torch.as_tensor(self.dev.read(local)).reshape(n, my_rows).cuda()
+                mine.view(n, self.part_rows)[:, :my_rows] = src
+            dist.all_gather_into_tensor(self._parts, mine, group=self.group)
+        self.dev.gather_rows(out, parts, n, self.rows, self.world, self.align)

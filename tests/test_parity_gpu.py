@@ -341,3 +341,15 @@ def test_config3_shapes_full_size(dev, oracle, fmt, rows, cols, n):
 
 def test_config2_q4_k_m16_bf16_full_size(dev, oracle):
     full_size_case(dev, oracle, "q4_k", 17408, 5120, 16, seed=2, bf16=True)
+
+
+# ---- sharding: the device's re-assembly against the host statement of it ---------------------
+def test_gather_rows_matches_the_host_assembly(dev):
+    from dwim_b200 import shard
+    rng = np.random.default_rng(51)
+    for rows, world, align, n in [(17408, 8, 16, 3), (5120, 2, 16, 16), (77, 4, 16, 2), (100, 3, 7, 5)]:
+        pr = shard.part_rows(rows, world, align)
+        parts = rng.standard_normal((world, n, pr)).astype(np.float32)
+        out = dev.alloc(n * rows)
+        dev.gather_rows(out, dev.buffer(parts), n, rows, world, align)
+        assert np.array_equal(dev.read(out).reshape(n, rows), shard.assemble(parts, n, rows, world, align))
