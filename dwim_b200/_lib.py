@@ -51,6 +51,7 @@ SIGNATURES = {
     "dwim_b200_matmul": (C.c_int, [_vp, _vp, _vp, _vp]),
     "dwim_b200_matmul_add": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "dwim_b200_swiglu": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "dwim_b200_matmul_static": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "dwim_b200_shard_rows": (C.c_int, [_sz, C.c_int, C.c_int, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "dwim_b200_gather_rows": (C.c_int, [_vp, _vp, _vp, _sz, _sz, C.c_int, _sz]),
 }

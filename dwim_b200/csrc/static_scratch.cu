@@ -1,0 +1,69 @@
+// A matmul entry point that allocates nothing.
+//
+// Who needs it: callers that hold their GPU memory in an arena sized once at
+// start-up (the engine fits its context to the memory that is free,
+// inference/memory.rs:33-46, and then must not grow), and callers inside a
+// region where cudaMalloc is not allowed or would synchronize the device.
+// dwim_b200_matmul keeps the 16-bit operand form of the activations in a
+// buffer it allocates on first use; here that scratch is a fixed array in the
+// library's own image instead.
+//
+// The array lives in every GPU's memory from the moment the library is loaded
+// there until the process ends (STATIC_SCRATCH_BYTES per device).  All calls
+// share it and it keeps the last call's contents: every byte a call reads it
+// has written itself first (the prologue rewrites each panel in full), so
+// nothing has to start at zero — but two calls that overlap on the GPU (two
+// contexts, two streams) would race on it.  Calls on one context are ordered
+// by its stream.
+#include "common.cuh"
+
+namespace {
+
+constexpr size_t STATIC_SCRATCH_BYTES = 1u << 20;   // 1 MiB
+
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the array, per device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use.
+void *g_scratch_addr[64] = {nullptr};
+
+int scratch_address(dwim_b200_ctx *ctx, void **out) {
+    const int d = ctx->device;
+    if (d < 0 || d >= 64) return dwim::fail(ctx, DWIM_B200_EINVAL, "device %d out of range", d);
+    if (!g_scratch_addr[d]) {
+        int current = -1;
+        DWIM_CUDA(ctx, cudaGetDevice(&current));
+        if (current != d) DWIM_CUDA(ctx, cudaSetDevice(d));
+        void *p = nullptr;
+        DWIM_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_scratch));
+        g_scratch_addr[d] = p;
+    }
+    *out = g_scratch_addr[d];
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwim_b200_weight *w, const float *x, size_t n) {
+    using namespace dwim;
+    if (!ctx || !w) return DWIM_B200_EINVAL;
+    const WeightView &v = w->v;
+    if (n == 0 || v.rows == 0) return 0;
+    if (!out || !x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: null pointer");
+    if (out == x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: output aliases input");
+    const int split = 1;                                  // f32 activations: value + remainder columns
+    if (n > (size_t)gemv_max_tokens(split))
+        return fail(ctx, DWIM_B200_EINVAL, "matmul_static: %zu tokens, at most %d", n, gemv_max_tokens(split));
+    const int ncols = (int)n * 2;
+    const size_t need = panel_bytes(v.cols, ncols);
+    if (need > STATIC_SCRATCH_BYTES)
+        return fail(ctx, DWIM_B200_EINVAL,
+                    "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
+                    v.cols, need, STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    int rc = scratch_address(ctx, &scratch);
+    if (rc) return rc;
+    rc = build_panels(ctx, x, n, v.cols, v.fmt == Q4_K ? SHADOW_PANEL_Q4K : SHADOW_PANEL_NATURAL, split, (__half *)scratch);
+    if (rc) return rc;
+    return gemv_small(ctx, v, (const __half *)scratch, ncols, 0, (int)n, 0, split, out, nullptr, EPI_STORE);
+}

@@ -144,6 +144,13 @@ class B200:
     def swiglu(self, out: Buffer, gate: Weight, up: Weight, x: Buffer, scratch: Buffer) -> None:
         self._check(self._L.dwim_b200_swiglu(self._ctx, out._h, gate._h, up._h, x._h, scratch._h))
 
+    def matmul_static(self, out: Buffer, w: Weight, x: Buffer) -> None:
+        """``matmul`` for up to 8 tokens that allocates nothing: the operand
+        scratch is a fixed array inside the library, shared by every call on
+        the GPU.  For callers that must not allocate device memory."""
+        n = len(x) // w.shape[1]
+        self._check(self._L.dwim_b200_matmul_static(self._ctx, out.ptr, w._h, x.ptr, n))
+
     # -- beside the trait -----------------------------------------------------
     def sync(self) -> None:
         self._check(self._L.dwim_b200_sync(self._ctx))

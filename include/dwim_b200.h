@@ -156,6 +156,20 @@ DWIM_B200_API int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, 
 DWIM_B200_API int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *gate,
                                    const dwim_b200_weight *up, dwim_b200_buffer *x, dwim_b200_buffer *scratch);
 
+/* No counterpart in the reference.  out[t] = w . x[t] for n <= 8 token rows,
+ * like dwim_b200_matmul, but without allocating anything: `out` (n * rows f32)
+ * and `x` (n * cols f32) are device pointers the caller owns, and the 16-bit
+ * operand form of x goes to a fixed 1 MiB array inside the library instead of
+ * a buffer allocated on first use.  For callers whose device memory is an
+ * arena sized once, or that run where cudaMalloc is not allowed.  Sizes whose
+ * operand form does not fit (n * cols beyond about 246 000) are refused with
+ * EINVAL.  The array is shared by all calls on a GPU: calls that overlap there
+ * race; calls on one context are ordered.  The first call on a device looks
+ * the array's address up (cudaGetSymbolAddress) and should come before any
+ * stream capture. */
+DWIM_B200_API int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwim_b200_weight *w, const float *x,
+                                          size_t n);
+
 /* ---- sharding across GPUs (no counterpart in the reference) -------------- */
 
 /* The rows rank `rank` of `world` holds when a matrix is split by output
