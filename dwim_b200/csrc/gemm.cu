@@ -47,6 +47,7 @@ namespace {
 constexpr int TILE_M = 128;   // weight rows per CTA
 constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of f16
 constexpr int KSTAGES = 4;    // = K blocks per unit: stage index == K block within the unit
+constexpr int KPAIRS = 2;     // K blocks change hands in pairs: one barrier round trip per 128 of K
 constexpr int RAW_STAGES = 3;
 constexpr int MIN_STAGES = 2;
 constexpr int SCALE_SLOTS = 4;
@@ -109,6 +110,23 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
         "}\n" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// The same with the descriptors given as (low word, shared high word) and the
+// accumulate flag fixed at compile time: the issuing thread has about one
+// instruction slot per five cycles, so every instruction between two MMAs counts.
+template <int ACC>
+__device__ __forceinline__ void umma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
         : "memory");
 }
 // Arrive on an mbarrier once every MMA this thread issued so far has finished.
@@ -205,7 +223,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzled tiles want 1024-byte alignment
     // barriers, 8 bytes each
-    const uint32_t full0 = base, empty0 = base + 32, minfull0 = base + 64, minempty0 = base + 80;
+    const uint32_t full0 = base, empty0 = base + 32, minfull0 = base + 64;
     const uint32_t rawfull0 = base + 96, rawempty0 = base + 128, accfull0 = base + 160, accempty0 = base + 176;
     const uint32_t tmem_slot = base + 192;
     const uint32_t stage0 = base + BAR_BYTES;
@@ -219,14 +237,13 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     int tn = 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < KSTAGES; s++) {
+        for (int s = 0; s < KPAIRS; s++) {
             mbar_init(full0 + 8 * s, 1 + N_DEQ_WARPS);   // the producer's expect_tx arrival + one per dequant warp
             mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
         }
         for (int s = 0; s < MIN_STAGES; s++) {
             mbar_init(minfull0 + 8 * s, 1 + N_DEQ_WARPS);
-            mbar_init(minempty0 + 8 * s, 1);
-            mbar_init(accfull0 + 8 * s, 1);
+            mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's means operand has been read
             mbar_init(accempty0 + 8 * s, N_DRAIN_WARPS);
         }
         for (int s = 0; s < RAW_STAGES; s++) {
@@ -253,13 +270,14 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 mbar_wait_parked(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
                 mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
                 tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
-                for (int g = 0; g < 4; g++) {
-                    mbar_wait_parked(empty0 + 8 * g, par, a.status, 0x20u);
-                    gtrace(a, tn, 1, 4 * u + g);
-                    mbar_expect_tx(full0 + 8 * g, C::B_BYTES);
-                    tma_load_2d(stage0 + g * C::STAGE_BYTES + A_BYTES, &tmap_x, (4 * u + g) * BK, col0, full0 + 8 * g);
+                for (int p = 0; p < KPAIRS; p++) {
+                    mbar_wait_parked(empty0 + 8 * p, par, a.status, 0x20u);
+                    gtrace(a, tn, 1, 4 * u + 2 * p);
+                    mbar_expect_tx(full0 + 8 * p, 2 * C::B_BYTES);
+                    for (int g = 2 * p; g < 2 * p + 2; g++)
+                        tma_load_2d(stage0 + g * C::STAGE_BYTES + A_BYTES, &tmap_x, (4 * u + g) * BK, col0, full0 + 8 * p);
                 }
-                mbar_wait_parked(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);
+                mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);   // unit u-2 has read its means
                 mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
                 const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
                 tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // hi parts: K 0..7
@@ -268,36 +286,48 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
+        // The whole warp runs the loop (uniform control flow keeps addresses
+        // and descriptors on the uniform data path) and one lane issues.  The
+        // 16 descriptor pairs of a unit are the same for every unit; units are
+        // taken two at a time so that the accumulator buffer is static too.
         constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
-        for (int u = 0; u < units; u++) {
-            const int ab = u & 1;
-            const uint32_t s1 = tmem_base + ab * BN, s2 = tmem_base + 2 * BN + ab * BN;
-            mbar_wait_parked(accempty0 + 8 * ab, ((u >> 1) & 1) ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
-            tc_fence_after();
-            for (int g = 0; g < 4; g++) {
-                gtrace(a, tn, 2, 4 * u + g);
-                mbar_wait_parked(full0 + 8 * g, u & 1, a.status, 0x100u);
-                gtrace(a, tn, 3, 4 * u + g);
+        constexpr uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);   // stride offset 1024 B, version 1, 128-byte swizzle
+        const uint32_t a_lo = ((stage0 & 0x3ffffu) >> 4) | (1u << 16), b_lo = (((stage0 + A_BYTES) & 0x3ffffu) >> 4) | (1u << 16);
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
+        for (int u0 = 0; u0 < units; u0 += 2) {
+#pragma unroll
+            for (int ab = 0; ab < 2; ab++) {
+                const int u = u0 + ab;
+                if (u >= units) break;
+                const uint32_t s1 = tm + ab * BN, s2 = tm + 2 * BN + ab * BN;
+                const uint32_t upar = (u0 >> 1) & 1;
+                mbar_wait_parked(accempty0 + 8 * ab, upar ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
+#pragma unroll
+                for (int p = 0; p < KPAIRS; p++) {
+                    gtrace(a, tn, 2, 4 * u + 2 * p);
+                    mbar_wait_parked(full0 + 8 * p, ab, a.status, 0x100u);
+                    gtrace(a, tn, 3, 4 * u + 2 * p);
+                    tc_fence_after();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {   // K block 2p + j/4, 32 bytes further along the swizzled row per K=16
+                            const uint32_t off = (2 * p + (j >> 2)) * (C::STAGE_BYTES >> 4) + 2 * (j & 3);
+                            if (p == 0 && j == 0) umma_f16_lo<0>(s1, a_lo + off, b_lo + off, desc_hi, idesc);
+                            else umma_f16_lo<1>(s1, a_lo + off, b_lo + off, desc_hi, idesc);
+                        }
+                        umma_commit(empty0 + 8 * p);    // the two stages may be refilled once these finish
+                    }
+                    __syncwarp();
+                }
+                mbar_wait_parked(minfull0 + 8 * ab, upar, a.status, 0x200u);
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t a_addr = stage0 + g * C::STAGE_BYTES;
-                    const uint64_t ad = smem_desc_sw128(a_addr), bd = smem_desc_sw128(a_addr + A_BYTES);
-#pragma unroll
-                    for (int k = 0; k < BK / 16; k++)   // 32 bytes further along the swizzled row per K=16
-                        umma_f16(s1, ad + 2 * k, bd + 2 * k, idesc, (g | k) != 0);
-                    umma_commit(empty0 + 8 * g);        // the stage may be refilled once these finish
+                    const uint32_t am = min0 + ab * C::MIN_BYTES;
+                    umma_f16(s2, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(am + AMIN_BYTES, BN * 16), idesc, 0);
+                    umma_commit(accfull0 + 8 * ab);     // both sums of the unit are complete
                 }
                 __syncwarp();
             }
-            mbar_wait_parked(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x200u);
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t am = min0 + ab * C::MIN_BYTES;
-                umma_f16(s2, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(am + AMIN_BYTES, BN * 16), idesc, 0);
-                umma_commit(minempty0 + 8 * ab);
-                umma_commit(accfull0 + 8 * ab);         // both sums of the unit are complete
-            }
-            __syncwarp();
         }
     } else if (warp >= 2 + N_DRAIN_WARPS) {
         // ------------------------------ dequantizers ------------------------------
@@ -315,21 +345,17 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
             for (int g = 0; g < 4; g += 2) {
                 gtrace(a, tn, 4, 4 * u + g);
-                mbar_wait_parked(empty0 + 8 * g, (u & 1) ^ 1, a.status, 0x800u);
-                mbar_wait_parked(empty0 + 8 * (g + 1), (u & 1) ^ 1, a.status, 0x800u);
+                mbar_wait_parked(empty0 + 8 * (g >> 1), (u & 1) ^ 1, a.status, 0x800u);
                 gtrace(a, tn, 5, 4 * u + g);
                 dequant_q4k_32(hdr, raw_row, g, h, stage0 + g * C::STAGE_BYTES + r * 128, r & 7);
                 dequant_q4k_32(hdr, raw_row, g + 1, h, stage0 + (g + 1) * C::STAGE_BYTES + r * 128, r & 7);
                 gtrace(a, tn, 6, 4 * u + g);
                 fence_async_smem();      // the tensor core reads shared memory through the async proxy
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full0 + 8 * g);
-                    mbar_arrive(full0 + 8 * (g + 1));
-                }
+                if (lane == 0) mbar_arrive(full0 + 8 * (g >> 1));
                 gtrace(a, tn, 7, 4 * u + g);
             }
-            mbar_wait_parked(minempty0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);
+            mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);   // unit u-2 has read its minimums
             uint32_t m8[4];
             mins_q4k(hdr, m8);
             // A' = [m_0..m_7 | m_0..m_7]: K half h of row r
