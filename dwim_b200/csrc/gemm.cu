@@ -51,8 +51,8 @@ constexpr int KPAIRS = 2;     // K blocks change hands in pairs: one barrier rou
 constexpr int RAW_STAGES = 3;
 constexpr int MIN_STAGES = 2;
 constexpr int SCALE_SLOTS = 4;
-constexpr int N_DEQ_WARPS = 8, N_DRAIN_WARPS = 8;
-constexpr int GEMM_THREADS = (2 + N_DRAIN_WARPS + N_DEQ_WARPS) * 32;
+constexpr int N_WORKERS = 16;                                      // warps 2..17: four per TMEM lane quadrant
+constexpr int GEMM_THREADS = (2 + N_WORKERS) * 32;
 constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // 18 KB
 constexpr int A_BYTES = TILE_M * BK * 2;                           // 16 KB
 constexpr int AMIN_BYTES = TILE_M * 16 * 2;                        // 4 KB: [k half][row][16 B]
@@ -88,7 +88,8 @@ template <int BN> struct Cfg {
     static constexpr int SMEM = BAR_BYTES + KSTAGES * STAGE_BYTES + MIN_STAGES * MIN_BYTES + RAW_STAGES * RAW_BYTES +
                                 SCALE_BYTES + 1024;                // + alignment slack
     static constexpr int TMEM_COLS = 4 * BN < 32 ? 32 : 4 * BN;    // S1 x2, S2 x2
-    static constexpr int DRAIN_COLS = BN / 2;                      // columns per drain warp
+    static constexpr int DRAIN_COLS = BN / 4 < 16 ? 16 : BN / 4;   // accumulator columns per draining warp
+    static constexpr int DRAINERS = BN / DRAIN_COLS;               // draining warps per lane quadrant (4, or 2 at BN=32)
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
@@ -178,30 +179,44 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f
 
 constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_M64 = 0xD400D400u, H2_SIXTEENTH = 0x2C002C00u;
 
-// ---- dequantizer: 32 weights of one row as exact sc*q halves ----------------------------
-// Thread (row, h) of K block g (0..3 inside the unit) owns sub-block 2g + h:
-// nibble h of the 32 bytes of group g.  A word's bytes come out in the order
+// ---- dequantizer: the 64 weights of one row and K block as exact sc*q halves ----------
+// K block g (0..3 inside the unit) is group g of the block's quants: 32 bytes
+// whose low nibbles are sub-block 2g (k = 0..31 of the K block) and high
+// nibbles sub-block 2g+1 (k = 32..63).  A word's bytes come out in the order
 // (0, 2, 1, 3); the activations are stored in the same order.
-__device__ __forceinline__ void dequant_q4k_32(const uint4 &hdr, uint32_t raw_row, int g, int h, uint32_t a_row, int row7) {
+struct Q4kBlock {
+    uint32_t words[8];                 // the 32 bytes of group g
+    uint32_t mul[2], add[2];           // per nibble half: x*mul + add turns the magic-number halves into sc*q
+};
+__device__ __forceinline__ void load_q4k_block(const uint4 &hdr, uint32_t raw_row, int g, Q4kBlock &b) {
     const uint4 q0 = lds128(raw_row + 16 + 32 * g), q1 = lds128(raw_row + 32 + 32 * g);
+    b.words[0] = q0.x; b.words[1] = q0.y; b.words[2] = q0.z; b.words[3] = q0.w;
+    b.words[4] = q1.x; b.words[5] = q1.y; b.words[6] = q1.z; b.words[7] = q1.w;
     const int sh = (g & 1) * 16;
     const uint32_t y = (hdr.y >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
     const uint32_t sc2 = g < 2 ? (y & 0x3f3fu) : ((w & 0x0f0fu) | ((y >> 2) & 0x3030u));
-    const uint32_t sc = (sc2 >> (8 * h)) & 0xffu;
-    const uint32_t scp = hsub2(0x64006400u | sc | (sc << 16), H2_1024);   // half2(sc, sc)
+    const uint32_t sa = sc2 & 0xffu, sb = sc2 >> 8;
+    const uint32_t spa = hsub2(0x64006400u | sa | (sa << 16), H2_1024);   // half2(sc_2g, sc_2g)
+    const uint32_t spb = hsub2(0x64006400u | sb | (sb << 16), H2_1024);   // half2(sc_2g+1, ..)
     // low nibbles: (1024 + q)*sc - 1024*sc; high nibbles: (1024 + 16q)*(sc/16) - 64*sc
-    const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu;
-    const uint32_t mul = h ? hmul2(scp, H2_SIXTEENTH) : scp;
-    const uint32_t add = hmul2(scp, h ? H2_M64 : H2_M1024);
-    const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    b.mul[0] = spa; b.add[0] = hmul2(spa, H2_M1024);
+    b.mul[1] = hmul2(spb, H2_SIXTEENTH); b.add[1] = hmul2(spb, H2_M64);
+}
+// Writes the row's 128 bytes of the stage's A tile (K-major, 128-byte swizzle:
+// 16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+__device__ __forceinline__ void store_q4k_block(const Q4kBlock &b, uint32_t a_row, int row7) {
 #pragma unroll
-    for (int c = 0; c < 4; c++) {   // 16-byte chunk c of this half: weights 8c .. 8c+7
-        const uint32_t w0 = words[2 * c], w1 = words[2 * c + 1];
-        const uint32_t o0 = hfma2(lop3_and_or(w0, mask, H2_1024), mul, add);        // bytes 0, 2
-        const uint32_t o1 = hfma2(lop3_and_or(w0 >> 8, mask, H2_1024), mul, add);   // bytes 1, 3
-        const uint32_t o2 = hfma2(lop3_and_or(w1, mask, H2_1024), mul, add);
-        const uint32_t o3 = hfma2(lop3_and_or(w1 >> 8, mask, H2_1024), mul, add);
-        sts128(a_row + (((4 * h + c) ^ row7) << 4), o0, o1, o2, o3);
+    for (int c = 0; c < 4; c++) {   // words 2c, 2c+1: weights 8c .. 8c+7 of either sub-block
+        const uint32_t w0 = b.words[2 * c], w1 = b.words[2 * c + 1], s0 = w0 >> 8, s1 = w1 >> 8;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu;
+            const uint32_t o0 = hfma2(lop3_and_or(w0, mask, H2_1024), b.mul[h], b.add[h]);   // bytes 0, 2
+            const uint32_t o1 = hfma2(lop3_and_or(s0, mask, H2_1024), b.mul[h], b.add[h]);   // bytes 1, 3
+            const uint32_t o2 = hfma2(lop3_and_or(w1, mask, H2_1024), b.mul[h], b.add[h]);
+            const uint32_t o3 = hfma2(lop3_and_or(s1, mask, H2_1024), b.mul[h], b.add[h]);
+            sts128(a_row + (((4 * h + c) ^ row7) << 4), o0, o1, o2, o3);
+        }
     }
 }
 
@@ -238,17 +253,17 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < KPAIRS; s++) {
-            mbar_init(full0 + 8 * s, 1 + N_DEQ_WARPS);   // the producer's expect_tx arrival + one per dequant warp
+            mbar_init(full0 + 8 * s, 1 + N_WORKERS / 2); // the producer's expect_tx arrival + the pair's eight worker warps
             mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
         }
         for (int s = 0; s < MIN_STAGES; s++) {
-            mbar_init(minfull0 + 8 * s, 1 + N_DEQ_WARPS);
+            mbar_init(minfull0 + 8 * s, 1 + 4);          // the producer + the four warps that write the minimums
             mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's means operand has been read
-            mbar_init(accempty0 + 8 * s, N_DRAIN_WARPS);
+            mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS);
         }
         for (int s = 0; s < RAW_STAGES; s++) {
             mbar_init(rawfull0 + 8 * s, 1);
-            mbar_init(rawempty0 + 8 * s, N_DEQ_WARPS);
+            mbar_init(rawempty0 + 8 * s, N_WORKERS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -329,55 +344,23 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 __syncwarp();
             }
         }
-    } else if (warp >= 2 + N_DRAIN_WARPS) {
-        // ------------------------------ dequantizers ------------------------------
-        // warp w decodes half h = w / 4 of rows 32*(w % 4) + lane: 32 different
-        // rows per store instruction, which the swizzle spreads over all banks
-        const int dw = warp - (2 + N_DRAIN_WARPS);
-        const int r = (dw & 3) * 32 + lane, h = dw >> 2;
-        for (int u = 0; u < units; u++) {
-            const int rs = u % RAW_STAGES, ms = u & 1;
-            mbar_wait_parked(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
-            const uint32_t raw_row = raw0 + rs * RAW_BYTES + r * 144;
-            const uint4 hdr = lds128(raw_row);
-            // two K blocks per hand-over: the fixed cost (barrier wait, proxy fence,
-            // arrive) is paid once per 128 of K and the two decodes overlap
-#pragma unroll
-            for (int g = 0; g < 4; g += 2) {
-                gtrace(a, tn, 4, 4 * u + g);
-                mbar_wait_parked(empty0 + 8 * (g >> 1), (u & 1) ^ 1, a.status, 0x800u);
-                gtrace(a, tn, 5, 4 * u + g);
-                dequant_q4k_32(hdr, raw_row, g, h, stage0 + g * C::STAGE_BYTES + r * 128, r & 7);
-                dequant_q4k_32(hdr, raw_row, g + 1, h, stage0 + (g + 1) * C::STAGE_BYTES + r * 128, r & 7);
-                gtrace(a, tn, 6, 4 * u + g);
-                fence_async_smem();      // the tensor core reads shared memory through the async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full0 + 8 * (g >> 1));
-                gtrace(a, tn, 7, 4 * u + g);
-            }
-            mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);   // unit u-2 has read its minimums
-            uint32_t m8[4];
-            mins_q4k(hdr, m8);
-            // A' = [m_0..m_7 | m_0..m_7]: K half h of row r
-            sts128(min0 + ms * C::MIN_BYTES + h * (TILE_M * 16) + r * 16, m8[0], m8[1], m8[2], m8[3]);
-            if (h == 0) sts64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + r) * 8, h2f_lo(hdr.x), 32.0f * h2f_hi(hdr.x));
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(minfull0 + 8 * ms);
-                mbar_arrive(rawempty0 + 8 * rs);
-            }
-        }
     } else {
-        // ------------------------------ drain + epilogue (warps 2-9) ------------------------------
-        const int quad = warp & 3;                      // the TMEM lanes this warp may read: 32*quad ..
-        const int chalf = (warp - 2) >> 2;              // which half of the tile's columns
+        // ------------------------------ workers (warps 2-17) ------------------------------
+        // Warp w owns TMEM lane quadrant w % 4 (weight rows 32*(w % 4) + lane)
+        // and K block g = (w - 2) / 4 of every unit: it decodes that block of
+        // its rows into the stage's A tile, then drains column quarter g of the
+        // previous unit's sums while the tensor cores work on this one.
+        const int quad = warp & 3;
+        const int g = (warp - 2) >> 2;
         const int rl = quad * 32 + lane;                // row within the tile = TMEM lane
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * C::DRAIN_COLS;
+        const bool drains = g < C::DRAINERS;
+        const uint32_t drain_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * C::DRAIN_COLS;
+        const uint32_t a_row = stage0 + g * C::STAGE_BYTES + rl * 128;
         float acc[C::DRAIN_COLS];
 #pragma unroll
         for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] = 0.0f;
-        for (int u = 0; u < units; u++) {
+
+        auto drain = [&](int u) {
             const int ab = u & 1;
             mbar_wait_parked(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x2000u);    // the row scales are written
             gtrace(a, tn, 8, u);
@@ -388,8 +371,8 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
             for (int c = 0; c < C::DRAIN_COLS / 16; c++) {
                 uint32_t v1[16], v2[16];
-                tmem_ld16(lane_addr + ab * BN + c * 16, v1);
-                tmem_ld16(lane_addr + 2 * BN + ab * BN + c * 16, v2);
+                tmem_ld16(drain_addr + ab * BN + c * 16, v1);
+                tmem_ld16(drain_addr + 2 * BN + ab * BN + c * 16, v2);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; j++)
@@ -399,32 +382,70 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
             gtrace(a, tn, 10, u);
+        };
+
+        for (int u = 0; u < units; u++) {
+            const int rs = u % RAW_STAGES, ms = u & 1;
+            mbar_wait_parked(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
+            const uint32_t raw_row = raw0 + rs * RAW_BYTES + rl * 144;
+            const uint4 hdr = lds128(raw_row);
+            Q4kBlock blk;
+            load_q4k_block(hdr, raw_row, g, blk);
+            gtrace(a, tn, 4, 4 * u + g);
+            mbar_wait_parked(empty0 + 8 * (g >> 1), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
+            gtrace(a, tn, 5, 4 * u + g);
+            store_q4k_block(blk, a_row, rl & 7);
+            gtrace(a, tn, 6, 4 * u + g);
+            fence_async_smem();          // the tensor core reads shared memory through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * (g >> 1));
+            gtrace(a, tn, 7, 4 * u + g);
+            if (g == 0) {
+                // the minimums' A operand [K half][row][16 B] (both K halves hold m_0..m_7:
+                // the means operand's halves are the means' hi and lo parts) and the row's scales
+                mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);   // unit u-2 has read its minimums
+                uint32_t m8[4];
+                mins_q4k(hdr, m8);
+                const uint32_t am = min0 + ms * C::MIN_BYTES + rl * 16;
+                sts128(am, m8[0], m8[1], m8[2], m8[3]);
+                sts128(am + TILE_M * 16, m8[0], m8[1], m8[2], m8[3]);
+                sts64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 8, h2f_lo(hdr.x), 32.0f * h2f_hi(hdr.x));
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(minfull0 + 8 * ms);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(rawempty0 + 8 * rs);
+            if (drains && u > 0) drain(u - 1);
         }
-        const size_t row = (size_t)row0 + rl;
-        if (row < a.rows) {
-            const size_t cbase = (size_t)col0 + chalf * C::DRAIN_COLS;
-            if (a.split) {
+        if (drains) {
+            drain(units - 1);
+            const size_t row = (size_t)row0 + rl;
+            if (row < a.rows) {
+                const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
+                if (a.split) {
 #pragma unroll
-                for (int j = 0; j < C::DRAIN_COLS; j += 2) {
-                    const size_t t = (cbase + j) >> 1;
-                    if (t < a.n) {
-                        const size_t i = t * a.rows + row;
-                        float x = acc[j] + acc[j + 1];
-                        if (a.epi == EPI_ADD) x += a.out[i];
-                        else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
-                        a.out[i] = x;
+                    for (int j = 0; j < C::DRAIN_COLS; j += 2) {
+                        const size_t t = (cbase + j) >> 1;
+                        if (t < a.n) {
+                            const size_t i = t * a.rows + row;
+                            float x = acc[j] + acc[j + 1];
+                            if (a.epi == EPI_ADD) x += a.out[i];
+                            else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
+                            a.out[i] = x;
+                        }
                     }
-                }
-            } else {
+                } else {
 #pragma unroll
-                for (int j = 0; j < C::DRAIN_COLS; j++) {
-                    const size_t t = cbase + j;
-                    if (t < a.n) {
-                        const size_t i = t * a.rows + row;
-                        float x = acc[j];
-                        if (a.epi == EPI_ADD) x += a.out[i];
-                        else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
-                        a.out[i] = x;
+                    for (int j = 0; j < C::DRAIN_COLS; j++) {
+                        const size_t t = cbase + j;
+                        if (t < a.n) {
+                            const size_t i = t * a.rows + row;
+                            float x = acc[j];
+                            if (a.epi == EPI_ADD) x += a.out[i];
+                            else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
+                            a.out[i] = x;
+                        }
                     }
                 }
             }
