@@ -55,7 +55,7 @@ constexpr int N_WORKERS = 16;                                      // warps 2..1
 constexpr int GEMM_THREADS = (2 + N_WORKERS) * 32;
 constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // 18 KB
 constexpr int A_BYTES = TILE_M * BK * 2;                           // 16 KB
-constexpr int AMIN_BYTES = TILE_M * 16 * 2;                        // 4 KB: [k half][row][16 B]
+constexpr int AMIN_BYTES = TILE_M * 16 * 4;                        // 8 KB: [K group of 8][row][16 B], four groups
 constexpr int BAR_BYTES = 1024;
 
 struct GemmArgs {
@@ -82,12 +82,12 @@ __device__ __forceinline__ void gtrace(const GemmArgs &a, int &n, int tag, int i
 template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [k half][column][16 B]
+    static constexpr int BMIN_BYTES = BN * 16 * 4;                 // [K group of 8][column][16 B], four groups
     static constexpr int MIN_BYTES = AMIN_BYTES + ((BMIN_BYTES + 1023) / 1024) * 1024;
-    static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 8;   // (d, 32*dmin) per row
+    static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 4;   // the unit's scale per row
     static constexpr int SMEM = BAR_BYTES + KSTAGES * STAGE_BYTES + MIN_STAGES * MIN_BYTES + RAW_STAGES * RAW_BYTES +
                                 SCALE_BYTES + 1024;                // + alignment slack
-    static constexpr int TMEM_COLS = 4 * BN < 32 ? 32 : 4 * BN;    // S1 x2, S2 x2
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;    // two accumulator buffers
     static constexpr int DRAIN_COLS = BN / 4 < 16 ? 16 : BN / 4;   // accumulator columns per draining warp
     static constexpr int DRAINERS = BN / DRAIN_COLS;               // draining warps per lane quadrant (4, or 2 at BN=32)
 };
@@ -167,23 +167,51 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n) {
 __device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
-__device__ __forceinline__ void sts64f(uint32_t a, float x, float y) {
-    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(x), "f"(y) : "memory");
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(x), "r"(y) : "memory");
 }
-__device__ __forceinline__ float2 lds64f(uint32_t a) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+__device__ __forceinline__ void sts32f(uint32_t a, float x) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x) : "memory"); }
+__device__ __forceinline__ float lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
+}
+// Two floats rounded to f16, `lo` in the low half.
+__device__ __forceinline__ uint32_t f16x2_rn(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_M64 = 0xD400D400u, H2_SIXTEENTH = 0x2C002C00u;
+constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_64 = 0x54005400u, H2_M64 = 0xD400D400u;
 
 // ---- dequantizer: the 64 weights of one row and K block as exact sc*q halves ----------
 // K block g (0..3 inside the unit) is group g of the block's quants: 32 bytes
 // whose low nibbles are sub-block 2g (k = 0..31 of the K block) and high
 // nibbles sub-block 2g+1 (k = 32..63).  A word's bytes come out in the order
 // (0, 2, 1, 3); the activations are stored in the same order.
+// A row's unit is drained as s * S, with S the one accumulator both operands
+// add into, and s = d * 2^e.  The main operand is sc*q*2^-e (still exact in
+// f16, subnormals included, for e <= 24) and the minimums enter as
+// -(32*dmin/s)*m_j.  e = 0 unless dmin is more than ~32 times d: it is chosen
+// from the two exponents so that 63 * 32*dmin/s stays below f16's maximum.
+// When d is zero, or e would pass 24 (the sc*q term is then below 2^-19 of the
+// other), s = 32*dmin, the main operand is zero and the minimums enter as -m_j.
+struct Q4kFold {
+    int e;        // the main operand is scaled by 2^-e
+    bool zero;    // the main operand is dropped
+};
+__device__ __forceinline__ Q4kFold q4k_fold(uint32_t d_dmin) {
+    const float d = h2f_lo(d_dmin), dmin = h2f_hi(d_dmin);
+    const int ed = (int)((__float_as_uint(d) >> 23) & 0xffu), em = (int)((__float_as_uint(dmin) >> 23) & 0xffu);
+    Q4kFold f;
+    f.e = max(0, em - ed - 4);
+    f.zero = d == 0.0f || f.e > 24;
+    if (f.zero) f.e = 0;
+    return f;
+}
+
 struct Q4kBlock {
     uint32_t words[8];                 // the 32 bytes of group g
     uint32_t mul[2], add[2];           // per nibble half: x*mul + add turns the magic-number halves into sc*q
@@ -196,11 +224,15 @@ __device__ __forceinline__ void load_q4k_block(const uint4 &hdr, uint32_t raw_ro
     const uint32_t y = (hdr.y >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
     const uint32_t sc2 = g < 2 ? (y & 0x3f3fu) : ((w & 0x0f0fu) | ((y >> 2) & 0x3030u));
     const uint32_t sa = sc2 & 0xffu, sb = sc2 >> 8;
-    const uint32_t spa = hsub2(0x64006400u | sa | (sa << 16), H2_1024);   // half2(sc_2g, sc_2g)
-    const uint32_t spb = hsub2(0x64006400u | sb | (sb << 16), H2_1024);   // half2(sc_2g+1, ..)
-    // low nibbles: (1024 + q)*sc - 1024*sc; high nibbles: (1024 + 16q)*(sc/16) - 64*sc
+    const Q4kFold f = q4k_fold(hdr.x);
+    // 2^-e as a half: normal down to 2^-14, subnormal below; zero drops the operand
+    const uint32_t p1 = f.zero ? 0u : (f.e <= 14 ? (uint32_t)(15 - f.e) << 10 : 1u << (24 - f.e));
+    const uint32_t p2 = p1 | (p1 << 16);
+    const uint32_t spa = hmul2(hsub2(0x64006400u | sa | (sa << 16), H2_1024), p2);   // half2 of sc_2g * 2^-e
+    const uint32_t spb = hmul2(hsub2(0x64006400u | sb | (sb << 16), H2_1024), p2);   // half2 of sc_2g+1 * 2^-e
+    // low nibbles: (1024 + q)*sc - 1024*sc; high nibbles: (64 + q)*sc - 64*sc
     b.mul[0] = spa; b.add[0] = hmul2(spa, H2_M1024);
-    b.mul[1] = hmul2(spb, H2_SIXTEENTH); b.add[1] = hmul2(spb, H2_M64);
+    b.mul[1] = spb; b.add[1] = hmul2(spb, H2_M64);
 }
 // Writes the row's 128 bytes of the stage's A tile (K-major, 128-byte swizzle:
 // 16-byte chunk c of row r sits at chunk c ^ (r & 7)).
@@ -210,24 +242,31 @@ __device__ __forceinline__ void store_q4k_block(const Q4kBlock &b, uint32_t a_ro
         const uint32_t w0 = b.words[2 * c], w1 = b.words[2 * c + 1], s0 = w0 >> 8, s1 = w1 >> 8;
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu;
-            const uint32_t o0 = hfma2(lop3_and_or(w0, mask, H2_1024), b.mul[h], b.add[h]);   // bytes 0, 2
-            const uint32_t o1 = hfma2(lop3_and_or(s0, mask, H2_1024), b.mul[h], b.add[h]);   // bytes 1, 3
-            const uint32_t o2 = hfma2(lop3_and_or(w1, mask, H2_1024), b.mul[h], b.add[h]);
-            const uint32_t o3 = hfma2(lop3_and_or(s1, mask, H2_1024), b.mul[h], b.add[h]);
+            // 0x6400 | q = 1024 + q; 0x5400 | q << 4 = 64 + q (the ulp of 64.0 is 1/16)
+            const uint32_t mask = h ? 0x00f000f0u : 0x000f000fu, magic = h ? H2_64 : H2_1024;
+            const uint32_t o0 = hfma2(lop3_and_or(w0, mask, magic), b.mul[h], b.add[h]);   // bytes 0, 2
+            const uint32_t o1 = hfma2(lop3_and_or(s0, mask, magic), b.mul[h], b.add[h]);   // bytes 1, 3
+            const uint32_t o2 = hfma2(lop3_and_or(w1, mask, magic), b.mul[h], b.add[h]);
+            const uint32_t o3 = hfma2(lop3_and_or(s1, mask, magic), b.mul[h], b.add[h]);
             sts128(a_row + (((4 * h + c) ^ row7) << 4), o0, o1, o2, o3);
         }
     }
 }
 
-// The row's eight 6-bit minimums as eight halves (16 bytes).
-__device__ __forceinline__ void mins_q4k(const uint4 &hdr, uint32_t (&o)[4]) {
-    const uint32_t lo4 = hdr.z & 0x3f3f3f3fu;                                          // m_0..m_3
-    const uint32_t hi4 = ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u);  // m_4..m_7
-    o[0] = hsub2(prmt(lo4, 0x64646464u, 0x5140u), H2_1024);
-    o[1] = hsub2(prmt(lo4, 0x64646464u, 0x5342u), H2_1024);
-    o[2] = hsub2(prmt(hi4, 0x64646464u, 0x5140u), H2_1024);
-    o[3] = hsub2(prmt(hi4, 0x64646464u, 0x5342u), H2_1024);
+// Four of the row's eight 6-bit minimums (m_0..m_3 for part 0, m_4..m_7 for
+// part 1), each times f, as two f16 terms (value and rounding remainder):
+// b[t] holds term t of the four values, two per word.
+__device__ __forceinline__ void mins_q4k_terms(const uint4 &hdr, int part, float f, uint32_t (&b)[2][2]) {
+    const uint32_t m4 = part ? (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3f3f3f3fu);
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        // byte -> float through the 2^23 magic number
+        const float p0 = (__uint_as_float(prmt(m4, 0x4B000000u, 0x7650 + 2 * i)) - 8388608.0f) * f;
+        const float p1 = (__uint_as_float(prmt(m4, 0x4B000000u, 0x7651 + 2 * i)) - 8388608.0f) * f;
+        const uint32_t hi = f16x2_rn(p0, p1);
+        b[0][i] = hi;
+        b[1][i] = f16x2_rn(p0 - h2f_lo(hi), p1 - h2f_hi(hi));
+    }
 }
 
 template <int BN>
@@ -257,7 +296,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
         }
         for (int s = 0; s < MIN_STAGES; s++) {
-            mbar_init(minfull0 + 8 * s, 1 + 4);          // the producer + the four warps that write the minimums
+            mbar_init(minfull0 + 8 * s, 1 + 8);          // the producer + the eight warps that write the minimums
             mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's means operand has been read
             mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS);
         }
@@ -295,8 +334,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);   // unit u-2 has read its means
                 mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
                 const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
-                tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // hi parts: K 0..7
-                tma_load_2d(bm + BN * 16, &tmap_m, u * 16 + 8, col0, minfull0 + 8 * ms);   // lo parts: K 8..15
+                // the means' hi and lo parts as K groups (hi, lo, hi, lo), against the
+                // minimums' terms (hi, hi, lo, lo): all four products
+                for (int k = 0; k < 4; k++)
+                    tma_load_2d(bm + k * BN * 16, &tmap_m, u * 16 + 8 * (k & 1), col0, minfull0 + 8 * ms);
             }
         }
     } else if (warp == 1) {
@@ -314,7 +355,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             for (int ab = 0; ab < 2; ab++) {
                 const int u = u0 + ab;
                 if (u >= units) break;
-                const uint32_t s1 = tm + ab * BN, s2 = tm + 2 * BN + ab * BN;
+                const uint32_t s1 = tm + ab * BN;
                 const uint32_t upar = (u0 >> 1) & 1;
                 mbar_wait_parked(accempty0 + 8 * ab, upar ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
 #pragma unroll
@@ -337,9 +378,12 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 mbar_wait_parked(minfull0 + 8 * ab, upar, a.status, 0x200u);
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t am = min0 + ab * C::MIN_BYTES;
-                    umma_f16(s2, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(am + AMIN_BYTES, BN * 16), idesc, 0);
-                    umma_commit(accfull0 + 8 * ab);     // both sums of the unit are complete
+                    // the minimums: K = 32 as two K=16 steps, two 16-byte groups apart
+                    const uint32_t am = min0 + ab * C::MIN_BYTES, bm = am + AMIN_BYTES;
+                    umma_f16(s1, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(bm, BN * 16), idesc, 1);
+                    umma_f16(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), smem_desc_plain(bm + 2 * BN * 16, BN * 16),
+                             idesc, 1);
+                    umma_commit(accfull0 + 8 * ab);     // the unit's sum is complete
                 }
                 __syncwarp();
             }
@@ -367,16 +411,14 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);    // the unit's sums are complete
             gtrace(a, tn, 9, u);
             tc_fence_after();
-            const float2 sc = lds64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 8);
+            const float sc = lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4);
 #pragma unroll
             for (int c = 0; c < C::DRAIN_COLS / 16; c++) {
-                uint32_t v1[16], v2[16];
-                tmem_ld16(drain_addr + ab * BN + c * 16, v1);
-                tmem_ld16(drain_addr + 2 * BN + ab * BN + c * 16, v2);
+                uint32_t v[16];
+                tmem_ld16(drain_addr + ab * BN + c * 16, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++)
-                    acc[c * 16 + j] += sc.x * __uint_as_float(v1[j]) - sc.y * __uint_as_float(v2[j]);
+                for (int j = 0; j < 16; j++) acc[c * 16 + j] = fmaf(sc, __uint_as_float(v[j]), acc[c * 16 + j]);
             }
             tc_fence_before();
             __syncwarp();
@@ -400,16 +442,21 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8 * (g >> 1));
             gtrace(a, tn, 7, 4 * u + g);
-            if (g == 0) {
-                // the minimums' A operand [K half][row][16 B] (both K halves hold m_0..m_7:
-                // the means operand's halves are the means' hi and lo parts) and the row's scales
+            if (g >= 2) {
+                // the minimums' A operand [K group][row][16 B]: groups (hi, hi, lo, lo) of the
+                // two f16 terms of -(32*dmin/s)*m_j; K block 2's warp writes m_0..m_3, K block 3's m_4..m_7
                 mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);   // unit u-2 has read its minimums
-                uint32_t m8[4];
-                mins_q4k(hdr, m8);
-                const uint32_t am = min0 + ms * C::MIN_BYTES + rl * 16;
-                sts128(am, m8[0], m8[1], m8[2], m8[3]);
-                sts128(am + TILE_M * 16, m8[0], m8[1], m8[2], m8[3]);
-                sts64f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 8, h2f_lo(hdr.x), 32.0f * h2f_hi(hdr.x));
+                const Q4kFold f = q4k_fold(hdr.x);
+                const float dmin32 = 32.0f * h2f_hi(hdr.x);
+                const float sc = f.zero ? dmin32 : h2f_lo(hdr.x) * __uint_as_float((uint32_t)(127 + f.e) << 23);
+                uint32_t b[2][2];
+                mins_q4k_terms(hdr, g - 2, f.zero ? -1.0f : -(dmin32 / sc), b);
+                const uint32_t am = min0 + ms * C::MIN_BYTES + rl * 16 + (g - 2) * 8;
+                sts64(am, b[0][0], b[0][1]);
+                sts64(am + TILE_M * 16, b[0][0], b[0][1]);
+                sts64(am + 2 * TILE_M * 16, b[1][0], b[1][1]);
+                sts64(am + 3 * TILE_M * 16, b[1][0], b[1][1]);
+                if (g == 2) sts32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4, sc);
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(minfull0 + 8 * ms);

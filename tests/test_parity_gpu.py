@@ -191,6 +191,40 @@ def test_matmul_golden_cases(dev, fmt):
     assert max_rel_err(dev.read(out), g[f"{fmt}_swiglu"]) <= 1e-4
 
 
+@pytest.mark.parametrize("bf16", [False, True])
+def test_q4_k_gemm_scale_extremes(dev, oracle, bf16):
+    """The tensor-core kernel folds a block's minimums into the same accumulator
+    as its quants, scaled by dmin/d: rows whose blocks have d = 0, dmin = 0, either
+    sign, or dmin up to 2^40 times d must still match the CPU result."""
+    rng = np.random.default_rng(47)
+    rows, cols, n = 256, 1024, 40
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)).copy()
+    regimes = [(1e-3, 2e-3), (0.0, 0.05), (0.05, 0.0), (0.0, 0.0), (1e-3, 0.1), (1e-4, 6.0), (2.4e-7, 30.0),
+               (6e-8, 60000.0), (-1e-3, 2e-3), (1e-3, -2e-3), (3e-5, 1.0), (1.0, 6e-8)]
+    v = blocks.reshape(rows, cols // 256, 144)
+    for r in range(rows):
+        d, dmin = regimes[r % len(regimes)]
+        v[r, :, 0:2] = np.frombuffer(np.float16(d).tobytes(), np.uint8)
+        v[r, :, 2:4] = np.frombuffer(np.float16(dmin).tobytes(), np.uint8)
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    xb = dev.alloc(n * cols)
+    if bf16:
+        bits = oracle.to_bf16(x)
+        dev.write_bf16(xb, bits)
+        x = oracle.bf16(bits).reshape(n, cols)
+    else:
+        dev.write(xb, x)
+    out = dev.alloc(n * rows)
+    dev.matmul(out, upload(dev, "q4_k", rows, cols, blocks), xb)
+    got, want = dev.read(out).reshape(n, rows), oracle.matmul("q4_k", blocks, rows, cols, x).reshape(n, rows)
+    for k, (d, dmin) in enumerate(regimes):
+        g, w = got[:, k::len(regimes)], want[:, k::len(regimes)]
+        if d == 0.0 and dmin == 0.0:
+            assert not g.any() and not w.any()
+        else:
+            assert max_rel_err(g, w) <= 2e-5, f"d={d} dmin={dmin}: {max_rel_err(g, w):.2e}"
+
+
 def test_shadow_is_rebuilt_after_a_write(dev, oracle):
     """One input buffer reused: across formats (different operand layouts) and
     after being overwritten."""
