@@ -46,16 +46,15 @@ namespace {
 
 constexpr int TILE_M = 128;   // weight rows per CTA
 constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of f16
-constexpr int KSTAGES = 4;    // = K blocks per unit: stage index == K block within the unit
-constexpr int KPAIRS = 2;     // K blocks change hands in pairs: one barrier round trip per 128 of K
-constexpr int RAW_STAGES = 3;
-constexpr int MIN_STAGES = 2;
+constexpr int KBLOCKS = 4;    // K blocks per unit = stages of the A ring: A stage index == K block within the unit
 constexpr int SCALE_SLOTS = 4;
 constexpr int N_WORKERS = 16;                                      // warps 2..17: four per TMEM lane quadrant
-constexpr int GEMM_THREADS = (2 + N_WORKERS) * 32;
+constexpr int RAW_WARP = 2 + N_WORKERS;                            // the packed weights' producer
+constexpr int GEMM_THREADS = (3 + N_WORKERS) * 32;
 constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // 18 KB
 constexpr int A_BYTES = TILE_M * BK * 2;                           // 16 KB
 constexpr int AMIN_BYTES = TILE_M * 16 * 4;                        // 8 KB: [K group of 8][row][16 B], four groups
+constexpr int MAX_SMEM = 227 * 1024;
 constexpr int BAR_BYTES = 1024;
 
 struct GemmArgs {
@@ -79,14 +78,26 @@ __device__ __forceinline__ void gtrace(const GemmArgs &a, int &n, int tag, int i
     }
 }
 
+// Per tile width.  Up to 128 columns everything is double-buffered by units:
+// the B ring has one stage per K block like the A ring, and K blocks change
+// hands in pairs (one barrier round trip per 128 of K, which the MMA warp's
+// 64-cycle issue budget needs).  At 256 columns a decoded weight is used twice
+// as often, an MMA takes 128 cycles, and shared memory is the limit: three B
+// stages, two raw stages, one stage of the minimums' operands, and a hand-over
+// per K block (a B stage is reloaded as soon as its own K block is done).
 template <int BN> struct Cfg {
+    static constexpr int B_STAGES = BN > 128 ? 3 : 4;
+    static constexpr int RAW_STAGES = BN > 128 ? 2 : 3;
+    static constexpr int MIN_STAGES = BN > 128 ? 1 : 2;
+    static constexpr int HAND = BN > 128 ? 1 : 2;                  // K blocks per hand-over
+    static constexpr int NHAND = KBLOCKS / HAND;
     static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BMIN_BYTES = BN * 16 * 4;                 // [K group of 8][column][16 B], four groups
+    static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [K group of 8][column][16 B]: the means' hi and lo parts
     static constexpr int MIN_BYTES = AMIN_BYTES + ((BMIN_BYTES + 1023) / 1024) * 1024;
     static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 4;   // the unit's scale per row
-    static constexpr int SMEM = BAR_BYTES + KSTAGES * STAGE_BYTES + MIN_STAGES * MIN_BYTES + RAW_STAGES * RAW_BYTES +
-                                SCALE_BYTES + 1024;                // + alignment slack
+    static constexpr int SMEM = BAR_BYTES + KBLOCKS * A_BYTES + B_STAGES * B_BYTES + MIN_STAGES * MIN_BYTES +
+                                RAW_STAGES * RAW_BYTES + SCALE_BYTES + 1024;   // + alignment slack
+    static_assert(SMEM <= MAX_SMEM, "the tile does not fit shared memory");
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;    // two accumulator buffers
     static constexpr int DRAIN_COLS = BN / 4 < 16 ? 16 : BN / 4;   // accumulator columns per draining warp
     static constexpr int DRAINERS = BN / DRAIN_COLS;               // draining warps per lane quadrant (4, or 2 at BN=32)
@@ -280,10 +291,11 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const uint32_t full0 = base, empty0 = base + 32, minfull0 = base + 64;
     const uint32_t rawfull0 = base + 96, rawempty0 = base + 128, accfull0 = base + 160, accempty0 = base + 176;
     const uint32_t tmem_slot = base + 192;
-    const uint32_t stage0 = base + BAR_BYTES;
-    const uint32_t min0 = stage0 + KSTAGES * C::STAGE_BYTES;
-    const uint32_t raw0 = min0 + MIN_STAGES * C::MIN_BYTES;
-    const uint32_t scale0 = raw0 + RAW_STAGES * RAW_BYTES;
+    const uint32_t astage0 = base + BAR_BYTES;
+    const uint32_t bstage0 = astage0 + KBLOCKS * A_BYTES;
+    const uint32_t min0 = bstage0 + C::B_STAGES * C::B_BYTES;
+    const uint32_t raw0 = min0 + C::MIN_STAGES * C::MIN_BYTES;
+    const uint32_t scale0 = raw0 + C::RAW_STAGES * RAW_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
@@ -291,16 +303,16 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     int tn = 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < KPAIRS; s++) {
-            mbar_init(full0 + 8 * s, 1 + N_WORKERS / 2); // the producer's expect_tx arrival + the pair's eight worker warps
+        for (int s = 0; s < C::NHAND; s++) {
+            mbar_init(full0 + 8 * s, 1 + 4 * C::HAND);   // the producer's expect_tx arrival + the hand-over's worker warps
             mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
         }
-        for (int s = 0; s < MIN_STAGES; s++) {
+        for (int s = 0; s < 2; s++) {
             mbar_init(minfull0 + 8 * s, 1 + 8);          // the producer + the eight warps that write the minimums
-            mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's means operand has been read
+            mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's minimums and means have been read
             mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS);
         }
-        for (int s = 0; s < RAW_STAGES; s++) {
+        for (int s = 0; s < C::RAW_STAGES; s++) {
             mbar_init(rawfull0 + 8 * s, 1);
             mbar_init(rawempty0 + 8 * s, N_WORKERS);
         }
@@ -319,37 +331,54 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             for (int u = 0; u < units; u++) {
-                const int rs = u % RAW_STAGES, ms = u & 1;
-                const uint32_t par = (u & 1) ^ 1;   // K stage g is used once per unit
-                mbar_wait_parked(rawempty0 + 8 * rs, ((u / RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
-                mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
-                tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
-                for (int p = 0; p < KPAIRS; p++) {
-                    mbar_wait_parked(empty0 + 8 * p, par, a.status, 0x20u);
-                    gtrace(a, tn, 1, 4 * u + 2 * p);
-                    mbar_expect_tx(full0 + 8 * p, 2 * C::B_BYTES);
-                    for (int g = 2 * p; g < 2 * p + 2; g++)
-                        tma_load_2d(stage0 + g * C::STAGE_BYTES + A_BYTES, &tmap_x, (4 * u + g) * BK, col0, full0 + 8 * p);
+                const int ms = u % C::MIN_STAGES;
+                for (int h = 0; h < C::NHAND; h++) {
+                    // B stage kb % B_STAGES was last read by K block kb - B_STAGES
+                    for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
+                        const int prev = KBLOCKS * u + g - C::B_STAGES;
+                        if (prev >= 0)
+                            mbar_wait_parked(empty0 + 8 * ((prev % KBLOCKS) / C::HAND), (prev / KBLOCKS) & 1, a.status, 0x20u);
+                    }
+                    gtrace(a, tn, 1, KBLOCKS * u + h * C::HAND);
+                    mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES);
+                    for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
+                        const int kb = KBLOCKS * u + g;
+                        tma_load_2d(bstage0 + (kb % C::B_STAGES) * C::B_BYTES, &tmap_x, kb * BK, col0, full0 + 8 * h);
+                    }
                 }
-                mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x40u);   // unit u-2 has read its means
+                // the minimums' stage was last read by unit u - MIN_STAGES
+                if (u >= C::MIN_STAGES) {
+                    const int uu = u - C::MIN_STAGES;
+                    mbar_wait_parked(accfull0 + 8 * (uu & 1), (uu >> 1) & 1, a.status, 0x40u);
+                }
                 mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
                 const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
-                // the means' hi and lo parts as K groups (hi, lo, hi, lo), against the
-                // minimums' terms (hi, hi, lo, lo): all four products
-                for (int k = 0; k < 4; k++)
-                    tma_load_2d(bm + k * BN * 16, &tmap_m, u * 16 + 8 * (k & 1), col0, minfull0 + 8 * ms);
+                tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // the means' hi parts
+                tma_load_2d(bm + BN * 16, &tmap_m, u * 16 + 8, col0, minfull0 + 8 * ms);   // and lo parts
+            }
+        }
+    } else if (warp == RAW_WARP) {
+        // ------------------------------ packed weights' producer ------------------------------
+        // Its own warp: the blocks come from HBM and must run as far ahead as the
+        // ring allows, whatever the activations' producer is waiting for.
+        if (lane == 0) {
+            for (int u = 0; u < units; u++) {
+                const int rs = u % C::RAW_STAGES;
+                mbar_wait_parked(rawempty0 + 8 * rs, ((u / C::RAW_STAGES) & 1) ^ 1, a.status, 0x10u);
+                mbar_expect_tx(rawfull0 + 8 * rs, TILE_M * 144);
+                tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
             }
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp runs the loop (uniform control flow keeps addresses
-        // and descriptors on the uniform data path) and one lane issues.  The
-        // 16 descriptor pairs of a unit are the same for every unit; units are
-        // taken two at a time so that the accumulator buffer is static too.
+        // and descriptors on the uniform data path) and one lane issues.  Units
+        // are taken two at a time so that the accumulator buffer is static.
         constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
         constexpr uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);   // stride offset 1024 B, version 1, 128-byte swizzle
-        const uint32_t a_lo = ((stage0 & 0x3ffffu) >> 4) | (1u << 16), b_lo = (((stage0 + A_BYTES) & 0x3ffffu) >> 4) | (1u << 16);
+        const uint32_t a_lo = ((astage0 & 0x3ffffu) >> 4) | (1u << 16), b_lo = ((bstage0 & 0x3ffffu) >> 4) | (1u << 16);
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
+        int bs = 0;                                                   // the B stage of the next K block
         for (int u0 = 0; u0 < units; u0 += 2) {
 #pragma unroll
             for (int ab = 0; ab < 2; ab++) {
@@ -359,30 +388,37 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 const uint32_t upar = (u0 >> 1) & 1;
                 mbar_wait_parked(accempty0 + 8 * ab, upar ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
 #pragma unroll
-                for (int p = 0; p < KPAIRS; p++) {
-                    gtrace(a, tn, 2, 4 * u + 2 * p);
-                    mbar_wait_parked(full0 + 8 * p, ab, a.status, 0x100u);
-                    gtrace(a, tn, 3, 4 * u + 2 * p);
+                for (int h = 0; h < C::NHAND; h++) {
+                    gtrace(a, tn, 2, KBLOCKS * u + h * C::HAND);
+                    mbar_wait_parked(full0 + 8 * h, ab, a.status, 0x100u);
+                    gtrace(a, tn, 3, KBLOCKS * u + h * C::HAND);
                     tc_fence_after();
-                    if (lane == 0) {
 #pragma unroll
-                        for (int j = 0; j < 8; j++) {   // K block 2p + j/4, 32 bytes further along the swizzled row per K=16
-                            const uint32_t off = (2 * p + (j >> 2)) * (C::STAGE_BYTES >> 4) + 2 * (j & 3);
-                            if (p == 0 && j == 0) umma_f16_lo<0>(s1, a_lo + off, b_lo + off, desc_hi, idesc);
-                            else umma_f16_lo<1>(s1, a_lo + off, b_lo + off, desc_hi, idesc);
+                    for (int gg = 0; gg < C::HAND; gg++) {
+                        const int g = h * C::HAND + gg;
+                        const uint32_t ad = a_lo + g * (A_BYTES >> 4);
+                        const uint32_t bd = b_lo + (C::B_STAGES == KBLOCKS ? g : bs) * (C::B_BYTES >> 4);
+                        if (lane == 0) {
+#pragma unroll
+                            for (int k = 0; k < BK / 16; k++) {   // 32 bytes further along the swizzled row per K=16
+                                if (g == 0 && k == 0) umma_f16_lo<0>(s1, ad, bd, desc_hi, idesc);
+                                else umma_f16_lo<1>(s1, ad + 2 * k, bd + 2 * k, desc_hi, idesc);
+                            }
                         }
-                        umma_commit(empty0 + 8 * p);    // the two stages may be refilled once these finish
+                        bs = bs + 1 == C::B_STAGES ? 0 : bs + 1;
                     }
+                    if (lane == 0) umma_commit(empty0 + 8 * h);   // the stages may be refilled once these finish
                     __syncwarp();
                 }
-                mbar_wait_parked(minfull0 + 8 * ab, upar, a.status, 0x200u);
+                const int ms = u % C::MIN_STAGES;
+                mbar_wait_parked(minfull0 + 8 * ms, (u / C::MIN_STAGES) & 1, a.status, 0x200u);
                 tc_fence_after();
                 if (lane == 0) {
-                    // the minimums: K = 32 as two K=16 steps, two 16-byte groups apart
-                    const uint32_t am = min0 + ab * C::MIN_BYTES, bm = am + AMIN_BYTES;
-                    umma_f16(s1, smem_desc_plain(am, TILE_M * 16), smem_desc_plain(bm, BN * 16), idesc, 1);
-                    umma_f16(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), smem_desc_plain(bm + 2 * BN * 16, BN * 16),
-                             idesc, 1);
+                    // the minimums: terms (hi, hi | lo, lo) against the means' (hi, lo) twice
+                    const uint32_t am = min0 + ms * C::MIN_BYTES;
+                    const uint64_t bdm = smem_desc_plain(am + AMIN_BYTES, BN * 16);
+                    umma_f16(s1, smem_desc_plain(am, TILE_M * 16), bdm, idesc, 1);
+                    umma_f16(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), bdm, idesc, 1);
                     umma_commit(accfull0 + 8 * ab);     // the unit's sum is complete
                 }
                 __syncwarp();
@@ -399,16 +435,17 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int rl = quad * 32 + lane;                // row within the tile = TMEM lane
         const bool drains = g < C::DRAINERS;
         const uint32_t drain_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * C::DRAIN_COLS;
-        const uint32_t a_row = stage0 + g * C::STAGE_BYTES + rl * 128;
+        const uint32_t a_row = astage0 + g * A_BYTES + rl * 128;
         float acc[C::DRAIN_COLS];
 #pragma unroll
         for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] = 0.0f;
 
         auto drain = [&](int u) {
             const int ab = u & 1;
-            mbar_wait_parked(minfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x2000u);    // the row scales are written
+            // the unit's sum is complete; its last MMAs waited for the minimums'
+            // stage, which the row scales were written before
             gtrace(a, tn, 8, u);
-            mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);    // the unit's sums are complete
+            mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);
             gtrace(a, tn, 9, u);
             tc_fence_after();
             const float sc = lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4);
@@ -427,25 +464,28 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         };
 
         for (int u = 0; u < units; u++) {
-            const int rs = u % RAW_STAGES, ms = u & 1;
-            mbar_wait_parked(rawfull0 + 8 * rs, (u / RAW_STAGES) & 1, a.status, 0x400u);
+            const int rs = u % C::RAW_STAGES, ms = u % C::MIN_STAGES;
+            mbar_wait_parked(rawfull0 + 8 * rs, (u / C::RAW_STAGES) & 1, a.status, 0x400u);
             const uint32_t raw_row = raw0 + rs * RAW_BYTES + rl * 144;
             const uint4 hdr = lds128(raw_row);
             Q4kBlock blk;
             load_q4k_block(hdr, raw_row, g, blk);
             gtrace(a, tn, 4, 4 * u + g);
-            mbar_wait_parked(empty0 + 8 * (g >> 1), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
+            mbar_wait_parked(empty0 + 8 * (g / C::HAND), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
             gtrace(a, tn, 5, 4 * u + g);
             store_q4k_block(blk, a_row, rl & 7);
             gtrace(a, tn, 6, 4 * u + g);
             fence_async_smem();          // the tensor core reads shared memory through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8 * (g >> 1));
+            if (lane == 0) mbar_arrive(full0 + 8 * (g / C::HAND));
             gtrace(a, tn, 7, 4 * u + g);
             if (g >= 2) {
                 // the minimums' A operand [K group][row][16 B]: groups (hi, hi, lo, lo) of the
                 // two f16 terms of -(32*dmin/s)*m_j; K block 2's warp writes m_0..m_3, K block 3's m_4..m_7
-                mbar_wait_parked(accfull0 + 8 * ms, ((u >> 1) & 1) ^ 1, a.status, 0x1000u);   // unit u-2 has read its minimums
+                if (u >= C::MIN_STAGES) {   // the unit that used this stage last has read its minimums
+                    const int uu = u - C::MIN_STAGES;
+                    mbar_wait_parked(accfull0 + 8 * (uu & 1), (uu >> 1) & 1, a.status, 0x1000u);
+                }
                 const Q4kFold f = q4k_fold(hdr.x);
                 const float dmin32 = 32.0f * h2f_hi(hdr.x);
                 const float sc = f.zero ? dmin32 : h2f_lo(hdr.x) * __uint_as_float((uint32_t)(127 + f.e) << 23);
@@ -599,7 +639,8 @@ int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, s
     const size_t ncols = n * (split ? 2 : 1);
     if (ncols <= 32) return launch_gemm<32>(ctx, w, operand, n, split, out, aux, epilogue);
     if (ncols <= 64) return launch_gemm<64>(ctx, w, operand, n, split, out, aux, epilogue);
-    return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
+    if (ncols <= 128 || getenv("DWIM_B200_GEMM_NARROW")) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
+    return launch_gemm<256>(ctx, w, operand, n, split, out, aux, epilogue);
 }
 
 void gemm_release(dwim_b200_ctx *) {}
