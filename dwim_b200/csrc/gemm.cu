@@ -1,37 +1,46 @@
 // The large-M product (prefill, long verify batches) for Q4_K: a dense
-// contraction on the 5th-generation tensor cores whose products are exact.
-// Replaces the reference's matmul_tile64_* kernels (matmul_tile.cu:94-258;
-// host side gpu/cuda/mod.rs:402-442).
+// contraction on the 5th-generation tensor cores whose weight products are
+// exact.  Replaces the reference's matmul_tile64_* kernels
+// (matmul_tile.cu:94-258; host side gpu/cuda/mod.rs:402-442).
 //
 // out[t][r] = sum_k W[r][k] x[t][k], with W[r][k] = d*(sc_j*q) - dmin*m_j
 // (d, dmin per 256-weight unit and row; sc_j, m_j per 32-weight sub-block).
 // The integer sc_j*q <= 945 is exact in f16, so for every unit u of K
-//     S1_u[r][t] = sum_k (sc*q)[r][k] * x[t][k]          16 MMAs of K=16
-//     S2_u[r][t] = sum_j m_j[r] * mean_j(x[t])            1 MMA of K=16
-// are sums of exact products in the tensor cores' fp32 accumulators, and
-//     out[r][t] = sum_u  d_u[r]*S1_u - 32*dmin_u[r]*S2_u
-// is applied by CUDA cores in fp32.  (The reference's tile kernel rounds every
-// dequantized weight to f16 instead, matmul_tile.cu:66-74: 2e-4 of rms error.)
-// An f32 activation travels as two f16 columns, value and rounding remainder,
-// which the epilogue adds up again; a bf16 one is exact in one column.
+//     S_u[r][t] = sum_k (sc*q)[r][k] * x[t][k]                    16 MMAs of K=16
+//               - sum_j (32*dmin/d * m_j)[r] * mean_j(x[t])         2 MMAs of K=16
+// is accumulated in the tensor cores' fp32 accumulators and
+//     out[r][t] = sum_u d_u[r] * S_u[r][t]
+// is applied by CUDA cores in fp32.  The first sum's products are exact; the
+// second's factors travel as f16 value + rounding remainder on both sides (22
+// bits each), and a power of two moves between d and the operands when dmin/d
+// is large (q4k_fold below).  The reference's tile kernel rounds every
+// dequantized weight to f16 instead (matmul_tile.cu:66-74): 2e-4 of rms error
+// against 5e-7 here.  An f32 activation travels as two f16 columns, value and
+// rounding remainder, which the epilogue adds up again; a bf16 one is exact in
+// one column.
 //
-// A CTA owns 128 weight rows (one TMEM lane each) by BN columns:
-//   warp 0        TMA producer: per unit the tile's packed blocks
-//                 ([128 rows][144 B]) into a raw ring and the means operand;
-//                 per 64 of K the activations' f16 tile ([BN][64], 128-byte
-//                 swizzle).
-//   warp 1        MMA issuer (one thread): tcgen05.mma M=128 N=BN K=16 into
-//                 S1 and S2 of the unit's accumulator buffer (two buffers, so
-//                 unit u+1 multiplies while unit u drains).
-//   warps 2-9     drain: tcgen05.ld S1 and S2, acc += d*S1 - 32*dmin*S2 in
-//                 registers (thread = weight row, 64 columns per warp at
-//                 BN=128); after the last unit the operator's epilogue
-//                 (store / add / SwiGLU) and the store, coalesced over rows.
-//   warps 10-17   dequantizers: thread (row, half) turns 32 nibbles into
-//                 sc*q halves (lop3 magic number + one HFMA2 per two weights)
-//                 and stores them into the stage's A tile in the K-major
-//                 128-byte-swizzled layout of the MMA's descriptor; once per
-//                 unit it writes the row's eight m_j and (d, 32*dmin).
+// A CTA owns 128 weight rows (one TMEM lane each) by BN columns (32..256):
+//   warp 0        activations' producer (one thread): per K block of 64 the f16
+//                 tile [BN][64] (TMA, 128-byte swizzle) into the B ring; per
+//                 unit the sub-block means' hi and lo parts.
+//   warp 1        MMA issuer: tcgen05.mma M=128 N=BN K=16 into the unit's
+//                 accumulator buffer (two buffers, so unit u+1 multiplies
+//                 while unit u drains).  The whole warp runs the loop and one
+//                 lane issues: that thread has about one instruction slot per
+//                 five cycles, and an N=128 MMA leaves it 64 cycles.
+//   warps 2-17    workers.  Warp w owns TMEM lane quadrant w % 4 (weight rows
+//                 32*(w % 4) + lane) and K block (w - 2) / 4 of every unit:
+//                 thread = row turns the block's 64 nibbles into sc*q halves
+//                 (lop3 magic number + one HFMA2 per two weights) and stores
+//                 them into the stage's A tile in the K-major 128-byte-
+//                 swizzled layout of the MMA's descriptor; then it drains a
+//                 quarter of the previous unit's columns: tcgen05.ld, acc +=
+//                 d*S in registers.  K blocks 2 and 3's warps also write the
+//                 unit's minimums operand and the row scales.  After the last
+//                 unit: the operator's epilogue (store / add / SwiGLU),
+//                 coalesced over rows.
+//   warp 18       packed weights' producer (one thread): per unit the tile's
+//                 blocks [128 rows][144 B] from HBM into the raw ring.
 // Every mbarrier wait is bounded (ptx.cuh); a kernel that gave up says so in
 // the context's status word.
 #include <cuda.h>
@@ -67,15 +76,18 @@ struct GemmArgs {
     unsigned long long *trace;   // debugging only: clock stamps of CTA (0,0), null in normal use
 };
 
-// Debug trace: (clock, tag, index) stamps, 400 slots per warp.
+// Debug trace, compiled in with -DDWIM_B200_GEMM_TRACE_BUILD only: (clock, tag,
+// index) stamps of CTA (0,0), 400 slots per warp.
 #define GEMM_TRACE_SLOTS 400
 __device__ __forceinline__ void gtrace(const GemmArgs &a, int &n, int tag, int idx) {
+#ifdef DWIM_B200_GEMM_TRACE_BUILD
     if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && n < GEMM_TRACE_SLOTS) {
         unsigned long long *p = a.trace + 2 * ((threadIdx.x >> 5) * GEMM_TRACE_SLOTS + n);
         p[0] = clock64();
         p[1] = ((unsigned long long)tag << 32) | (unsigned)idx;
         n++;
     }
+#endif
 }
 
 // Per tile width.  Up to 128 columns everything is double-buffered by units:
@@ -153,6 +165,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// d = a * b + d on two packed floats.
+__device__ __forceinline__ void ffma2(uint64_t &d, uint64_t a, uint64_t b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -246,8 +273,10 @@ __device__ __forceinline__ void load_q4k_block(const uint4 &hdr, uint32_t raw_ro
     b.mul[1] = spb; b.add[1] = hmul2(spb, H2_M64);
 }
 // Writes the row's 128 bytes of the stage's A tile (K-major, 128-byte swizzle:
-// 16-byte chunk c of row r sits at chunk c ^ (r & 7)).
-__device__ __forceinline__ void store_q4k_block(const Q4kBlock &b, uint32_t a_row, int row7) {
+// 16-byte chunk c of row r sits at chunk c ^ (r & 7)).  `a_row_sw` is the row's
+// address with (r & 7) << 4 or-ed in (rows are 128-byte aligned), so chunk c
+// is at a_row_sw ^ (c << 4).
+__device__ __forceinline__ void store_q4k_block(const Q4kBlock &b, uint32_t a_row_sw) {
 #pragma unroll
     for (int c = 0; c < 4; c++) {   // words 2c, 2c+1: weights 8c .. 8c+7 of either sub-block
         const uint32_t w0 = b.words[2 * c], w1 = b.words[2 * c + 1], s0 = w0 >> 8, s1 = w1 >> 8;
@@ -259,7 +288,7 @@ __device__ __forceinline__ void store_q4k_block(const Q4kBlock &b, uint32_t a_ro
             const uint32_t o1 = hfma2(lop3_and_or(s0, mask, magic), b.mul[h], b.add[h]);   // bytes 1, 3
             const uint32_t o2 = hfma2(lop3_and_or(w1, mask, magic), b.mul[h], b.add[h]);
             const uint32_t o3 = hfma2(lop3_and_or(s1, mask, magic), b.mul[h], b.add[h]);
-            sts128(a_row + (((4 * h + c) ^ row7) << 4), o0, o1, o2, o3);
+            sts128(a_row_sw ^ ((4 * h + c) << 4), o0, o1, o2, o3);
         }
     }
 }
@@ -387,6 +416,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 const uint32_t s1 = tm + ab * BN;
                 const uint32_t upar = (u0 >> 1) & 1;
                 mbar_wait_parked(accempty0 + 8 * ab, upar ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
+                gtrace(a, tn, 12, u);
 #pragma unroll
                 for (int h = 0; h < C::NHAND; h++) {
                     gtrace(a, tn, 2, KBLOCKS * u + h * C::HAND);
@@ -411,7 +441,9 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                     __syncwarp();
                 }
                 const int ms = u % C::MIN_STAGES;
+                gtrace(a, tn, 11, u);
                 mbar_wait_parked(minfull0 + 8 * ms, (u / C::MIN_STAGES) & 1, a.status, 0x200u);
+                gtrace(a, tn, 13, u);
                 tc_fence_after();
                 if (lane == 0) {
                     // the minimums: terms (hi, hi | lo, lo) against the means' (hi, lo) twice
@@ -435,10 +467,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const int rl = quad * 32 + lane;                // row within the tile = TMEM lane
         const bool drains = g < C::DRAINERS;
         const uint32_t drain_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * C::DRAIN_COLS;
-        const uint32_t a_row = astage0 + g * A_BYTES + rl * 128;
-        float acc[C::DRAIN_COLS];
+        const uint32_t a_row_sw = (astage0 + g * A_BYTES + rl * 128) | ((rl & 7) << 4);
+        uint64_t acc2[C::DRAIN_COLS / 2];   // the row's sums, two columns per packed pair
 #pragma unroll
-        for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] = 0.0f;
+        for (int j = 0; j < C::DRAIN_COLS / 2; j++) acc2[j] = 0ull;
 
         auto drain = [&](int u) {
             const int ab = u & 1;
@@ -448,14 +480,15 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);
             gtrace(a, tn, 9, u);
             tc_fence_after();
-            const float sc = lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4);
+            const uint32_t sc = __float_as_uint(lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4));
+            const uint64_t sc2 = pack2(sc, sc);
 #pragma unroll
             for (int c = 0; c < C::DRAIN_COLS / 16; c++) {
                 uint32_t v[16];
                 tmem_ld16(drain_addr + ab * BN + c * 16, v);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++) acc[c * 16 + j] = fmaf(sc, __uint_as_float(v[j]), acc[c * 16 + j]);
+                for (int j = 0; j < 8; j++) ffma2(acc2[c * 8 + j], sc2, pack2(v[2 * j], v[2 * j + 1]));
             }
             tc_fence_before();
             __syncwarp();
@@ -465,7 +498,9 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 
         for (int u = 0; u < units; u++) {
             const int rs = u % C::RAW_STAGES, ms = u % C::MIN_STAGES;
+            gtrace(a, tn, 14, u);
             mbar_wait_parked(rawfull0 + 8 * rs, (u / C::RAW_STAGES) & 1, a.status, 0x400u);
+            gtrace(a, tn, 15, u);
             const uint32_t raw_row = raw0 + rs * RAW_BYTES + rl * 144;
             const uint4 hdr = lds128(raw_row);
             Q4kBlock blk;
@@ -473,7 +508,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             gtrace(a, tn, 4, 4 * u + g);
             mbar_wait_parked(empty0 + 8 * (g / C::HAND), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
             gtrace(a, tn, 5, 4 * u + g);
-            store_q4k_block(blk, a_row, rl & 7);
+            store_q4k_block(blk, a_row_sw);
             gtrace(a, tn, 6, 4 * u + g);
             fence_async_smem();          // the tensor core reads shared memory through the async proxy
             __syncwarp();
@@ -507,6 +542,9 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
         if (drains) {
             drain(units - 1);
+            float acc[C::DRAIN_COLS];
+#pragma unroll
+            for (int j = 0; j < C::DRAIN_COLS / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
             const size_t row = (size_t)row0 + rl;
             if (row < a.rows) {
                 const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
@@ -592,6 +630,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
                         BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
         return rc;
     GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status, nullptr};
+#ifdef DWIM_B200_GEMM_TRACE_BUILD
     static unsigned long long *tbuf = nullptr;
     static int traced = 0;
     const char *tenv = getenv("DWIM_B200_GEMM_TRACE");
@@ -600,6 +639,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
         cudaMemsetAsync(tbuf, 0, 2 * 32 * GEMM_TRACE_SLOTS * sizeof(unsigned long long), ctx->stream);
         a.trace = tbuf;
     }
+#endif
     auto kern = gemm_q4k_kernel<BN>;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
@@ -609,6 +649,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     kern<<<grid, GEMM_THREADS, C::SMEM, ctx->stream>>>(tw, tx, tm, a);
     DWIM_LAUNCHED(ctx);
+#ifdef DWIM_B200_GEMM_TRACE_BUILD
     if (tenv && ++traced == atoi(tenv)) {
         static unsigned long long host[2 * 32 * GEMM_TRACE_SLOTS];
         cudaStreamSynchronize(ctx->stream);
@@ -622,6 +663,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
                 if (v) fprintf(stderr, "GTRACE %llu tag=%llu warp=%d idx=%llu\n", host[2 * (wv * GEMM_TRACE_SLOTS + i)] - t0, v >> 32, wv, v & 0xffffffffull);
             }
     }
+#endif
     return 0;
 }
 
