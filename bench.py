@@ -302,9 +302,10 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             if m == 1:
                 traffic, traffic_note = 50.47e6, "profiles/gemv_kernel_q4k_c1.md"
             elif gemm:
-                # captured at M=512 (76.6 MB); weights fixed, the rest in proportion to M
-                traffic = 50.1e6 + 26.5e6 * m / 512
-                traffic_note = "profiles/gemm_q4k_kernel_c2.md, captured at M=512 and scaled by M"
+                # captured at M=512; weights fixed, operand reads in proportion to M, output in full
+                traffic = 50.1e6 + (7.7e6 + 35.65e6) * m / 512
+                traffic_note = ("profiles/gemm_q4k_kernel_c2.md: reads captured at M=512 (weights once + 7.7 MB of "
+                                "operands per 512 tokens) scaled by M, plus the output in full")
         if gemm:
             flops = 2.0 * m * my_rows * cols
             achieved = flops / per_kernel / 1e12
