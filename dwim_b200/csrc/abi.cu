@@ -384,7 +384,9 @@ int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, co
 static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size_t cols, int split) {
     if (x->shadow_kind == kind && x->shadow_cols == cols && x->shadow_split == split) return 0;
     size_t n = x->len / cols;
-    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n * (split ? 2 : 1)) : panel_bytes(cols, (int)n * (split ? 2 : 1));
+    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n * (split ? 2 : 1))
+                  : kind == SHADOW_PANEL_I8 ? panel_i8_bytes(cols, n)
+                                            : panel_bytes(cols, (int)n * (split ? 2 : 1));
     if (need > x->shadow_cap) {
         if (x->shadow) {
             DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -396,8 +398,9 @@ static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size
         x->shadow_cap = need;
     }
     x->shadow_kind = SHADOW_NONE;
-    int rc = kind == SHADOW_GEMM ? build_gemm_operand(ctx, x->data, n, cols, split, (__half *)x->shadow)
-                                     : build_panels(ctx, x->data, n, cols, kind, split, (__half *)x->shadow);
+    int rc = kind == SHADOW_GEMM       ? build_gemm_operand(ctx, x->data, n, cols, split, (__half *)x->shadow)
+             : kind == SHADOW_PANEL_I8 ? build_panels_i8(ctx, x->data, n, cols, (uint8_t *)x->shadow)
+                                       : build_panels(ctx, x->data, n, cols, kind, split, (__half *)x->shadow);
     if (rc) return rc;
     x->shadow_kind = kind;
     x->shadow_cols = cols;
@@ -421,6 +424,12 @@ static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b2
         int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
         if (rc) return rc;
         return gemm_large(ctx, v, (const __half *)x->shadow, n, split, out, aux, epilogue);
+    }
+    // one or two tokens of Q4_K: integer nibbles against the activations' int8 digit planes
+    if (gemv_takes_i8(v, n)) {
+        int rc = ensure_shadow(ctx, x, SHADOW_PANEL_I8, v.cols, 0);
+        if (rc) return rc;
+        return gemv_small_i8(ctx, v, (const uint8_t *)x->shadow, (int)n, out, aux, epilogue);
     }
     // bf16 activations are exact in one f16 column; f32 ones travel as two.
     int split = x->bf16_exact ? 0 : 1;

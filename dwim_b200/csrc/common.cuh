@@ -16,7 +16,8 @@ enum ShadowKind : int {
     SHADOW_NONE = 0,
     SHADOW_PANEL_NATURAL,   // small-M panels, k in order            (Q8_0, Q6_K)
     SHADOW_PANEL_Q4K,       // small-M panels, k permuted + swizzled (Q4_K)
-    SHADOW_GEMM             // f16 rows + sub-block means, for the tensor-core GEMM
+    SHADOW_GEMM,            // f16 rows + sub-block means, for the tensor-core GEMM
+    SHADOW_PANEL_I8         // int8 digit planes per 256-wide unit, for the one- and two-token Q4_K kernel
 };
 
 struct dwim_b200_buffer {
@@ -93,6 +94,15 @@ int quantize_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const
 constexpr int PANEL_STRIDE = 272;
 size_t panel_bytes(size_t cols, int ncols);
 int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels);
+// int8 panels: per unit of 256 activations one blob of i8_unit_bytes(nc), nc = 4 * tokens columns
+// (column = 4*token + plane):
+//   [sub-block j (8)][column][32 digits]        256*nc B
+//   [column][a_0..a_7 | b_0..b_7]                16*nc B   the digits' sums per sub-block, 128*a + b
+//   [column] float                                4*nc B   what one unit of the plane's digit is worth
+constexpr int I8_MAX_TOKENS = 2;
+constexpr int i8_unit_bytes(int nc) { return 276 * nc; }
+size_t panel_i8_bytes(size_t cols, size_t n);
+int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, uint8_t *panels);
 size_t gemm_operand_bytes(size_t cols, size_t ncols);
 int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out);
 
@@ -100,6 +110,9 @@ int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols
 enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 // One launch: tokens [t0, t0 + n_tokens) of a panel array holding ncols_total
 // columns, the launch's first at col0.  aux is the `up` product for EPI_SWIGLU.
+bool gemv_takes_i8(const WeightView &w, size_t n);
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
+                  int epilogue);
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
                size_t t0, int split, float *out, const float *aux, int epilogue);
 int gemv_max_tokens(int split);

@@ -41,6 +41,8 @@ struct GemvArgs {
     WeightView w;
     const uint8_t *panels;   // [units][ncols_total][PANEL_BYTES]
     int ncols_total;         // columns in the panel array
+    int xunit;               // bytes of one unit's panels for this launch
+    int xsrc_stride;         // bytes between units in the panel array
     int col0;                // first column of this launch
     int ncols;               // columns of this launch (<= 8*NT)
     int split;               // 1: columns are (hi, lo) pairs of a token
@@ -82,8 +84,13 @@ constexpr uint32_t H2_M1024 = 0xE400E400u;  // half2(-1024, -1024)
 constexpr uint32_t H2_M64 = 0xD400D400u;    // half2(-64, -64)
 constexpr uint32_t H2_SIXTEENTH = 0x2C002C00u;  // half2(1/16, 1/16)
 
+// Q4_K through the int8 tensor-core path (one or two tokens): the same blocks,
+// another activation operand and unit routine.
+constexpr int Q4K_I8 = 1012;
+
 template <int FMT> struct Traits;
 template <> struct Traits<Q4_K> { static constexpr int UNIT_Q = 144; };
+template <> struct Traits<Q4K_I8> { static constexpr int UNIT_Q = 144; };
 template <> struct Traits<Q6_K> { static constexpr int UNIT_Q = 208; };
 template <> struct Traits<Q8_0> { static constexpr int UNIT_Q = 256; };
 
@@ -92,6 +99,7 @@ struct Lane {
     int g, c;                // row within the 8-row group; k-quarter
     uint32_t row_a, row_b;   // shared addresses of rows g and g+8 (quant region)
     uint32_t srow_a, srow_b; // shared addresses of the rows' scales
+    uint32_t xbase;          // shared address of the launch's panels (unit 0 of the stage, or of the row when resident)
     uint32_t x[2];           // shared address of this lane's column panel, per column group
     bool xv[2];              // whether that column exists
 };
@@ -191,6 +199,84 @@ __device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int xu, int ncol
         acc[nt][2] += sb.d * (c1[nt][2] + c1h[nt][2]) - sb.dmin32 * c2[nt][2];
         acc[nt][3] += sb.d * (c1[nt][3] + c1h[nt][3]) - sb.dmin32 * c2[nt][3];
     }
+}
+
+// ---------------------------------------------------------------------------
+// Q4_K, one or two tokens, int8 tensor-core path
+// ---------------------------------------------------------------------------
+// The nibbles stay integers: four of them per AND, multiplied on the tensor
+// cores (mma.sync m16n8k32 u8 x s8 -> s32) with the activations' signed
+// base-256 digit planes as columns (prologue.cu: column = 4*token + plane).
+// One MMA covers one 32-weight sub-block of 16 rows; its sums are weighted by
+// the sub-block's 6-bit scale with integer multiply-adds, so a whole unit is an
+// exact integer per (row, column), which d and the plane's worth then scale.
+// High nibbles are masked in place (16*q: no shift) and their sums divided by
+// 16 once per unit.  The minimums use the digits' per-sub-block sums (dp4a).
+// About half the instructions of the f16 routine above for the same weights.
+__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // a unsigned bytes, b signed bytes
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ float2 lds64f2(uint32_t a) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+    return v;
+}
+
+// Lane (g, c) owns bytes [8c, 8c+8) of each 32-byte group of its two rows: MMA
+// k-slots 4c..4c+3 and 16+4c..16+4c+3, matched by the same eight digits of the
+// lane's column.  acc: (row a, col 2c), (row a, col 2c+1), (row b, ..), (row b, ..).
+__device__ __forceinline__ void unit_q4k_i8(const Lane &L, int ul, int xu, int nc, float (&acc)[4]) {
+    const uint32_t ba = L.row_a + ul * 144, bb = L.row_b + ul * 144;
+    const uint4 ha = lds128(ba), hb = lds128(bb);
+    const uint32_t blob = L.xbase + xu * i8_unit_bytes(nc);
+    const bool bcol = L.g < nc, ccol = 2 * L.c < nc;   // this lane's B column / accumulator columns exist
+    // the 6-bit scales and minimums as bytes: entries 0..3 and 4..7
+    const uint32_t sa[2] = {ha.y & 0x3f3f3f3fu, (ha.w & 0x0f0f0f0fu) | ((ha.y >> 2) & 0x30303030u)};
+    const uint32_t sb[2] = {hb.y & 0x3f3f3f3fu, (hb.w & 0x0f0f0f0fu) | ((hb.y >> 2) & 0x30303030u)};
+    int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int G = 0; G < 4; G++) {   // group G: low nibbles = sub-block 2G, high nibbles = 2G+1
+        const uint2 wa = lds64(ba + 16 + 32 * G + 8 * L.c), wb = lds64(bb + 16 + 32 * G + 8 * L.c);
+        uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
+        if (bcol) {
+            x0 = lds64(blob + ((2 * G) * nc + L.g) * 32 + 8 * L.c);
+            x1 = lds64(blob + ((2 * G + 1) * nc + L.g) * 32 + 8 * L.c);
+        }
+        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        imma_u8s8(c0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, x0.x, x0.y);
+        imma_u8s8(c1, wa.x & 0xf0f0f0f0u, wb.x & 0xf0f0f0f0u, wa.y & 0xf0f0f0f0u, wb.y & 0xf0f0f0f0u, x1.x, x1.y);
+        const int sh = 16 * (G & 1);
+        const int s0a = (sa[G >> 1] >> sh) & 0xff, s1a = (sa[G >> 1] >> (sh + 8)) & 0xff;
+        const int s0b = (sb[G >> 1] >> sh) & 0xff, s1b = (sb[G >> 1] >> (sh + 8)) & 0xff;
+        ilo[0] += s0a * c0[0]; ilo[1] += s0a * c0[1]; ilo[2] += s0b * c0[2]; ilo[3] += s0b * c0[3];
+        ihi[0] += s1a * c1[0]; ihi[1] += s1a * c1[1]; ihi[2] += s1b * c1[2]; ihi[3] += s1b * c1[3];
+    }
+    // minimums: sum_j m_j * (128*a_j + b_j) per column
+    const uint32_t ma[2] = {ha.z & 0x3f3f3f3fu, ((ha.w >> 4) & 0x0f0f0f0fu) | ((ha.z >> 2) & 0x30303030u)};
+    const uint32_t mb[2] = {hb.z & 0x3f3f3f3fu, ((hb.w >> 4) & 0x0f0f0f0fu) | ((hb.z >> 2) & 0x30303030u)};
+    uint4 t0 = make_uint4(0, 0, 0, 0), t1 = t0;
+    float2 worth = make_float2(0.0f, 0.0f);
+    if (ccol) {
+        t0 = lds128(blob + 256 * nc + (2 * L.c) * 16);
+        t1 = lds128(blob + 256 * nc + (2 * L.c + 1) * 16);
+        worth = lds64f2(blob + 272 * nc + 8 * L.c);
+    }
+    const int m0 = (dp4a_us(ma[1], t0.y, dp4a_us(ma[0], t0.x, 0)) << 7) + dp4a_us(ma[1], t0.w, dp4a_us(ma[0], t0.z, 0));
+    const int m1 = (dp4a_us(ma[1], t1.y, dp4a_us(ma[0], t1.x, 0)) << 7) + dp4a_us(ma[1], t1.w, dp4a_us(ma[0], t1.z, 0));
+    const int m2 = (dp4a_us(mb[1], t0.y, dp4a_us(mb[0], t0.x, 0)) << 7) + dp4a_us(mb[1], t0.w, dp4a_us(mb[0], t0.z, 0));
+    const int m3 = (dp4a_us(mb[1], t1.y, dp4a_us(mb[0], t1.x, 0)) << 7) + dp4a_us(mb[1], t1.w, dp4a_us(mb[0], t1.z, 0));
+    const float da = h2f_lo(ha.x), dma = h2f_hi(ha.x), db = h2f_lo(hb.x), dmb = h2f_hi(hb.x);
+    acc[0] += worth.x * (da * (float)(ilo[0] + (ihi[0] >> 4)) - dma * (float)m0);
+    acc[1] += worth.y * (da * (float)(ilo[1] + (ihi[1] >> 4)) - dma * (float)m1);
+    acc[2] += worth.x * (db * (float)(ilo[2] + (ihi[2] >> 4)) - dmb * (float)m2);
+    acc[3] += worth.y * (db * (float)(ilo[3] + (ihi[3] >> 4)) - dmb * (float)m3);
 }
 
 // ---------------------------------------------------------------------------
@@ -330,6 +416,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
     constexpr int NW = RT * KS;
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
+    constexpr bool HAS_SCALES = FMT == Q6_K || FMT == Q8_0;   // scales kept apart from the quants
     constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NT * 4 * 32 : 0;
 
     extern __shared__ __align__(128) uint8_t smem[];
@@ -361,7 +448,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         if (a.x_resident && lane == 0 && (int)blockIdx.x < a.n_tiles) {
             // the launch's panels are one contiguous run: [units][ncols][PANEL_BYTES]
             mbar_expect_tx(xbar, a.xres_bytes);
-            bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);
+            bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);   // col0 = 0 for int8 panels
         }
         for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
             const size_t row0 = (size_t)tile * R;
@@ -382,11 +469,11 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                     size_t s_end = min((size_t)pad8(u0 + kcc), a.w.srow);
                     sbytes = (uint32_t)(s_end - s_first) * 2;
                 }
-                const uint32_t xbytes = a.x_resident ? 0u : (uint32_t)a.ncols * PANEL_BYTES;
+                const uint32_t xbytes = a.x_resident ? 0u : (uint32_t)a.xunit;
                 const uint32_t bar = full0 + 8 * s;
                 if (a.whole_rows) {
                     if (lane == 0)
-                        mbar_expect_tx(bar, nrows * (uint32_t)(a.w.qpitch + (FMT != Q4_K ? a.w.srow * 2 : 0)) + kcc * xbytes);
+                        mbar_expect_tx(bar, nrows * (uint32_t)(a.w.qpitch + (HAS_SCALES ? a.w.srow * 2 : 0)) + kcc * xbytes);
                 } else if (lane == 0) {
                     mbar_expect_tx(bar, nrows * (qbytes + sbytes) + kcc * xbytes);
                 }
@@ -395,18 +482,18 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                 if (a.whole_rows) {
                     // consecutive rows are one contiguous run (rows sit qpitch apart, and so do the stage's)
                     if (lane == 0) bulk_g2s(st, a.w.quants + row0 * a.w.qpitch, nrows * (uint32_t)a.w.qpitch, bar);
-                    if (FMT != Q4_K && lane == 1)
+                    if (HAS_SCALES && lane == 1)
                         bulk_g2s(st + a.s_off, a.w.scales + row0 * a.w.srow, nrows * (uint32_t)a.w.srow * 2, bar);
                 } else {
                     for (int r = lane; r < nrows; r += 32) {
                         bulk_g2s(st + r * a.q_stride, a.w.quants + (row0 + r) * a.w.qpitch + (size_t)u0 * UNIT_Q, qbytes, bar);
-                        if (FMT != Q4_K)
+                        if (HAS_SCALES)
                             bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
                     }
                 }
                 for (int u = lane; u < kcc && !a.x_resident; u += 32)
                     bulk_g2s(st + a.x_off + u * xbytes,
-                             a.panels + ((size_t)(u0 + u) * a.ncols_total + a.col0) * PANEL_BYTES, xbytes, bar);
+                             a.panels + (size_t)(u0 + u) * a.xsrc_stride + (size_t)a.col0 * PANEL_BYTES, xbytes, bar);
                 trace(a, tn, 3, it);
             }
         }
@@ -429,6 +516,11 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
     Lane L;
     L.g = lane >> 2;
     L.c = lane & 3;
+    // The int8 routine reads 8 bytes per lane and row: with rows an odd number
+    // of 16-byte steps apart, the four rows of a half-warp must be two steps
+    // apart to cover all banks, so lanes g = 0..3 take rows 0, 2, 4, 6 of the
+    // eight and g = 4..7 rows 1, 3, 5, 7.
+    const int grow = FMT == Q4K_I8 ? ((L.g & 3) * 2 + (L.g >> 2)) : L.g;
 #pragma unroll
     for (int nt = 0; nt < 2; nt++) L.xv[nt] = nt < NT && (nt * 8 + L.g) < a.ncols;
     uint32_t xo[4];
@@ -453,18 +545,19 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
             trace(a, tn, 5, it);
             const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
             const uint32_t st = stage0 + s * a.stage_bytes;
-            L.row_a = st + (rt * 16 + L.g) * a.q_stride;
+            L.row_a = st + (rt * 16 + grow) * a.q_stride;
             L.row_b = L.row_a + 8 * a.q_stride;
-            L.srow_a = st + a.s_off + (rt * 16 + L.g) * a.s_stride;
+            L.srow_a = st + a.s_off + (rt * 16 + grow) * a.s_stride;
             L.srow_b = L.srow_a + 8 * a.s_stride;
+            L.xbase = a.x_resident ? smem_u32(xres) : st + a.x_off;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                L.x[nt] = (a.x_resident ? smem_u32(xres) : st + a.x_off) + (nt * 8 + L.g) * PANEL_BYTES;
+            for (int nt = 0; nt < NT; nt++) L.x[nt] = L.xbase + (nt * 8 + L.g) * PANEL_BYTES;
             const int xu0 = a.x_resident ? u0 : 0;
             // units are dealt to the K-split warps round-robin over the whole row,
             // so every warp gets the same number whatever the chunking
             for (int ul = (ks + KS - u0 % KS) % KS; ul < kcc; ul += KS) {
-                if (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
+                if (FMT == Q4K_I8) unit_q4k_i8(L, ul, xu0 + ul, a.ncols, acc[0]);
+                else if (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
                 else if (FMT == Q8_0) unit_q8_0<NT>(L, ul, xu0 + ul, a.ncols, acc);
                 else unit_q6k<NT>(L, ul, xu0 + ul, a.ncols, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc);
             }
@@ -495,7 +588,19 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 
         trace(a, tn, 7, it);
         // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
-        const size_t r0 = (size_t)tile * R + rt * 16 + L.g, r1 = r0 + 8;
+        const size_t r0 = (size_t)tile * R + rt * 16 + grow, r1 = r0 + 8;
+        if (FMT == Q4K_I8) {
+            // a token's four planes are columns 4t..4t+3: lanes c = 2t, 2t+1
+            float va = acc[0][0] + acc[0][1], vb = acc[0][2] + acc[0][3];
+            va += __shfl_xor_sync(0xffffffffu, va, 1);
+            vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+            const int t = L.c >> 1;
+            if (!(L.c & 1) && t < a.n_tokens) {
+                emit(a, t, r0, va);
+                emit(a, t, r1, vb);
+            }
+            continue;
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             if (a.split) {
@@ -539,7 +644,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     const int fixed = 256 + RED_BYTES;
     // Panels stay resident when the launch covers the whole panel array (one
     // contiguous run) and it is small next to the ring.
-    const int xall = a.units * a.ncols * PANEL_BYTES;
+    const int xall = a.units * a.xunit;
     a.x_resident = a.col0 == 0 && a.ncols == a.ncols_total && xall <= 80 * 1024;
     a.xres_bytes = a.x_resident ? xall : 0;
     // K per stage.  Whole rows when two stages of them fit: the tile is then one
@@ -550,7 +655,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     const int budget = SMEM_MAX - fixed - a.xres_bytes;
     const int srow_bytes = (int)a.w.srow * 2;
     auto whole_stage = [&]() {
-        return (int)((R * (a.w.qpitch + srow_bytes) + (a.x_resident ? 0 : a.units * a.ncols * PANEL_BYTES) + 127) & ~127);
+        return (int)((R * (a.w.qpitch + srow_bytes) + (a.x_resident ? 0 : a.units * a.xunit) + 127) & ~127);
     };
     a.whole_rows = tune().kc <= 0 && 2 * whole_stage() <= budget;
     if (a.whole_rows) {
@@ -572,7 +677,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
             a.s_off = R * qs;
             a.s_stride = FMT == Q8_0 ? 16 * a.kc + 16 : FMT == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
             a.x_off = a.s_off + R * a.s_stride;
-            a.stage_bytes = (a.x_off + (a.x_resident ? 0 : a.kc * a.ncols * PANEL_BYTES) + 127) & ~127;
+            a.stage_bytes = (a.x_off + (a.x_resident ? 0 : a.kc * a.xunit) + 127) & ~127;
             a.stages = budget / a.stage_bytes;
             if (a.stages >= 2 || a.kc == 1 || tune().kc > 0) break;
         }
@@ -627,7 +732,7 @@ static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
     // when there are rows enough for two tiles per SM, the wider formats with
     // 16-row tiles (their stages are larger); eight K-split warps throughout.
     const size_t tiles32 = (a.w.rows + 31) / 32;
-    int rt = FMT == Q4_K && tiles32 >= (size_t)2 * ctx->sm_count ? 2 : 1;
+    int rt = (FMT == Q4_K || FMT == Q4K_I8) && tiles32 >= (size_t)2 * ctx->sm_count ? 2 : 1;
     int ks = 8;
     if (tune().rt > 0) rt = tune().rt;
     if (tune().ks > 0) ks = tune().ks;
@@ -658,6 +763,8 @@ int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, in
     a.aux = aux;
     a.epi = epilogue;
     a.units = (int)((w.cols + 255) / 256);
+    a.xunit = a.ncols * PANEL_BYTES;
+    a.xsrc_stride = ncols_total * PANEL_BYTES;
     a.status = ctx->status;
     if (a.ncols > 16) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: %d columns", a.ncols);
     const bool two = a.ncols > 8;
@@ -667,6 +774,37 @@ int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, in
     case Q8_0: return two ? launch_shape<Q8_0, 2>(ctx, a) : launch_shape<Q8_0, 1>(ctx, a);
     default: return fail(ctx, DWIM_B200_EFORMAT, "unknown weight format %d", w.fmt);
     }
+}
+
+// Whether a product of n tokens takes the int8 routine.  DWIM_B200_GEMV_F16 in
+// the environment keeps the f16 routine, for comparison.
+bool gemv_takes_i8(const WeightView &w, size_t n) {
+    static const bool off = getenv("DWIM_B200_GEMV_F16") != nullptr;
+    return !off && w.fmt == Q4_K && n >= 1 && n <= I8_MAX_TOKENS && w.cols % 256 == 0;
+}
+
+// One or two tokens of a Q4_K matrix through the int8 routine; `panels` from
+// build_panels_i8.
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
+                  int epilogue) {
+    if (w.rows == 0 || n_tokens == 0) return 0;
+    if (w.fmt != Q4_K || n_tokens > I8_MAX_TOKENS || w.cols % 256 != 0)
+        return fail(ctx, DWIM_B200_EINVAL, "int8 small-M kernel: format %d, %d tokens", w.fmt, n_tokens);
+    GemvArgs a{};
+    a.w = w;
+    a.panels = panels;
+    a.ncols_total = a.ncols = 4 * n_tokens;
+    a.col0 = 0;
+    a.split = 0;
+    a.n_tokens = n_tokens;
+    a.t0 = 0;
+    a.out = out;
+    a.aux = aux;
+    a.epi = epilogue;
+    a.units = (int)(w.cols / 256);
+    a.xunit = a.xsrc_stride = i8_unit_bytes(a.ncols);
+    a.status = ctx->status;
+    return launch_shape<Q4K_I8, 1>(ctx, a);
 }
 
 }  // namespace dwim

@@ -102,6 +102,70 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
 //                             f16 values, as a hi half (entries 0-7) and the
 //                             remainder (entries 8-15): the operand the
 //                             sub-block minimums are multiplied with
+// ---- int8 digit planes (one- and two-token Q4_K kernel) --------------------------------
+// A unit's 256 activations of a token share one exponent e (|x| < 2^e for all of
+// them) and become 31-bit fixed point, Y = rint(x * 2^(30-e)), written as four
+// signed base-256 digits: Y = d0*2^24 + d1*2^16 + d2*2^8 + d3, each in
+// [-128, 127].  An activation within 2^-6 of the unit's largest is exact; a
+// smaller one is rounded at 2^-31 of the largest.  Plane p of token t is column
+// 4t + p of the int8 MMA; a unit of its digit is worth 2^(e-6-8p).
+// One block per (unit, token slot); warp j owns sub-block j.
+size_t panel_i8_bytes(size_t cols, size_t n) { return ((cols + 255) / 256) * (size_t)i8_unit_bytes(4 * (int)n); }
+
+__global__ void __launch_bounds__(256) panel_i8_kernel(const float *__restrict__ x, size_t cols, int n, uint8_t *__restrict__ panels) {
+    const int u = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, j = tid >> 5, lane = tid & 31;
+    const int nc = 4 * n;
+    uint8_t *blob = panels + (size_t)u * i8_unit_bytes(nc);
+    const size_t k = (size_t)u * 256 + tid;
+    const float v = k < cols ? x[(size_t)t * cols + k] : 0.0f;
+    // the unit's largest magnitude
+    __shared__ float wmax[8];
+    float m = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) wmax[j] = m;
+    __syncthreads();
+    m = wmax[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) m = fmaxf(m, wmax[i]);
+    // |x| < 2^e; floored so that the planes' worths stay normal floats
+    int e = m > 0.0f ? (int)((__float_as_uint(m) >> 23) & 0xffu) - 126 : -90;
+    if (e < -90) e = -90;
+    const float up = __uint_as_float((uint32_t)(127 + 15 - (e >> 1)) << 23) * __uint_as_float((uint32_t)(127 + 15 - (e - (e >> 1))) << 23);
+    int y = __float2int_rn(v * up);   // v * 2^(30-e), |y| <= 2^30
+    int d[4];
+#pragma unroll
+    for (int p = 3; p > 0; p--) {
+        d[p] = ((y + 128) & 255) - 128;
+        y = (y - d[p]) >> 8;
+    }
+    d[0] = y;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const int col = 4 * t + p;
+        blob[(j * nc + col) * 32 + lane] = (uint8_t)(int8_t)d[p];
+        int s = d[p];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) {
+            const int b = ((s + 64) & 127) - 64, a = (s - b) >> 7;   // s = 128*a + b
+            blob[256 * nc + col * 16 + j] = (uint8_t)(int8_t)a;
+            blob[256 * nc + col * 16 + 8 + j] = (uint8_t)(int8_t)b;
+        }
+        if (tid == 0)
+            reinterpret_cast<float *>(blob + 272 * nc)[col] = __uint_as_float((uint32_t)(127 + e - 6 - 8 * p) << 23);
+    }
+}
+
+int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, uint8_t *panels) {
+    if (n == 0 || cols == 0) return 0;
+    if (n > I8_MAX_TOKENS) return fail(ctx, DWIM_B200_EINVAL, "int8 panels take at most %d tokens, not %zu", I8_MAX_TOKENS, n);
+    dim3 grid((unsigned)((cols + 255) / 256), (unsigned)n);
+    panel_i8_kernel<<<grid, 256, 0, ctx->stream>>>(x, cols, (int)n, panels);
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}
+
 size_t gemm_operand_bytes(size_t cols, size_t ncols) {
     return ncols * cols * sizeof(__half) + ncols * (cols / 256) * 16 * sizeof(__half);
 }

@@ -51,6 +51,20 @@ extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwi
     if (n == 0 || v.rows == 0) return 0;
     if (!out || !x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: null pointer");
     if (out == x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: output aliases input");
+    if (gemv_takes_i8(v, n)) {
+        // one or two tokens of Q4_K: the int8 digit-plane operand, as dwim_b200_matmul
+        const size_t need = panel_i8_bytes(v.cols, n);
+        if (need > STATIC_SCRATCH_BYTES)
+            return fail(ctx, DWIM_B200_EINVAL,
+                        "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
+                        v.cols, need, STATIC_SCRATCH_BYTES);
+        void *scratch = nullptr;
+        int rc = scratch_address(ctx, &scratch);
+        if (rc) return rc;
+        rc = build_panels_i8(ctx, x, n, v.cols, (uint8_t *)scratch);
+        if (rc) return rc;
+        return gemv_small_i8(ctx, v, (const uint8_t *)scratch, (int)n, out, nullptr, EPI_STORE);
+    }
     const int split = 1;                                  // f32 activations: value + remainder columns
     if (n > (size_t)gemv_max_tokens(split))
         return fail(ctx, DWIM_B200_EINVAL, "matmul_static: %zu tokens, at most %d", n, gemv_max_tokens(split));
