@@ -1,5 +1,6 @@
 // Handles behind the C ABI and the helpers every translation unit shares.
 #pragma once
+#include <stdlib.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdint.h>
@@ -72,6 +73,26 @@ inline int fail(dwim_b200_ctx *ctx, int code, const char *fmt, ...) {
             return dwim::fail(ctx, e_ == cudaErrorMemoryAllocation ? DWIM_B200_ENOMEM : DWIM_B200_ECUDA, \
                               "%s: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
     } while (0)
+
+// Launches `kern` so that it may begin while the kernel ahead of it in the
+// stream still runs (programmatic dependent launch).  Only for kernels that
+// call griddep_wait() (ptx.cuh) before they touch anything an earlier kernel
+// may read or write.  DWIM_B200_NO_PDL in the environment turns it off.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    static const bool pdl = getenv("DWIM_B200_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 
 #define DWIM_LAUNCHED(ctx)                                                                     \
     do {                                                                                       \

@@ -43,6 +43,7 @@ struct GemvArgs {
     int ncols_total;         // columns in the panel array
     int xunit;               // bytes of one unit's panels for this launch
     int xsrc_stride;         // bytes between units in the panel array
+    int ctas_per_sm;         // 0: one
     int col0;                // first column of this launch
     int ncols;               // columns of this launch (<= 8*NT)
     int split;               // 1: columns are (hi, lo) pairs of a token
@@ -437,6 +438,10 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // The next launch in the stream may start as soon as SMs free up: what it
+    // does before its own griddep_wait() (streaming its weights) depends on
+    // nothing this kernel writes.
+    griddep_launch();
 
     const int n_chunks = (a.units + a.kc - 1) / a.kc;
     const uint32_t stage0 = smem_u32(stages);
@@ -444,12 +449,15 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 
     if (warp == NW) {
         // ------------------------------ producer ------------------------------
+        // Weights are written by uploads only, which are ordinary launches long
+        // complete: their copies may start before the kernel ahead has finished.
+        // The panels come from the prologue that may be that very kernel.
+        // So: the first ring-full of weight stages is requested at once, then the
+        // warp waits for the kernel ahead and requests the panels.
         uint32_t it = 0;
-        if (a.x_resident && lane == 0 && (int)blockIdx.x < a.n_tiles) {
-            // the launch's panels are one contiguous run: [units][ncols][PANEL_BYTES]
-            mbar_expect_tx(xbar, a.xres_bytes);
-            bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);   // col0 = 0 for int8 panels
-        }
+        const int my_tiles = (int)blockIdx.x < a.n_tiles ? (a.n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const uint32_t ahead = (uint32_t)min(S, my_tiles * n_chunks);   // stages that need no free slot
+        bool waited = false;
         for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
             const size_t row0 = (size_t)tile * R;
             const int nrows = (int)min((size_t)R, a.w.rows - row0);
@@ -491,6 +499,15 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                             bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
                     }
                 }
+                if (!waited && (!a.x_resident || it + 1 == ahead)) {
+                    griddep_wait();
+                    waited = true;
+                    if (a.x_resident && lane == 0) {
+                        // the launch's panels are one contiguous run: [units][ncols][PANEL_BYTES]; col0 = 0 for int8 panels
+                        mbar_expect_tx(xbar, a.xres_bytes);
+                        bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);
+                    }
+                }
                 for (int u = lane; u < kcc && !a.x_resident; u += 32)
                     bulk_g2s(st + a.x_off + u * xbytes,
                              a.panels + (size_t)(u0 + u) * a.xsrc_stride + (size_t)a.col0 * PANEL_BYTES, xbytes, bar);
@@ -529,6 +546,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 
     uint32_t it = 0;
     int tile_parity = 0;
+    bool out_ready = false;
     if (a.x_resident && (int)blockIdx.x < a.n_tiles) mbar_wait(xbar, 0, a.status, 0x4u);
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, tile_parity ^= 1) {
         float acc[NT][4];
@@ -587,6 +605,10 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         }
 
         trace(a, tn, 7, it);
+        if (!out_ready) {   // the kernel ahead may still be writing `out` or `aux`
+            griddep_wait();
+            out_ready = true;
+        }
         // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
         const size_t r0 = (size_t)tile * R + rt * 16 + grow, r1 = r0 + 8;
         if (FMT == Q4K_I8) {
@@ -623,13 +645,13 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 // ---------------------------------------------------------------------------
 int gemv_max_tokens(int split) { return split ? 8 : 16; }
 
-// DWIM_B200_GEMV_TUNE="rt,ks,kc,stages" overrides the launch shape (0 = keep
-// the default), for sweeps on the device.  Read once.
-struct Tune { int rt = 0, ks = 0, kc = 0, stages = 0; };
+// DWIM_B200_GEMV_TUNE="rt,ks,kc,stages,ctas_per_sm" overrides the launch shape
+// (0 = keep the default), for sweeps on the device.  Read once.
+struct Tune { int rt = 0, ks = 0, kc = 0, stages = 0, cps = 0; };
 static const Tune &tune() {
     static Tune t = [] {
         Tune v;
-        if (const char *e = getenv("DWIM_B200_GEMV_TUNE")) sscanf(e, "%d,%d,%d,%d", &v.rt, &v.ks, &v.kc, &v.stages);
+        if (const char *e = getenv("DWIM_B200_GEMV_TUNE")) sscanf(e, "%d,%d,%d,%d,%d", &v.rt, &v.ks, &v.kc, &v.stages, &v.cps);
         return v;
     }();
     return t;
@@ -640,7 +662,10 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
     constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NT * 4 * 32 * 4 + 127) & ~127) : 0;
-    constexpr int SMEM_MAX = 227 * 1024;
+    constexpr int SMEM_LIMIT = 227 * 1024;
+    // CTAs per SM: two smaller CTAs overlap one's fill and drain with the other's steady state
+    const int cps = tune().cps > 0 ? tune().cps : a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
+    const int SMEM_MAX = cps > 1 ? (228 * 1024) / cps - 1024 : SMEM_LIMIT;
     const int fixed = 256 + RED_BYTES;
     // Panels stay resident when the launch covers the whole panel array (one
     // contiguous run) and it is small next to the ring.
@@ -690,10 +715,10 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     auto kern = gemv_kernel<FMT, NT, RT, KS>;
     static bool configured[64] = {false};   // per instantiation, per device
     if (!configured[ctx->device & 63]) {
-        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_MAX));
+        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
         configured[ctx->device & 63] = true;
     }
-    int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
+    int grid = a.n_tiles < cps * ctx->sm_count ? a.n_tiles : cps * ctx->sm_count;
     static unsigned long long *tbuf = nullptr;
     static int traced = 0;
     const bool tracing = getenv("DWIM_B200_GEMV_TRACE") != nullptr;
@@ -704,7 +729,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
         memset(tbuf, 0, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
         a.trace = tbuf;
     }
-    kern<<<grid, nwarps * 32, smem, ctx->stream>>>(a);
+    DWIM_CUDA(ctx, launch_dependent(kern, dim3((unsigned)grid), dim3((unsigned)(nwarps * 32)), (size_t)smem, ctx->stream, a));
     DWIM_LAUNCHED(ctx);
     if (tracing) {
         cudaStreamSynchronize(ctx->stream);

@@ -23,6 +23,7 @@
 //     run  = 16c + 8*nib + (j ^ c)      k = 64c + 32*nib + 4j + e
 //     position = 4*run + {0,2,1,3}[e]
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace dwim {
 
@@ -48,6 +49,9 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <bool Q4K>
 __global__ void __launch_bounds__(256) panel_kernel(const float *__restrict__ x, size_t cols, int ncols, int split,
                                                     __half *__restrict__ panels) {
+    // as panel_i8_kernel: let the next small-M launch begin, wait for the kernel ahead
+    griddep_launch();
+    griddep_wait();
     int u = blockIdx.x, t = blockIdx.y, k = threadIdx.x;
     size_t kk = (size_t)u * 256 + k;
     float v = kk < cols ? x[(size_t)t * cols + kk] : 0.0f;
@@ -85,8 +89,10 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
     if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one panel build: %zu", n);
     dim3 grid((unsigned)units, (unsigned)n);
     int ncols = (int)n * (split ? 2 : 1);
-    if (kind == SHADOW_PANEL_Q4K) panel_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, cols, ncols, split, panels);
-    else panel_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, cols, ncols, split, panels);
+    if (kind == SHADOW_PANEL_Q4K)
+        DWIM_CUDA(ctx, launch_dependent(panel_kernel<true>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
+    else
+        DWIM_CUDA(ctx, launch_dependent(panel_kernel<false>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
     DWIM_LAUNCHED(ctx);
     return 0;
 }
@@ -113,6 +119,10 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
 size_t panel_i8_bytes(size_t cols, size_t n) { return ((cols + 255) / 256) * (size_t)i8_unit_bytes(4 * (int)n); }
 
 __global__ void __launch_bounds__(256) panel_i8_kernel(const float *__restrict__ x, size_t cols, int n, uint8_t *__restrict__ panels) {
+    // the small-M kernel launched next may start streaming its weights now; the
+    // panels may still be read, and x written, by the kernel ahead
+    griddep_launch();
+    griddep_wait();
     const int u = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, j = tid >> 5, lane = tid & 31;
     const int nc = 4 * n;
     uint8_t *blob = panels + (size_t)u * i8_unit_bytes(nc);
@@ -161,7 +171,7 @@ int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, u
     if (n == 0 || cols == 0) return 0;
     if (n > I8_MAX_TOKENS) return fail(ctx, DWIM_B200_EINVAL, "int8 panels take at most %d tokens, not %zu", I8_MAX_TOKENS, n);
     dim3 grid((unsigned)((cols + 255) / 256), (unsigned)n);
-    panel_i8_kernel<<<grid, 256, 0, ctx->stream>>>(x, cols, (int)n, panels);
+    DWIM_CUDA(ctx, launch_dependent(panel_i8_kernel, grid, dim3(256), 0, ctx->stream, x, cols, (int)n, panels));
     DWIM_LAUNCHED(ctx);
     return 0;
 }

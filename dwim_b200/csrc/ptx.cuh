@@ -84,6 +84,13 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint32_
     mbar_wait_slow(bar, parity, status, code);
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start
+// while the kernel before it in the stream still runs.  griddep_wait() returns
+// once that kernel has completed and its writes are visible (at once when the
+// launch was an ordinary one); griddep_launch() lets the next such launch begin.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
