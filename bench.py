@@ -41,6 +41,8 @@ WORKLOADS = {
     "c3_q6k": ("q6_k", 151936, 5120, 1, "f32"),
     "c3_q8": ("q8_0", 5120, 5120, 1, "f32"),
     "c3_attn": ("q4_k", 12288, 5120, 1, "f32"),
+    # the feed-forward block gate/up [17408,5120], down [5120,17408], tensor parallel over the ranks
+    "c5": ("q4_k", 17408, 5120, 1, "bf16"),
 }
 L2_BYTES = 126 * 1024 * 1024
 
@@ -125,8 +127,10 @@ def algorithmic_bytes(fmt, rows, cols, m):
 
 
 # ---------------------------------------------------------------------------------------
-def run_reference(args, fmt, rows, cols, m, act):
-    """The reference's CPU path (restated in oracle/) on the host cores."""
+def run_reference(args, fmt, rows, cols, m, act, ffn=False):
+    """The reference's CPU path (restated in oracle/) on the host cores.  For the
+    feed-forward block: one [rows, cols] product timed, times three (gate, up and
+    down hold the same number of weights; the SiLU is noise beside them)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -153,11 +157,15 @@ def run_reference(args, fmt, rows, cols, m, act):
     full = dt * rows / sample_rows                       # a whole step, scaled by rows
     metric, unit, value = headline(fmt, rows, cols, m, full)
     sample = f"{sample_rows} of {rows} weight rows x {m} tokens per step, time scaled by rows"
+    if ffn:
+        full *= 3
+        metric, unit, value = "q4k_ffn_tok_per_s", "tok/s", m / full
+        sample += ", times three for gate, up and down"
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(fmt, rows, cols, m, act, args.gpus),
+        "config": ffn_config(rows, cols, m, act, args.gpus) if ffn else workload_config(fmt, rows, cols, m, act, args.gpus),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tok_per_s": m / full,
@@ -171,10 +179,16 @@ def headline(fmt, rows, cols, m, seconds):
     return ("q4k_decode_gemv_hbm_gbs" if fmt == "q4_k" else f"{fmt}_gemv_hbm_gbs"), "GB/s", algorithmic_bytes(fmt, rows, cols, m) / seconds / 1e9
 
 
-def workload_config(fmt, rows, cols, m, act, gpus):
+def workload_config(fmt, rows, cols, m, act, gpus, gather=False):
+    if gpus > 1:
+        sharding = (f"rows/{gpus} + all-gather of the f32 result" if gather else
+                    f"rows/{gpus}; a rank's rows of the result stay on it (they are the K slice its part of the "
+                    "down projection multiplies): no collective on this product; --gather adds the exchange")
+    else:
+        sharding = "none"
     return {"workload": f"{fmt.upper()} W[{rows},{cols}] x {act} X[{m},{cols}], fp32 accumulate",
             "format": fmt, "rows": rows, "cols": cols, "tokens": m, "activations": act,
-            "sharding": f"rows/{gpus} + all-gather" if gpus > 1 else "none",
+            "sharding": sharding,
             "l2": "weights rotate over copies totalling more than the 126 MB L2"}
 
 
@@ -208,7 +222,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
 
     xb = dev.alloc(m * cols)
     (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
-    if world > 1:
+    gather = world > 1 and args.gather
+    if gather:
         if my_rows != part_rows:
             raise SystemExit(f"{rows} rows do not split evenly over {world} ranks at multiples of {align}")
         parts_t = torch.empty(world * m * part_rows, dtype=torch.float32, device="cuda")
@@ -217,13 +232,13 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
         parts = dev.wrap(parts_t.data_ptr(), parts_t.numel())
         out = dev.alloc(m * rows)
     else:
-        out_local = out = dev.alloc(m * rows)
+        out_local = out = dev.alloc(m * my_rows)
 
     def step(i, fresh_input=True):
         if fresh_input:
             dev.resize(xb, m * cols)          # marks the input as rewritten: its 16-bit operand form is rebuilt
         dev.matmul(out_local, weights[i % copies], xb)
-        if world > 1:
+        if gather:
             with torch.cuda.stream(ext):
                 dist.all_gather_into_tensor(parts_t, mine_t)
             dev.gather_rows(out, parts, m, rows, world, align)
@@ -263,7 +278,7 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     else:
         hx = torch.empty(m * cols, dtype=torch.float32, pin_memory=True).numpy()
         hx[:] = x.ravel()
-    hout = torch.empty(m * rows, dtype=torch.float32, pin_memory=True).numpy()
+    hout = torch.empty(len(out), dtype=torch.float32, pin_memory=True).numpy()
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step(i):
@@ -273,7 +288,7 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
 
     def step_no_resize(i):
         dev.matmul(out_local, weights[i % copies], xb)
-        if world > 1:
+        if gather:
             with torch.cuda.stream(ext):
                 dist.all_gather_into_tensor(parts_t, mine_t)
             dev.gather_rows(out, parts, m, rows, world, align)
@@ -325,10 +340,10 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 (exact integer weights x f16 activations), f32 accumulate", "data": "synthetic",
-            "config": workload_config(fmt, rows, cols, m, act, world),
+            "config": workload_config(fmt, rows, cols, m, act, world, gather),
             "tok_per_s": m / per_step,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(hx.nbytes),
-                    "d2h_bytes_per_step": int(m * rows * 4), "ms_per_step": e2e_s * 1e3},
+                    "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": roof,
@@ -336,6 +351,137 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(fmt, rows, cols, m, act)
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def ffn_config(inner, hidden, m, act, gpus):
+    return {"workload": f"feed-forward block: Q4_K gate, up [{inner},{hidden}], down [{hidden},{inner}] x {act} X[{m},{hidden}]",
+            "format": "q4_k", "rows": inner, "cols": hidden, "tokens": m, "activations": act,
+            "sharding": (f"tensor parallel over {gpus}: gate/up by rows, down by the same K blocks (cuts at multiples of "
+                         "256), one NCCL all-reduce of the f32 [tokens, hidden] partial sums") if gpus > 1 else "none",
+            "l2": "blocks rotate over copies totalling more than the 126 MB L2"}
+
+
+def run_ffn(args, fmt, inner, hidden, m, act):
+    """Config 5: out = down . (silu(gate . x) * (up . x)), tokens per second."""
+    import torch
+    from dwim_b200 import B200, Tensor, shard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = B200(local)
+
+    # every rank draws the same block (seed 5) and keeps its shard
+    rng = np.random.default_rng(5)
+    b, e = shard.ffn_cuts(inner, world)[rank]
+    def quantized(rows, cols, keep_rows=None, keep_cols=None):
+        w = 0.02 * rng.standard_normal((rows, cols), dtype=np.float32)
+        if keep_rows is not None:
+            w = w[keep_rows[0]:keep_rows[1]]
+        if keep_cols is not None:
+            w = np.ascontiguousarray(w[:, keep_cols[0]:keep_cols[1]])
+        return dev.quantize(fmt, w) if w.shape[0] and w.shape[1] else None
+    gate, up, down = quantized(inner, hidden, (b, e)), quantized(inner, hidden, (b, e)), quantized(hidden, inner, None, (b, e))
+    my_inner = e - b
+    if not my_inner:
+        raise SystemExit(f"rank {rank} of {world} holds no part of the block")
+    my_bytes = gate.data.size + up.data.size + down.data.size
+    copies = int(min(24, max(2, -(-3 * L2_BYTES // my_bytes))))
+    blocks = [shard.ShardedFFN(dev, gate, up, down, 0, 1) for _ in range(copies)]   # already this rank's shard
+    for blk in blocks:
+        blk.world, blk.rank = world, rank
+    x = np.random.default_rng(6).standard_normal((m, hidden), dtype=np.float32)
+    bits = None
+    if act == "bf16":
+        x /= np.sqrt((x * x).mean(1, keepdims=True))
+        bits = ((x.view(np.uint32) + 0x7FFF + ((x.view(np.uint32) >> 16) & 1)) >> 16).astype(np.uint16)
+    xb = dev.alloc(m * hidden)
+    (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
+
+    def step(i):
+        dev.resize(xb, m * hidden)            # the input counts as rewritten: its operand form is rebuilt
+        return blocks[i % copies].forward(xb)
+
+    def timed(n_steps):
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        dev.sync()
+        launches0 = dev.launches
+        dev.timer_begin()
+        for i in range(n_steps):
+            step(i)
+        ms = dev.timer_end()
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / 1e3, dev.launches - launches0
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    with ClockSampler(local) as clocks:
+        seconds, launches = timed(args.steps)
+    per_step = seconds / args.steps
+
+    # end to end: pinned host x -> device -> block -> pinned host out
+    hx = torch.empty(m * hidden, dtype=torch.uint16 if bits is not None else torch.float32, pin_memory=True).numpy()
+    hx[:] = (bits if bits is not None else x).ravel()
+    hout = torch.empty(m * hidden, dtype=torch.float32, pin_memory=True).numpy()
+    def e2e_step(i):
+        (dev.write_bf16(xb, hx) if bits is not None else dev.write(xb, hx))
+        dev.read(blocks[i % copies].forward(xb), hout)
+    e2e_steps = max(3, min(args.steps, 20))
+    for i in range(2):
+        e2e_step(i)
+    if dist:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank == 0:
+        pk = peaks()
+        if m > 16:
+            achieved = 2.0 * m * 3 * my_inner * hidden / per_step / 1e12
+            roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"]}
+        else:
+            achieved = (my_bytes + m * hidden * 8 + m * my_inner * 8) / per_step / 1e9
+            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"]}
+        roof["note"] = "the whole step on this rank (three products, prologues, all-reduce), not one kernel"
+        line = {
+            "metric": "q4k_ffn_tok_per_s", "value": m / per_step, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16/int8 (exact integer weights), f32 accumulate", "data": "synthetic",
+            "config": ffn_config(inner, hidden, m, act, world),
+            "e2e": {"value": m / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(hx.nbytes),
+                    "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roof, "device": dev.name(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cb = cpu_baseline(fmt, inner, hidden, m, act)
+            dt = cb["ms_per_step"] * 3 / 1e3
+            line["cpu_baseline"] = {"value": m / dt, "unit": "tok/s", "cores": cb["cores"], "kind": "port",
+                                    "sample": cb["sample"] + ", times three for gate, up and down", "ms_per_step": dt * 1e3}
         print(json.dumps(line))
         sys.stdout.flush()
     if dist:
@@ -378,20 +524,25 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--m", type=int, default=None, help="tokens per step (default: the workload's)")
+    ap.add_argument("--m", "--tokens", dest="m", type=int, default=None, help="tokens per step (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", action="store_true",
+                    help="N > 1: all-gather the row-sharded result onto every rank inside the step")
     args = ap.parse_args()
     fmt, rows, cols, m, act = WORKLOADS[args.workload]
     if args.m:
         m = args.m
     if args.impl == "reference":
-        run_reference(args, fmt, rows, cols, m, act)
+        run_reference(args, fmt, rows, cols, m, act, ffn=args.workload == "c5")
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         if args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is {world})")
-    run_gpu(args, args.workload, fmt, rows, cols, m, act)
+    if args.workload == "c5":
+        run_ffn(args, fmt, rows, cols, m, act)
+    else:
+        run_gpu(args, args.workload, fmt, rows, cols, m, act)
 
 
 if __name__ == "__main__":

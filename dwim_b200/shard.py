@@ -1,4 +1,5 @@
-"""Row sharding of a weight matrix over the GPUs of one node.
+"""Sharding over the GPUs of one node: a weight matrix by rows, and the
+feed-forward block tensor-parallel (rows of gate/up, columns of down).
 
 The reference engine is single-GPU (gpu/cuda/mod.rs:230 opens device 0 and
 nothing else); this is new.  Output rows of ``out[t] = W . x[t]`` are
@@ -90,3 +91,75 @@ class RowSharded:
                 mine.view(n, self.part_rows)[:, :my_rows] = src
             dist.all_gather_into_tensor(self._parts, mine, group=self.group)
         self.dev.gather_rows(out, parts, n, self.rows, self.world, self.align)
+
+
+# ---- the feed-forward block, tensor parallel ------------------------------------------
+#
+#   out[t] = down . ( silu(gate . x[t]) * (up . x[t]) )
+#
+# (inference/qwen35/mod.rs:652-654: swiglu, then matmul_add with the down
+# projection).  gate and up are split by output rows, down by the same indices
+# along its K, so the intermediate of a rank is exactly the K slice its part
+# of down multiplies and never leaves the GPU; the ranks' partial sums of
+# ``out`` are added by one all-reduce.  The cuts fall on multiples of 256 rows:
+# whole blocks of down's rows (the k-quant formats pack 256 weights of K).
+
+FFN_ALIGN = 256
+
+
+def ffn_cuts(inner: int, world: int):
+    """[(begin, end)] of the intermediate dimension per rank, at multiples of 256."""
+    return plan(inner, world, FFN_ALIGN)
+
+
+def ffn_shard(gate: Tensor, up: Tensor, down: Tensor, rank: int, world: int):
+    """Rank ``rank``'s parts (gate rows, up rows, down columns) of the block."""
+    inner = gate.rows
+    if up.shape != gate.shape or down.cols != inner or down.rows != gate.cols:
+        raise ValueError(f"not a feed-forward block: gate {gate.shape}, up {up.shape}, down {down.shape}")
+    b, e = ffn_cuts(inner, world)[rank]
+    groups = range(b // FFN_ALIGN, e // FFN_ALIGN)
+    return gate.slice_rows(b, e), up.slice_rows(b, e), down.select_column_groups(FFN_ALIGN, groups)
+
+
+class ShardedFFN:
+    """The feed-forward block over the ranks of a process group (one process
+    per GPU).  ``forward`` leaves the block's full output on every rank."""
+
+    def __init__(self, dev: B200, gate: Tensor, up: Tensor, down: Tensor, rank: int = 0, world: int = 1, group=None):
+        import torch
+        self.dev, self.rank, self.world, self.group = dev, rank, world, group
+        self.hidden, self.inner = gate.cols, gate.rows
+        g, u, d = ffn_shard(gate, up, down, rank, world)
+        self.my_inner = g.rows
+        self.gate, self.up, self.down = dev.upload(g), dev.upload(u), dev.upload(d)
+        self._torch = torch
+        self._stream = torch.cuda.ExternalStream(dev.stream)
+        self._n = -1
+
+    def _buffers(self, n: int):
+        if n != self._n:
+            t = self._torch
+            self._out_t = t.zeros(n * self.hidden, dtype=t.float32, device="cuda")
+            self._out = self.dev.wrap(self._out_t.data_ptr(), n * self.hidden)
+            self._h = self.dev.alloc(n * self.my_inner)
+            self._scratch = self.dev.alloc(n * self.my_inner)
+            self._n = n
+        return self._out_t, self._out, self._h, self._scratch
+
+    def forward(self, x):
+        """The block applied to ``x`` (n * hidden floats): returns the device
+        buffer of n * hidden floats, valid until the next call."""
+        n = len(x) // self.hidden
+        out_t, out, h, scratch = self._buffers(n)
+        if self.my_inner:
+            self.dev.swiglu(h, self.gate, self.up, x, scratch)
+            self.dev.matmul(out, self.down, h)
+        else:
+            with self._torch.cuda.stream(self._stream):
+                out_t.zero_()
+        if self.world > 1:
+            import torch.distributed as dist
+            with self._torch.cuda.stream(self._stream):
+                dist.all_reduce(out_t, group=self.group)
+        return out
