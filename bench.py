@@ -43,6 +43,8 @@ WORKLOADS = {
     "c3_attn": ("q4_k", 12288, 5120, 1, "f32"),
     # the feed-forward block gate/up [17408,5120], down [5120,17408], tensor parallel over the ranks
     "c5": ("q4_k", 17408, 5120, 1, "bf16"),
+    # every matrix product of one decoded token: 64 layers + the vocabulary head (rows/cols here: the FFN's)
+    "c4": ("q4_k", 17408, 5120, 1, "f32"),
 }
 L2_BYTES = 126 * 1024 * 1024
 
@@ -489,6 +491,102 @@ def run_ffn(args, fmt, inner, hidden, m, act):
         dist.destroy_process_group()
 
 
+def run_decoder(args, m):
+    """Config 4: the matrix products of one decoder pass over m tokens, in the
+    engine's order (inference/qwen35/mod.rs:547-654; shapes and call counts after
+    gpu/tests.rs:431-436, 476-600): 16 attention layers (q+gate [12288,5120], k
+    and v [1024,5120], o [5120,6144]), 48 linear-attention layers (qkv
+    [10240,5120], z [6144,5120], out [5120,6144]), each followed by the
+    feed-forward block (gate, up [17408,5120], down [5120,17408]) in Q4_K, and
+    the vocabulary head [151936,5120] in Q6_K.  Every layer has its own copy of
+    its weights in HBM (14.4 GB in all), so L2 cannot help.  What sits between
+    the products (norms, attention, rope, ...) is not on this path and not run;
+    an input counts as rewritten wherever the engine would have rewritten it."""
+    import torch
+    from dwim_b200 import B200, row_bytes
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the decoder schedule runs on one GPU")
+    torch.cuda.set_device(0)
+    dev = B200(0)
+    rng = np.random.default_rng(4)
+    hidden, inner, attn = 5120, 17408, 6144
+
+    def host(fmt, rows, cols):
+        return dev.quantize(fmt, 0.02 * rng.standard_normal((rows, cols), dtype=np.float32))
+    shapes = {"qg": (12288, hidden), "kv": (1024, hidden), "o": (hidden, attn), "qkv": (10240, hidden), "z": (attn, hidden),
+              "gate": (inner, hidden), "down": (hidden, inner)}
+    proto = {k: host("q4_k", *v) for k, v in shapes.items()}
+    head = dev.upload(host("q6_k", 151936, hidden))
+    layers, total = [], 151936 * row_bytes("q6_k", hidden)
+    for l in range(64):
+        names = ["qg", "kv", "kv", "o"] if l % 4 == 3 else ["qkv", "z", "o"]
+        names += ["gate", "gate", "down"]
+        layers.append([dev.upload(proto[n]) for n in names])
+        total += sum(proto[n].data.size for n in names)
+    x = dev.buffer(rng.standard_normal((m, hidden), dtype=np.float32))        # the residual stream's normalized copy
+    a = dev.buffer(rng.standard_normal((m, attn), dtype=np.float32))          # attention output
+    res = dev.alloc(m * hidden)
+    outs = {r: dev.alloc(m * r) for r in (12288, 1024, 10240, attn)}
+    h, scratch, logits = dev.alloc(m * inner), dev.alloc(m * inner), dev.alloc(m * 151936)
+
+    def token():
+        for l, w in enumerate(layers):
+            dev.resize(x, m * hidden)                       # the layer's normalized input
+            if l % 4 == 3:
+                dev.matmul(outs[12288], w[0], x); dev.matmul(outs[1024], w[1], x); dev.matmul(outs[1024], w[2], x)
+                dev.resize(a, m * attn); dev.matmul_add(res, w[3], a)
+                f = w[4:]
+            else:
+                dev.matmul(outs[10240], w[0], x); dev.matmul(outs[attn], w[1], x)
+                dev.resize(a, m * attn); dev.matmul_add(res, w[2], a)
+                f = w[3:]
+            dev.resize(x, m * hidden)                       # normalized again before the feed-forward block
+            dev.swiglu(h, f[0], f[1], x, scratch)
+            dev.matmul_add(res, f[2], h)
+        dev.resize(x, m * hidden)
+        dev.matmul(logits, head, x)
+
+    for _ in range(max(2, args.warmup // 2)):
+        token()
+    dev.sync()
+    steps = max(3, min(args.steps, 20))
+    with ClockSampler(0) as clocks:
+        launches0 = dev.launches
+        dev.timer_begin()
+        for _ in range(steps):
+            token()
+        seconds = dev.timer_end() / 1e3 / steps
+        launches = (dev.launches - launches0) // steps
+    # end to end: the token's embedding row in, the logits out
+    hx = torch.empty(m * hidden, dtype=torch.float32, pin_memory=True).numpy(); hx[:] = 0.5
+    hl = torch.empty(m * 151936, dtype=torch.float32, pin_memory=True).numpy()
+    def e2e():
+        dev.write(x, hx); token(); dev.read(logits, hl)
+    e2e()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        e2e()
+    e2e_s = (time.perf_counter() - t0) / 3
+    pk = peaks()
+    achieved = total / seconds / 1e9
+    print(json.dumps({
+        "metric": "decode_matmul_tok_per_s", "value": m / seconds, "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(2, args.warmup // 2), "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8/f16 (exact integer weights), f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"all matrix products of one decoder pass, {m} token(s): 64 layers Q4_K + Q6_K head, "
+                               f"{total / 1e9:.2f} GB of weights resident, each read once per pass",
+                   "tokens": m, "products_per_pass": 16 * 7 + 48 * 6 + 1, "l2": "every layer has its own weights in HBM"},
+        "e2e": {"value": m / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(hx.nbytes), "d2h_bytes_per_step": int(hl.nbytes),
+                "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": int(launches), "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                     "traffic": None, "peak_source": pk["source"],
+                     "note": "weight bytes of the whole pass over its time: all kernels, prologues and launch gaps included"},
+        "device": dev.name(),
+    }))
+
+
 def cpu_baseline(fmt, rows, cols, m, act):
     """The oracle's matmul on the host cores, on a bounded sample (about 10 s)."""
     import oracle
@@ -539,7 +637,9 @@ def main():
     if world != args.gpus:
         if args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is {world})")
-    if args.workload == "c5":
+    if args.workload == "c4":
+        run_decoder(args, m)
+    elif args.workload == "c5":
         run_ffn(args, fmt, rows, cols, m, act)
     else:
         run_gpu(args, args.workload, fmt, rows, cols, m, act)
