@@ -236,6 +236,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     else:
         out_local = out = dev.alloc(m * my_rows)
 
+    per_rank = []
+
     def step(i, fresh_input=True):
         if fresh_input:
             dev.resize(xb, m * cols)          # marks the input as rewritten: its 16-bit operand form is rebuilt
@@ -251,24 +253,32 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
         torch.cuda.synchronize()
         dev.sync()
         launches0 = dev.launches
+        h0 = time.perf_counter()
         dev.timer_begin()
         for i in range(n_steps):
             step(i, fresh_input)
+        issue_ms = (time.perf_counter() - h0) * 1e3
         ms = dev.timer_end()
+        per_rank.clear()
+        per_rank.append({"device_ms_per_step": ms / n_steps, "host_issue_ms_per_step": issue_ms / n_steps})
         if world > 1:
             torch.cuda.synchronize()
             dist.barrier()
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            t = torch.tensor([ms, issue_ms], device="cuda")
+            all_t = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(all_t, t)
+            per_rank.clear()
+            per_rank.extend({"device_ms_per_step": float(v[0]) / n_steps, "host_issue_ms_per_step": float(v[1]) / n_steps} for v in all_t)
+            ms = max(float(v[0]) for v in all_t)
         return ms / 1e3, dev.launches - launches0
 
     for i in range(max(args.warmup, 3)):
         step(i)
     with ClockSampler(local) as clocks:
         seconds, launches = timed(args.steps)
+        ranks_report = list(per_rank)
         # the dominant kernel alone (operand form cached): what the roofline is about
-        kernel_seconds, _ = timed(args.steps, fresh_input=False) if world == 1 else (seconds, 0)
+        kernel_seconds, _ = timed(args.steps, fresh_input=False)
     per_step = seconds / args.steps
     per_kernel = kernel_seconds / args.steps
     metric, unit, value = headline(fmt, rows, cols, m, per_step)
@@ -350,6 +360,7 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             "clocks": clocks.summary(),
             "roofline": roof,
             "device": dev.name(),
+            "ranks": ranks_report,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(fmt, rows, cols, m, act)

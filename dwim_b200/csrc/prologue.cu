@@ -180,21 +180,53 @@ size_t gemm_operand_bytes(size_t cols, size_t ncols) {
     return ncols * cols * sizeof(__half) + ncols * (cols / 256) * 16 * sizeof(__half);
 }
 
-// grid (units, tokens), 256 threads.
+// grid (ceil(units / 4), tokens), 256 threads: a thread takes four consecutive
+// activations (one 16-byte load, one 8-byte store per column), eight threads a
+// 32-wide sub-block, 64 a unit.
+template <bool ALIGNED>   // whether x is 16-byte aligned (a wrapped caller's pointer need not be)
 __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *__restrict__ x, size_t cols, size_t units, int split,
                                                            __half *__restrict__ x16, __half *__restrict__ means) {
-    const int u = blockIdx.x, t = blockIdx.y, k = threadIdx.x;
-    const float v = x[(size_t)t * cols + (size_t)u * 256 + k];
-    const __half hi = to_f16_clamped(v);
-    const __half lo = to_f16_clamped(v - __half2float(hi));
-    const int e = k & 3, pos = (k & ~3) | ((e & 1) << 1) | (e >> 1);
+    const int t = blockIdx.y, k = threadIdx.x;
+    const size_t u = (size_t)blockIdx.x * 4 + (k >> 6);
+    if (u >= units) return;                           // whole 64-thread groups leave together
+    const size_t at = u * 256 + (size_t)(k & 63) * 4;
+    const float *src = x + (size_t)t * cols + at;
+    float f[4];
+    if (ALIGNED) {
+        const float4 v = *reinterpret_cast<const float4 *>(src);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 4; e++) f[e] = src[e];
+    }
+    __half hi[4], lo[4];
+    float sh = 0.0f, sl = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        hi[e] = to_f16_clamped(f[e]);
+        lo[e] = to_f16_clamped(f[e] - __half2float(hi[e]));
+        sh += __half2float(hi[e]);
+        sl += __half2float(lo[e]);
+    }
+    // a group of four goes out in the order (0, 2, 1, 3): the order the weights' bytes decode in
     const size_t col = split ? 2 * (size_t)t : (size_t)t;
-    x16[col * cols + (size_t)u * 256 + pos] = hi;
-    if (split) x16[(col + 1) * cols + (size_t)u * 256 + pos] = lo;
-    const float mh = warp_sum(__half2float(hi)) * (1.0f / 32.0f);
-    const float ml = split ? warp_sum(__half2float(lo)) * (1.0f / 32.0f) : 0.0f;
-    if ((k & 31) == 0) {
-        const int j = k >> 5;
+    auto pack = [](const __half (&h)[4]) {
+        uint2 r;
+        r.x = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[2]) << 16);
+        r.y = (uint32_t)__half_as_ushort(h[1]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+        return r;
+    };
+    *reinterpret_cast<uint2 *>(x16 + col * cols + at) = pack(hi);
+    if (split) *reinterpret_cast<uint2 *>(x16 + (col + 1) * cols + at) = pack(lo);
+    // sub-block sums over the eight threads that share it
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        sh += __shfl_xor_sync(0xffffffffu, sh, o);
+        sl += __shfl_xor_sync(0xffffffffu, sl, o);
+    }
+    if ((k & 7) == 0) {
+        const int j = (k & 63) >> 3;
+        const float mh = sh * (1.0f / 32.0f), ml = sl * (1.0f / 32.0f);
         __half *m = means + (col * units + u) * 16;
         const __half a = to_f16_clamped(mh);
         m[j] = a;
@@ -213,8 +245,11 @@ int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols
     if (cols % 256) return fail(ctx, DWIM_B200_EINVAL, "GEMM operand: %zu columns are not whole 256-weight units", cols);
     if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one operand build: %zu", n);
     const size_t units = cols / 256, ncols = n * (split ? 2 : 1);
-    dim3 grid((unsigned)units, (unsigned)n);
-    gemm_operand_kernel<<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
+    dim3 grid((unsigned)((units + 3) / 4), (unsigned)n);
+    if (reinterpret_cast<uintptr_t>(x) % 16 == 0)
+        gemm_operand_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
+    else
+        gemm_operand_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
     DWIM_LAUNCHED(ctx);
     return 0;
 }
