@@ -214,10 +214,11 @@ __device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int xu, int ncol
 // High nibbles are masked in place (16*q: no shift) and their sums divided by
 // 16 once per unit.  The minimums use the digits' per-sub-block sums (dp4a).
 // About half the instructions of the f16 routine above for the same weights.
+// c = a * b (the accumulator operand is zero, not a register that has to be cleared first)
 __device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {   // a unsigned bytes, b signed bytes
     int d;
@@ -242,20 +243,24 @@ __device__ __forceinline__ void unit_q4k_i8(const Lane &L, int ul, int xu, int n
     const uint32_t sa[2] = {ha.y & 0x3f3f3f3fu, (ha.w & 0x0f0f0f0fu) | ((ha.y >> 2) & 0x30303030u)};
     const uint32_t sb[2] = {hb.y & 0x3f3f3f3fu, (hb.w & 0x0f0f0f0fu) | ((hb.y >> 2) & 0x30303030u)};
     int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
+    const uint32_t qa = ba + 16 + 8 * L.c, qb = bb + 16 + 8 * L.c;
+    uint32_t xcol = blob + L.g * 32 + 8 * L.c;      // this lane's column, sub-block 0; a sub-block further on is 32*nc
+    const uint32_t xstep = 32 * nc;
 #pragma unroll
     for (int G = 0; G < 4; G++) {   // group G: low nibbles = sub-block 2G, high nibbles = 2G+1
-        const uint2 wa = lds64(ba + 16 + 32 * G + 8 * L.c), wb = lds64(bb + 16 + 32 * G + 8 * L.c);
+        const uint2 wa = lds64(qa + 32 * G), wb = lds64(qb + 32 * G);
         uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
         if (bcol) {
-            x0 = lds64(blob + ((2 * G) * nc + L.g) * 32 + 8 * L.c);
-            x1 = lds64(blob + ((2 * G + 1) * nc + L.g) * 32 + 8 * L.c);
+            x0 = lds64(xcol);
+            x1 = lds64(xcol + xstep);
         }
-        int c0[4] = {0, 0, 0, 0}, c1[4] = {0, 0, 0, 0};
+        xcol += 2 * xstep;
+        int c0[4], c1[4];
         imma_u8s8(c0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, x0.x, x0.y);
         imma_u8s8(c1, wa.x & 0xf0f0f0f0u, wb.x & 0xf0f0f0f0u, wa.y & 0xf0f0f0f0u, wb.y & 0xf0f0f0f0u, x1.x, x1.y);
-        const int sh = 16 * (G & 1);
-        const int s0a = (sa[G >> 1] >> sh) & 0xff, s1a = (sa[G >> 1] >> (sh + 8)) & 0xff;
-        const int s0b = (sb[G >> 1] >> sh) & 0xff, s1b = (sb[G >> 1] >> (sh + 8)) & 0xff;
+        // the two sub-blocks' scales: bytes 2(G&1) and 2(G&1)+1 of the word, each by one byte permute
+        const int s0a = (int)prmt(sa[G >> 1], 0u, 0x4440u + 2 * (G & 1)), s1a = (int)prmt(sa[G >> 1], 0u, 0x4441u + 2 * (G & 1));
+        const int s0b = (int)prmt(sb[G >> 1], 0u, 0x4440u + 2 * (G & 1)), s1b = (int)prmt(sb[G >> 1], 0u, 0x4441u + 2 * (G & 1));
         ilo[0] += s0a * c0[0]; ilo[1] += s0a * c0[1]; ilo[2] += s0b * c0[2]; ilo[3] += s0b * c0[3];
         ihi[0] += s1a * c1[0]; ihi[1] += s1a * c1[1]; ihi[2] += s1b * c1[2]; ihi[3] += s1b * c1[3];
     }
