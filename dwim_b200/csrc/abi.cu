@@ -470,10 +470,20 @@ int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_
             "swiglu: gate is [%zu, %zu] but up is [%zu, %zu]", gate->v.rows, gate->v.cols, up->v.rows, up->v.cols);
     REQUIRE(ctx, scratch->len == out->len, DWIM_B200_EINVAL, "swiglu: scratch of %zu for out of %zu", scratch->len, out->len);
     REQUIRE(ctx, scratch->data != out->data, DWIM_B200_EINVAL, "swiglu: scratch aliases out");
-    // up . x into scratch, then gate . x with the activation fused into the
-    // epilogue, as the reference's CUDA device does (gpu/cuda/mod.rs:1148-1175).
-    int rc = product(ctx, scratch->data, scratch->len, up, x, nullptr, EPI_STORE, "swiglu");
-    if (rc == 0) rc = product(ctx, out->data, out->len, gate, x, scratch->data, EPI_SWIGLU, "swiglu");
+    int rc;
+    const size_t n = gate->v.cols ? x->len / gate->v.cols : 0;
+    if (gate->v.fmt == up->v.fmt && gate->v.qpitch == up->v.qpitch && gemv_takes_i8(gate->v, n) &&
+        x->len == n * gate->v.cols && out->len == n * gate->v.rows && out->data != x->data && gate->v.rows) {
+        // one and two tokens: both matrices in one launch, the activation applied where the two sums meet
+        rc = ensure_shadow(ctx, x, SHADOW_PANEL_I8, gate->v.cols, 0);
+        if (rc == 0)
+            rc = gemv_small_i8(ctx, gate->v, (const uint8_t *)x->shadow, (int)n, out->data, nullptr, EPI_STORE, &up->v);
+    } else {
+        // up . x into scratch, then gate . x with the activation fused into the
+        // epilogue, as the reference's CUDA device does (gpu/cuda/mod.rs:1148-1175).
+        rc = product(ctx, scratch->data, scratch->len, up, x, nullptr, EPI_STORE, "swiglu");
+        if (rc == 0) rc = product(ctx, out->data, out->len, gate, x, scratch->data, EPI_SWIGLU, "swiglu");
+    }
     out->shadow_kind = scratch->shadow_kind = SHADOW_NONE;
     out->bf16_exact = scratch->bf16_exact = false;
     return rc;

@@ -133,7 +133,7 @@ enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 // columns, the launch's first at col0.  aux is the `up` product for EPI_SWIGLU.
 bool gemv_takes_i8(const WeightView &w, size_t n);
 int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
-                  int epilogue);
+                  int epilogue, const WeightView *up = nullptr);
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
                size_t t0, int split, float *out, const float *aux, int epilogue);
 int gemv_max_tokens(int split);

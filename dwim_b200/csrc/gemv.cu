@@ -44,6 +44,11 @@ struct GemvArgs {
     int xunit;               // bytes of one unit's panels for this launch
     int xsrc_stride;         // bytes between units in the panel array
     int ctas_per_sm;         // 0: one
+    // SwiGLU in one launch (int8 routine): `w` is the gate matrix, these the quants and scales of
+    // the up matrix of the same shape; a CTA takes a row tile of the one, then of the other, and
+    // writes silu(gate . x) * (up . x).  Null: an ordinary product.
+    const uint8_t *up_quants;
+    const __half *up_scales;
     int col0;                // first column of this launch
     int ncols;               // columns of this launch (<= 8*NT)
     int split;               // 1: columns are (hi, lo) pairs of a token
@@ -461,9 +466,13 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         // warp waits for the kernel ahead and requests the panels.
         uint32_t it = 0;
         const int my_tiles = (int)blockIdx.x < a.n_tiles ? (a.n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        const uint32_t ahead = (uint32_t)min(S, my_tiles * n_chunks);   // stages that need no free slot
+        const int n_mats = a.up_quants ? 2 : 1;
+        const uint32_t ahead = (uint32_t)min(S, my_tiles * n_mats * n_chunks);   // stages that need no free slot
         bool waited = false;
-        for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x) {
+        for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x)
+        for (int mat = 0; mat < n_mats; mat++) {
+            const uint8_t *wq = mat ? a.up_quants : a.w.quants;
+            const __half *wsc = mat ? a.up_scales : a.w.scales;
             const size_t row0 = (size_t)tile * R;
             const int nrows = (int)min((size_t)R, a.w.rows - row0);
             for (int ch = 0; ch < n_chunks; ch++, it++) {
@@ -494,14 +503,14 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                 const uint32_t st = stage0 + s * a.stage_bytes;
                 if (a.whole_rows) {
                     // consecutive rows are one contiguous run (rows sit qpitch apart, and so do the stage's)
-                    if (lane == 0) bulk_g2s(st, a.w.quants + row0 * a.w.qpitch, nrows * (uint32_t)a.w.qpitch, bar);
+                    if (lane == 0) bulk_g2s(st, wq + row0 * a.w.qpitch, nrows * (uint32_t)a.w.qpitch, bar);
                     if (HAS_SCALES && lane == 1)
-                        bulk_g2s(st + a.s_off, a.w.scales + row0 * a.w.srow, nrows * (uint32_t)a.w.srow * 2, bar);
+                        bulk_g2s(st + a.s_off, wsc + row0 * a.w.srow, nrows * (uint32_t)a.w.srow * 2, bar);
                 } else {
                     for (int r = lane; r < nrows; r += 32) {
-                        bulk_g2s(st + r * a.q_stride, a.w.quants + (row0 + r) * a.w.qpitch + (size_t)u0 * UNIT_Q, qbytes, bar);
+                        bulk_g2s(st + r * a.q_stride, wq + (row0 + r) * a.w.qpitch + (size_t)u0 * UNIT_Q, qbytes, bar);
                         if (HAS_SCALES)
-                            bulk_g2s(st + a.s_off + r * a.s_stride, a.w.scales + (row0 + r) * a.w.srow + s_first, sbytes, bar);
+                            bulk_g2s(st + a.s_off + r * a.s_stride, wsc + (row0 + r) * a.w.srow + s_first, sbytes, bar);
                     }
                 }
                 if (!waited && (!a.x_resident || it + 1 == ahead)) {
@@ -553,7 +562,10 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
     int tile_parity = 0;
     bool out_ready = false;
     if (a.x_resident && (int)blockIdx.x < a.n_tiles) mbar_wait(xbar, 0, a.status, 0x4u);
-    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x, tile_parity ^= 1) {
+    const int n_mats = a.up_quants ? 2 : 1;
+    float gate_a = 0.0f, gate_b = 0.0f;   // SwiGLU in one launch: the gate's sums for this lane's rows, kept until up's arrive
+    for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x)
+    for (int mat = 0; mat < n_mats; mat++, tile_parity ^= 1) {
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
@@ -622,9 +634,12 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
             va += __shfl_xor_sync(0xffffffffu, va, 1);
             vb += __shfl_xor_sync(0xffffffffu, vb, 1);
             const int t = L.c >> 1;
-            if (!(L.c & 1) && t < a.n_tokens) {
-                emit(a, t, r0, va);
-                emit(a, t, r1, vb);
+            if (n_mats == 2 && mat == 0) {
+                gate_a = va;
+                gate_b = vb;
+            } else if (!(L.c & 1) && t < a.n_tokens) {
+                emit(a, t, r0, n_mats == 2 ? silu_mul(gate_a, va) : va);
+                emit(a, t, r1, n_mats == 2 ? silu_mul(gate_b, vb) : vb);
             }
             continue;
         }
@@ -815,8 +830,9 @@ bool gemv_takes_i8(const WeightView &w, size_t n) {
 
 // One or two tokens of a Q4_K matrix through the int8 routine; `panels` from
 // build_panels_i8.
+// `up`, when given, makes it the SwiGLU of the pair (w = gate) in one launch.
 int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
-                  int epilogue) {
+                  int epilogue, const WeightView *up) {
     if (w.rows == 0 || n_tokens == 0) return 0;
     if (w.fmt != Q4_K || n_tokens > I8_MAX_TOKENS || w.cols % 256 != 0)
         return fail(ctx, DWIM_B200_EINVAL, "int8 small-M kernel: format %d, %d tokens", w.fmt, n_tokens);
@@ -833,6 +849,12 @@ int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels
     a.epi = epilogue;
     a.units = (int)(w.cols / 256);
     a.xunit = a.xsrc_stride = i8_unit_bytes(a.ncols);
+    if (up) {
+        if (up->fmt != w.fmt || up->rows != w.rows || up->cols != w.cols || up->qpitch != w.qpitch || epilogue != EPI_STORE)
+            return fail(ctx, DWIM_B200_EINVAL, "int8 small-M kernel: gate and up differ");
+        a.up_quants = up->quants;
+        a.up_scales = up->scales;
+    }
     a.status = ctx->status;
     return launch_shape<Q4K_I8, 1>(ctx, a);
 }

@@ -257,6 +257,21 @@ def test_swiglu_matches_cpu(dev, oracle, fmt):
         assert max_rel_err(got, want) <= TOL
 
 
+@pytest.mark.parametrize("n", [1, 2, 3])
+def test_swiglu_one_launch_at_model_width(dev, oracle, n):
+    """One and two tokens of Q4_K take gate and up in a single launch; three go the
+    two-launch way.  Rows that are not a whole tile, both ways against the CPU."""
+    rng = np.random.default_rng(53 + n)
+    rows, cols = 1000, 5120
+    gate = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    up = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
+    dev.swiglu(out, upload(dev, "q4_k", rows, cols, gate), upload(dev, "q4_k", rows, cols, up), dev.buffer(x), scratch)
+    want = oracle.swiglu("q4_k", gate, up, rows, cols, x)
+    assert max_rel_err(dev.read(out), want) <= 2e-5
+
+
 @pytest.mark.parametrize("fmt", FORMATS)
 def test_matmul_add_matches_cpu(dev, oracle, fmt):
     rng = oracle.Lcg(23)
