@@ -135,21 +135,28 @@ class ShardedFFN:
         self.gate, self.up, self.down = dev.upload(g), dev.upload(u), dev.upload(d)
         self._torch = torch
         self._stream = torch.cuda.ExternalStream(dev.stream)
-        self._n = -1
+
+    # Activation buffers are shared by every block of the same shape on a device (a
+    # decoder's layers use one residual stream, not one per layer): the all-reduce
+    # then always sees the same buffer, which NCCL has set up once.
+    _shared: dict = {}
 
     def _buffers(self, n: int):
-        if n != self._n:
+        key = (id(self.dev), n, self.hidden, self.my_inner)
+        bufs = ShardedFFN._shared.get(key)
+        if bufs is None:
             t = self._torch
-            self._out_t = t.zeros(n * self.hidden, dtype=t.float32, device="cuda")
-            self._out = self.dev.wrap(self._out_t.data_ptr(), n * self.hidden)
-            self._h = self.dev.alloc(n * self.my_inner)
-            self._scratch = self.dev.alloc(n * self.my_inner)
-            self._n = n
-        return self._out_t, self._out, self._h, self._scratch
+            out_t = t.zeros(n * self.hidden, dtype=t.float32, device="cuda")
+            bufs = (out_t, self.dev.wrap(out_t.data_ptr(), n * self.hidden), self.dev.alloc(n * self.my_inner),
+                    self.dev.alloc(n * self.my_inner))
+            ShardedFFN._shared[key] = bufs
+        self._out_t = bufs[0]
+        return bufs
 
     def forward(self, x):
         """The block applied to ``x`` (n * hidden floats): returns the device
-        buffer of n * hidden floats, valid until the next call."""
+        buffer of n * hidden floats, valid until the next ``forward`` of any
+        block of this shape on the device."""
         n = len(x) // self.hidden
         out_t, out, h, scratch = self._buffers(n)
         if self.my_inner:

@@ -402,3 +402,21 @@ def test_gather_rows_matches_the_host_assembly(dev):
         out = dev.alloc(n * rows)
         dev.gather_rows(out, dev.buffer(parts), n, rows, world, align)
         assert np.array_equal(dev.read(out).reshape(n, rows), shard.assemble(parts, n, rows, world, align))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [1, 40])
+def test_feed_forward_block_on_one_gpu(dev, oracle, n):
+    """ShardedFFN with a world of one: swiglu, then the down projection of the
+    f32 intermediate, against the CPU's two steps."""
+    from dwim_b200 import Tensor, shard
+    rng = np.random.default_rng(61 + n)
+    hidden, inner = 512, 1024
+    mk = lambda r, c: Tensor("q4_k", (r, c), oracle.quantize("q4_k", (0.05 * rng.standard_normal((r, c))).astype(np.float32)))
+    gate, up, down = mk(inner, hidden), mk(inner, hidden), mk(hidden, inner)
+    x = rng.standard_normal((n, hidden)).astype(np.float32)
+    block = shard.ShardedFFN(dev, gate, up, down)
+    got = dev.read(block.forward(dev.buffer(x))).reshape(n, hidden)
+    h = oracle.swiglu("q4_k", gate.data, up.data, inner, hidden, x)
+    want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
+    assert max_rel_err(got, want) <= 5e-5
