@@ -292,6 +292,7 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
             if (e == cudaSuccess) e = cudaMemcpyAsync(staging, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
             if (e == cudaSuccess)
                 rc = repack_to_device(ctx, fmt, rows, cols, staging, (uint8_t *)w->quants_alloc, (__half *)w->scales_alloc);
+                ctx->weights_written = true;
         }
     }
     // The host memory is the caller's again when this returns.

@@ -52,6 +52,10 @@ struct dwim_b200_ctx {
     char err[512] = {0};
     // the GEMM path's lazily created state
     void *gemm_state = nullptr;
+    // A kernel on the stream has written weight memory since the last small-M launch
+    // (an upload's repack): that launch must be an ordinary one, because a
+    // programmatic dependent streams weights before it waits for the kernels ahead.
+    bool weights_written = false;
 };
 
 namespace dwim {
@@ -79,8 +83,10 @@ inline int fail(dwim_b200_ctx *ctx, int code, const char *fmt, ...) {
 // call griddep_wait() (ptx.cuh) before they touch anything an earlier kernel
 // may read or write.  DWIM_B200_NO_PDL in the environment turns it off.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    static const bool pdl = getenv("DWIM_B200_NO_PDL") == nullptr;
+inline cudaError_t launch_dependent(bool allow, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    static const bool on = getenv("DWIM_B200_NO_PDL") == nullptr;
+    const bool pdl = on && allow;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

@@ -749,7 +749,9 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
         memset(tbuf, 0, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
         a.trace = tbuf;
     }
-    DWIM_CUDA(ctx, launch_dependent(kern, dim3((unsigned)grid), dim3((unsigned)(nwarps * 32)), (size_t)smem, ctx->stream, a));
+    const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
+    ctx->weights_written = false;
+    DWIM_CUDA(ctx, launch_dependent(dependent, kern, dim3((unsigned)grid), dim3((unsigned)(nwarps * 32)), (size_t)smem, ctx->stream, a));
     DWIM_LAUNCHED(ctx);
     if (tracing) {
         cudaStreamSynchronize(ctx->stream);

@@ -90,9 +90,9 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
     dim3 grid((unsigned)units, (unsigned)n);
     int ncols = (int)n * (split ? 2 : 1);
     if (kind == SHADOW_PANEL_Q4K)
-        DWIM_CUDA(ctx, launch_dependent(panel_kernel<true>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
+        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, panel_kernel<true>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
     else
-        DWIM_CUDA(ctx, launch_dependent(panel_kernel<false>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
+        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, panel_kernel<false>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
     DWIM_LAUNCHED(ctx);
     return 0;
 }
@@ -171,7 +171,7 @@ int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, u
     if (n == 0 || cols == 0) return 0;
     if (n > I8_MAX_TOKENS) return fail(ctx, DWIM_B200_EINVAL, "int8 panels take at most %d tokens, not %zu", I8_MAX_TOKENS, n);
     dim3 grid((unsigned)((cols + 255) / 256), (unsigned)n);
-    DWIM_CUDA(ctx, launch_dependent(panel_i8_kernel, grid, dim3(256), 0, ctx->stream, x, cols, (int)n, panels));
+    DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, panel_i8_kernel, grid, dim3(256), 0, ctx->stream, x, cols, (int)n, panels));
     DWIM_LAUNCHED(ctx);
     return 0;
 }
