@@ -420,3 +420,53 @@ def test_feed_forward_block_on_one_gpu(dev, oracle, n):
     h = oracle.swiglu("q4_k", gate.data, up.data, inner, hidden, x)
     want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
     assert max_rel_err(got, want) <= 5e-5
+
+
+@pytest.mark.parametrize("n", [1, 2])
+def test_int8_routine_activation_extremes(dev, oracle, n):
+    """One and two tokens of Q4_K go through int8 digit planes with one exponent per
+    256 activations: outliers, zeros, a zero unit, tiny and huge magnitudes."""
+    rng = np.random.default_rng(71 + n)
+    rows, cols = 96, 2048
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    weight = upload(dev, "q4_k", rows, cols, blocks)
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    x[:, 7] = 3.0e4                   # an outlier in the first unit
+    x[:, 256:512] = 0.0               # a unit of zeros
+    x[:, 512:768] *= 1e-30            # tiny
+    x[:, 768:1024] *= 1e20            # huge
+    x[:, 1024:1280:2] = 0.0           # every other one zero
+    x[:, 1300] = -65504.0
+    out = dev.alloc(n * rows)
+    dev.matmul(out, weight, dev.buffer(x))
+    got, want = dev.read(out).reshape(n, rows), oracle.matmul("q4_k", blocks, rows, cols, x)
+    assert np.isfinite(got).all()
+    assert max_rel_err(got, want) <= 2e-5
+
+
+def test_back_to_back_products_see_their_own_inputs(dev, oracle):
+    """Small-M kernels start while the kernel ahead still runs: every product of a
+    chain must still use the input written just before it, and accumulate in order."""
+    rng = np.random.default_rng(83)
+    rows, cols = 640, 1024
+    tensors = [oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)) for _ in range(2)]
+    weights = [upload(dev, "q4_k", rows, cols, t) for t in tensors]
+    xb, acc = dev.alloc(cols), dev.alloc(rows)
+    xs = rng.standard_normal((12, cols)).astype(np.float32)
+    want = np.zeros(rows, np.float32)
+    for i, x in enumerate(xs):
+        dev.write(xb, x)
+        dev.matmul_add(acc, weights[i % 2], xb)        # acc += w . x, twelve times without a sync
+        want = oracle.matmul_add("q4_k", tensors[i % 2], rows, cols, x, want).reshape(rows)
+    assert max_rel_err(dev.read(acc), want) <= 2e-5
+
+
+def test_gemm_above_the_batch_size(dev, oracle):
+    """More tokens than Device::batch() in one call, ragged against every tile size."""
+    rng = np.random.default_rng(89)
+    rows, cols, n = 200, 512, 2049
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    out = dev.alloc(n * rows)
+    dev.matmul(out, upload(dev, "q4_k", rows, cols, blocks), dev.buffer(x))
+    assert max_rel_err(dev.read(out), oracle.matmul("q4_k", blocks, rows, cols, x)) <= 2e-5
