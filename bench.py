@@ -174,6 +174,18 @@ def run_reference(args, fmt, rows, cols, m, act, ffn=False):
     }))
 
 
+def timed_e2e(step, n_steps):
+    """(median, mean) seconds of a step that ends with a blocking copy to the
+    host: the median, because one stall of the host among twenty steps would
+    otherwise decide the number."""
+    times = []
+    for i in range(n_steps):
+        t0 = time.perf_counter()
+        step(i)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), sum(times) / len(times)
+
+
 def headline(fmt, rows, cols, m, seconds):
     """The metric of a step: TFLOP/s for the GEMM sizes, GB/s for the GEMV sizes."""
     if m > 16:
@@ -309,14 +321,11 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
         e2e_step(i)
     if dist:
         dist.barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_s, e2e_mean_s = timed_e2e(e2e_step, e2e_steps)
     if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
+        t = torch.tensor([e2e_s, e2e_mean_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        e2e_s, e2e_mean_s = float(t[0].item()), float(t[1].item())
     _, _, e2e_value = headline(fmt, rows, cols, m, e2e_s)
 
     if rank == 0:
@@ -355,7 +364,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             "config": workload_config(fmt, rows, cols, m, act, world, gather),
             "tok_per_s": m / per_step,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(hx.nbytes),
-                    "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3},
+                    "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3, "ms_per_step_mean": e2e_mean_s * 1e3,
+                    "note": "median over the steps, each timed on the host from the copy in to the copy out"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": roof,
@@ -461,10 +471,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
         e2e_step(i)
     if dist:
         dist.barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(i)
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    e2e_s, _ = timed_e2e(e2e_step, e2e_steps)
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -597,10 +604,7 @@ def run_decoder(args, m):
     def e2e():
         dev.write(x, hx); token(); dev.read(logits, hl)
     e2e()
-    t0 = time.perf_counter()
-    for _ in range(3):
-        e2e()
-    e2e_s = (time.perf_counter() - t0) / 3
+    e2e_s, _ = timed_e2e(lambda i: e2e(), 5)
     pk = peaks()
     achieved = total / seconds / 1e9
     print(json.dumps({

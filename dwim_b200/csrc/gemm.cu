@@ -355,9 +355,15 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = lds32(tmem_slot);
+    // Launched as a programmatic dependent: the next launch on the stream may begin as SMs
+    // free up; here only the packed weights (written by uploads alone) are touched before
+    // griddep_wait(): the activations' producer waits before its first load, the workers
+    // before their first store.
+    griddep_launch();
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
+        griddep_wait();   // the operand comes from the prologue kernel just ahead
         if (lane == 0) {
             for (int u = 0; u < units; u++) {
                 const int ms = u % C::MIN_STAGES;
@@ -541,6 +547,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             if (drains && u > 0) drain(u - 1);
         }
         if (drains) {
+            griddep_wait();   // the kernel ahead may still read or write `out` and `aux`
             drain(units - 1);
             float acc[C::DRAIN_COLS];
 #pragma unroll
@@ -647,7 +654,9 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
         configured[ctx->device & 63] = true;
     }
     dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
-    kern<<<grid, GEMM_THREADS, C::SMEM, ctx->stream>>>(tw, tx, tm, a);
+    const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
+    DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, tm, a));
+    ctx->weights_written = false;
     DWIM_LAUNCHED(ctx);
 #ifdef DWIM_B200_GEMM_TRACE_BUILD
     if (tenv && ++traced == atoi(tenv)) {

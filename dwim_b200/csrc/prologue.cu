@@ -186,6 +186,10 @@ size_t gemm_operand_bytes(size_t cols, size_t ncols) {
 template <bool ALIGNED>   // whether x is 16-byte aligned (a wrapped caller's pointer need not be)
 __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *__restrict__ x, size_t cols, size_t units, int split,
                                                            __half *__restrict__ x16, __half *__restrict__ means) {
+    // as the small-M prologues: let the product's kernel begin (it streams weights first),
+    // wait for the kernel ahead, which may still read the operand or write x
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.y, k = threadIdx.x;
     const size_t u = (size_t)blockIdx.x * 4 + (k >> 6);
     if (u >= units) return;                           // whole 64-thread groups leave together
@@ -246,10 +250,13 @@ int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols
     if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one operand build: %zu", n);
     const size_t units = cols / 256, ncols = n * (split ? 2 : 1);
     dim3 grid((unsigned)((units + 3) / 4), (unsigned)n);
+    const bool dependent = !ctx->weights_written;
     if (reinterpret_cast<uintptr_t>(x) % 16 == 0)
-        gemm_operand_kernel<true><<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
+        DWIM_CUDA(ctx, launch_dependent(dependent, gemm_operand_kernel<true>, grid, dim3(256), 0, ctx->stream, x, cols, units, split,
+                                        out, out + ncols * cols));
     else
-        gemm_operand_kernel<false><<<grid, 256, 0, ctx->stream>>>(x, cols, units, split, out, out + ncols * cols);
+        DWIM_CUDA(ctx, launch_dependent(dependent, gemm_operand_kernel<false>, grid, dim3(256), 0, ctx->stream, x, cols, units, split,
+                                        out, out + ncols * cols));
     DWIM_LAUNCHED(ctx);
     return 0;
 }
