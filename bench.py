@@ -129,7 +129,13 @@ def algorithmic_bytes(fmt, rows, cols, m):
 
 
 # ---------------------------------------------------------------------------------------
-def run_reference(args, fmt, rows, cols, m, act, ffn=False):
+# weights of one decoder pass (config 4) over the weights of one [17408, 5120] matrix:
+# 64 x 3 FFN matrices + 16 x (12288 + 2 x 1024 + 6144) + 48 x (10240 + 6144 + 6144) rows of 5120,
+# and the Q6_K head counted by its bytes (210 against 144 per block)
+DECODER_OVER_FFN_MATRIX = (64 * 3 * 17408 + 16 * (12288 + 2048 + 6144) + 48 * (10240 + 6144 + 6144) + 151936 * 210 / 144) / 17408
+
+
+def run_reference(args, fmt, rows, cols, m, act, ffn=False, decoder=False):
     """The reference's CPU path (restated in oracle/) on the host cores.  For the
     feed-forward block: one [rows, cols] product timed, times three (gate, up and
     down hold the same number of weights; the SiLU is noise beside them)."""
@@ -163,11 +169,17 @@ def run_reference(args, fmt, rows, cols, m, act, ffn=False):
         full *= 3
         metric, unit, value = "q4k_ffn_tok_per_s", "tok/s", m / full
         sample += ", times three for gate, up and down"
+    if decoder:
+        full *= DECODER_OVER_FFN_MATRIX
+        metric, unit, value = "decode_matmul_tok_per_s", "tok/s", m / full
+        sample += f", times {DECODER_OVER_FFN_MATRIX:.1f} for the weights of the whole pass"
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": full * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": ffn_config(rows, cols, m, act, args.gpus) if ffn else workload_config(fmt, rows, cols, m, act, args.gpus),
+        "config": (ffn_config(rows, cols, m, act, args.gpus) if ffn else
+                   {"workload": f"all matrix products of one decoder pass, {m} token(s): 64 layers Q4_K + Q6_K head", "tokens": m}
+                   if decoder else workload_config(fmt, rows, cols, m, act, args.gpus)),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tok_per_s": m / full,
@@ -668,7 +680,7 @@ def main():
     if args.m:
         m = args.m
     if args.impl == "reference":
-        run_reference(args, fmt, rows, cols, m, act, ffn=args.workload == "c5")
+        run_reference(args, fmt, rows, cols, m, act, ffn=args.workload == "c5", decoder=args.workload == "c4")
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
