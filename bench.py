@@ -433,8 +433,16 @@ def run_ffn(args, fmt, inner, hidden, m, act):
     my_bytes = gate.data.size + up.data.size + down.data.size
     copies = int(min(24, max(2, -(-3 * L2_BYTES // my_bytes))))
     blocks = [shard.ShardedFFN(dev, gate, up, down, 0, 1) for _ in range(copies)]   # already this rank's shard
+    # a few tokens: the partial sums through the library's all-reduce over peer memory (--nccl: through NCCL)
+    peer, reduction = None, "NCCL all-reduce"
+    if world > 1 and m * hidden <= 16 * 1024 and not args.nccl:   # measured: at 8 tokens (160 KB) NCCL is level with it
+        try:
+            peer = shard.PeerReduce(dev, rank, world, 16 * 1024)
+            reduction = "peer-store all-reduce (library kernel over IPC-mapped mailboxes)"
+        except Exception as exc:   # noqa: BLE001 - NCCL takes over
+            reduction = f"NCCL all-reduce (peer set-up failed: {exc!r})"[:200]
     for blk in blocks:
-        blk.world, blk.rank = world, rank
+        blk.world, blk.rank, blk.peer = world, rank, peer
     x = np.random.default_rng(6).standard_normal((m, hidden), dtype=np.float32)
     bits = None
     if act == "bf16":
@@ -504,7 +512,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
             "metric": "q4k_ffn_tok_per_s", "value": m / per_step, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16/int8 (exact integer weights), f32 accumulate", "data": "synthetic",
-            "config": ffn_config(inner, hidden, m, act, world),
+            "config": dict(ffn_config(inner, hidden, m, act, world), reduction=reduction if world > 1 else "none"),
             "e2e": {"value": m / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(hx.nbytes),
                     "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3},
             "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roof, "device": dev.name(),
@@ -673,6 +681,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--m", "--tokens", dest="m", type=int, default=None, help="tokens per step (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--nccl", action="store_true", help="c5, N > 1: NCCL for the partial sums even for a few tokens")
     ap.add_argument("--gather", action="store_true",
                     help="N > 1: all-gather the row-sharded result onto every rank inside the step")
     args = ap.parse_args()

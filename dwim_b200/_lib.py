@@ -54,6 +54,10 @@ SIGNATURES = {
     "dwim_b200_matmul_static": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "dwim_b200_shard_rows": (C.c_int, [_sz, C.c_int, C.c_int, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "dwim_b200_gather_rows": (C.c_int, [_vp, _vp, _vp, _sz, _sz, C.c_int, _sz]),
+    "dwim_b200_peer_handle_bytes": (_sz, []),
+    "dwim_b200_peer_create": (C.c_int, [_vp, C.c_int, C.c_int, _sz, _vp, _sz]),
+    "dwim_b200_peer_connect": (C.c_int, [_vp, _vp, _sz]),
+    "dwim_b200_peer_allreduce": (C.c_int, [_vp, _vp, _sz]),
 }
 
 _lib = None

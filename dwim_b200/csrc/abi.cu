@@ -83,6 +83,7 @@ int dwim_b200_close(dwim_b200_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     gemm_release(ctx);
+    peer_release(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->status) cudaFree(ctx->status);

@@ -56,6 +56,8 @@ struct dwim_b200_ctx {
     // (an upload's repack): that launch must be an ordinary one, because a
     // programmatic dependent streams weights before it waits for the kernels ahead.
     bool weights_written = false;
+    // the peer all-reduce's mailbox and mappings (peer.cu), created on request
+    void *peer_state = nullptr;
 };
 
 namespace dwim {
@@ -140,6 +142,7 @@ enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 bool gemv_takes_i8(const WeightView &w, size_t n);
 int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
                   int epilogue, const WeightView *up = nullptr);
+void peer_release(dwim_b200_ctx *ctx);
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
                size_t t0, int split, float *out, const float *aux, int epilogue);
 int gemv_max_tokens(int split);

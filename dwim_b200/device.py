@@ -174,6 +174,25 @@ class B200:
     def gather_rows(self, out: Buffer, parts: Buffer, n: int, rows: int, world: int, align: int) -> None:
         self._check(self._L.dwim_b200_gather_rows(self._ctx, out._h, parts._h, n, rows, world, align))
 
+    # -- the small all-reduce over peer memory (one process per GPU) ------------
+    def peer_create(self, world: int, rank: int, cap: int) -> bytes:
+        """Allocates this rank's mailbox for vectors of up to ``cap`` floats;
+        returns its inter-process handle, to be exchanged among the ranks."""
+        nb = int(self._L.dwim_b200_peer_handle_bytes())
+        h = C.create_string_buffer(nb)
+        self._check(self._L.dwim_b200_peer_create(self._ctx, world, rank, cap, h, nb))
+        return h.raw
+
+    def peer_connect(self, handles) -> None:
+        """Maps the ranks' mailboxes; ``handles`` in rank order."""
+        nb = int(self._L.dwim_b200_peer_handle_bytes())
+        blob = b"".join(bytes(h)[:nb].ljust(nb, b"\0") for h in handles)
+        self._check(self._L.dwim_b200_peer_connect(self._ctx, blob, nb))
+
+    def peer_allreduce(self, buf: Buffer, n: int | None = None) -> None:
+        """The first ``n`` floats of ``buf`` become their sum over the ranks."""
+        self._check(self._L.dwim_b200_peer_allreduce(self._ctx, buf._h, len(buf) if n is None else n))
+
     @property
     def stream(self) -> int:
         return int(self._L.dwim_b200_stream(self._ctx) or 0)

@@ -101,7 +101,8 @@ class RowSharded:
 # projection).  gate and up are split by output rows, down by the same indices
 # along its K, so the intermediate of a rank is exactly the K slice its part
 # of down multiplies and never leaves the GPU; the ranks' partial sums of
-# ``out`` are added by one all-reduce.  The cuts fall on multiples of 256 rows:
+# ``out`` are added by one all-reduce (NCCL, or for a few tokens the library's own
+# over peer memory, ``PeerReduce``).  The cuts fall on multiples of 256 rows:
 # whole blocks of down's rows (the k-quant formats pack 256 weights of K).
 
 FFN_ALIGN = 256
@@ -122,13 +123,34 @@ def ffn_shard(gate: Tensor, up: Tensor, down: Tensor, rank: int, world: int):
     return gate.slice_rows(b, e), up.slice_rows(b, e), down.select_column_groups(FFN_ALIGN, groups)
 
 
+class PeerReduce:
+    """The library's small all-reduce over peer memory (``B200.peer_allreduce``),
+    set up for a process group: every rank creates its mailbox, the handles
+    travel through ``torch.distributed`` (any backend), every rank maps its
+    peers'.  One per device; vectors of up to ``cap`` floats."""
+
+    def __init__(self, dev: B200, rank: int, world: int, cap: int, group=None):
+        import torch.distributed as dist
+        self.dev, self.cap = dev, cap
+        mine = dev.peer_create(world, rank, cap)
+        handles = [None] * world
+        dist.all_gather_object(handles, mine, group=group)
+        dev.peer_connect(handles)
+        dist.barrier(group=group)          # nobody writes before everybody has mapped
+
+    def __call__(self, buf, n: int) -> None:
+        self.dev.peer_allreduce(buf, n)
+
+
 class ShardedFFN:
     """The feed-forward block over the ranks of a process group (one process
     per GPU).  ``forward`` leaves the block's full output on every rank."""
 
-    def __init__(self, dev: B200, gate: Tensor, up: Tensor, down: Tensor, rank: int = 0, world: int = 1, group=None):
+    def __init__(self, dev: B200, gate: Tensor, up: Tensor, down: Tensor, rank: int = 0, world: int = 1, group=None,
+                 peer: PeerReduce | None = None):
         import torch
         self.dev, self.rank, self.world, self.group = dev, rank, world, group
+        self.peer = peer                   # sums of up to peer.cap floats go through it instead of NCCL
         self.hidden, self.inner = gate.cols, gate.rows
         g, u, d = ffn_shard(gate, up, down, rank, world)
         self.my_inner = g.rows
@@ -166,7 +188,10 @@ class ShardedFFN:
             with self._torch.cuda.stream(self._stream):
                 out_t.zero_()
         if self.world > 1:
-            import torch.distributed as dist
-            with self._torch.cuda.stream(self._stream):
-                dist.all_reduce(out_t, group=self.group)
+            if self.peer is not None and n * self.hidden <= self.peer.cap:
+                self.peer(out, n * self.hidden)
+            else:
+                import torch.distributed as dist
+                with self._torch.cuda.stream(self._stream):
+                    dist.all_reduce(out_t, group=self.group)
         return out

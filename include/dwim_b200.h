@@ -181,6 +181,25 @@ DWIM_B200_API int dwim_b200_shard_rows(size_t rows, int rank, int world, size_t 
 DWIM_B200_API int dwim_b200_gather_rows(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *parts,
                                         size_t n, size_t rows, int world, size_t align);
 
+/* ---- a small all-reduce over peer memory ------------------------------------
+ * New (the reference engine is single-GPU): the sum of the ranks' partial
+ * results of a K-sharded product (the down projection of a tensor-parallel
+ * feed-forward block) for a few tokens, where a library collective's latency
+ * exceeds the product's time.  One process per GPU.  peer_create allocates this
+ * rank's mailbox (slots of `cap` floats) and writes its inter-process handle
+ * (dwim_b200_peer_handle_bytes() bytes) to `handle`; the caller exchanges the
+ * handles by its own means and passes all `world` of them, in rank order and
+ * `handle_bytes` apart, to peer_connect.  peer_allreduce then replaces the first
+ * n floats of `buf` on every rank by their sum over the ranks, added in rank
+ * order (the same bits everywhere).  Every rank must make the same calls in the
+ * same order; a rank that waits for its peers longer than the library's wait
+ * limit gives up, and the next sync reports DWIM_B200_ETIMEOUT. */
+DWIM_B200_API size_t dwim_b200_peer_handle_bytes(void);
+DWIM_B200_API int dwim_b200_peer_create(dwim_b200_ctx *ctx, int world, int rank, size_t cap, void *handle,
+                                        size_t handle_bytes);
+DWIM_B200_API int dwim_b200_peer_connect(dwim_b200_ctx *ctx, const void *handles, size_t handle_bytes);
+DWIM_B200_API int dwim_b200_peer_allreduce(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t n);
+
 #ifdef __cplusplus
 }
 #endif
