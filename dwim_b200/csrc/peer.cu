@@ -60,6 +60,9 @@ __device__ __forceinline__ uint32_t *flag_of(uint8_t *box, const PeerArgs &a, in
 }
 
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerArgs a) {
+    // a programmatic dependent: the vector comes from the product just ahead
+    dwim::griddep_launch();
+    dwim::griddep_wait();
     const size_t chunk = blockIdx.x, first = chunk * PEER_CHUNK;
     const int set = a.epoch & 1;
     // 1. this chunk of the local vector into slot `rank` of every mailbox
@@ -181,7 +184,7 @@ extern "C" int dwim_b200_peer_allreduce(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
     for (int r = 0; r < p->world; r++) a.box[r] = p->box[r];
     a.status = ctx->status;
     const unsigned grid = (unsigned)((n + PEER_CHUNK - 1) / PEER_CHUNK);
-    peer_allreduce_kernel<<<grid, PEER_THREADS, 0, ctx->stream>>>(a);
+    DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, peer_allreduce_kernel, dim3(grid), dim3(PEER_THREADS), 0, ctx->stream, a));
     DWIM_LAUNCHED(ctx);
     buf->shadow_kind = SHADOW_NONE;
     buf->bf16_exact = false;
