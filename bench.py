@@ -541,47 +541,79 @@ def run_decoder(args, m):
     the products (norms, attention, rope, ...) is not on this path and not run;
     an input counts as rewritten wherever the engine would have rewritten it."""
     import torch
-    from dwim_b200 import B200, row_bytes
+    from dwim_b200 import B200, row_bytes, shard, shard_rows
 
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        raise SystemExit("the decoder schedule runs on one GPU")
-    torch.cuda.set_device(0)
-    dev = B200(0)
+    # N > 1: tensor parallel.  Products whose output feeds a per-head or per-row step (q, k, v, qkv,
+    # z, gate, up, the head) are split by rows and their results stay on the rank; the two that
+    # close a sub-layer (o / out and down) are split along K the same way and their partial sums
+    # are added over the ranks: two reductions per layer, through the library's all-reduce over
+    # peer memory while they are small (NCCL otherwise).
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = B200(local)
     rng = np.random.default_rng(4)
-    hidden, inner, attn = 5120, 17408, 6144
+    hidden, inner, attn, vocab = 5120, 17408, 6144, 151936
 
     def host(fmt, rows, cols):
         return dev.quantize(fmt, 0.02 * rng.standard_normal((rows, cols), dtype=np.float32))
-    shapes = {"qg": (12288, hidden), "kv": (1024, hidden), "o": (hidden, attn), "qkv": (10240, hidden), "z": (attn, hidden),
-              "gate": (inner, hidden), "down": (hidden, inner)}
+    span = lambda n, align: (lambda be: be[1] - be[0])(shard_rows(n, rank, world, align))
+    my_inner, my_attn, my_vocab = span(inner, 256), span(attn, 256), span(vocab, 16)
+    shapes = {"qg": (span(12288, 16), hidden), "kv": (span(1024, 16), hidden), "o": (hidden, my_attn), "qkv": (span(10240, 16), hidden),
+              "z": (my_attn, hidden), "gate": (my_inner, hidden), "down": (hidden, my_inner)}
     proto = {k: host("q4_k", *v) for k, v in shapes.items()}
-    head = dev.upload(host("q6_k", 151936, hidden))
-    layers, total = [], 151936 * row_bytes("q6_k", hidden)
+    head = dev.upload(host("q6_k", my_vocab, hidden))
+    layers, total = [], my_vocab * row_bytes("q6_k", hidden)
     for l in range(64):
         names = ["qg", "kv", "kv", "o"] if l % 4 == 3 else ["qkv", "z", "o"]
         names += ["gate", "gate", "down"]
         layers.append([dev.upload(proto[n]) for n in names])
         total += sum(proto[n].data.size for n in names)
     x = dev.buffer(rng.standard_normal((m, hidden), dtype=np.float32))        # the residual stream's normalized copy
-    a = dev.buffer(rng.standard_normal((m, attn), dtype=np.float32))          # attention output
-    res = dev.alloc(m * hidden)
-    outs = {r: dev.alloc(m * r) for r in (12288, 1024, 10240, attn)}
-    h, scratch, logits = dev.alloc(m * inner), dev.alloc(m * inner), dev.alloc(m * 151936)
+    a = dev.buffer(rng.standard_normal((m, my_attn), dtype=np.float32))       # this rank's heads' attention output
+    outs = {k: dev.alloc(m * shapes[k][0]) for k in ("qg", "kv", "qkv", "z")}
+    h, scratch, logits = dev.alloc(m * my_inner), dev.alloc(m * my_inner), dev.alloc(m * my_vocab)
+    part_t = torch.zeros(m * hidden, dtype=torch.float32, device="cuda")      # a closing product's result / partial sums
+    part = dev.wrap(part_t.data_ptr(), m * hidden)
+    ext = torch.cuda.ExternalStream(dev.stream)
+    peer, reduction = None, "none"
+    if world > 1:
+        reduction = "NCCL all-reduce"
+        if m * hidden <= 16 * 1024 and not args.nccl:
+            try:
+                peer = shard.PeerReduce(dev, rank, world, 16 * 1024)
+                reduction = "peer-store all-reduce (library kernel over IPC-mapped mailboxes)"
+            except Exception as exc:   # noqa: BLE001 - NCCL takes over
+                reduction = f"NCCL all-reduce (peer set-up failed: {exc!r})"[:200]
+
+    def reduce_part():
+        if world == 1:
+            return
+        if peer is not None:
+            peer(part, m * hidden)
+        else:
+            with torch.cuda.stream(ext):
+                dist.all_reduce(part_t)
 
     def token():
         for l, w in enumerate(layers):
             dev.resize(x, m * hidden)                       # the layer's normalized input
             if l % 4 == 3:
-                dev.matmul(outs[12288], w[0], x); dev.matmul(outs[1024], w[1], x); dev.matmul(outs[1024], w[2], x)
-                dev.resize(a, m * attn); dev.matmul_add(res, w[3], a)
+                dev.matmul(outs["qg"], w[0], x); dev.matmul(outs["kv"], w[1], x); dev.matmul(outs["kv"], w[2], x)
+                dev.resize(a, m * my_attn); dev.matmul(part, w[3], a); reduce_part()
                 f = w[4:]
             else:
-                dev.matmul(outs[10240], w[0], x); dev.matmul(outs[attn], w[1], x)
-                dev.resize(a, m * attn); dev.matmul_add(res, w[2], a)
+                dev.matmul(outs["qkv"], w[0], x); dev.matmul(outs["z"], w[1], x)
+                dev.resize(a, m * my_attn); dev.matmul(part, w[2], a); reduce_part()
                 f = w[3:]
             dev.resize(x, m * hidden)                       # normalized again before the feed-forward block
             dev.swiglu(h, f[0], f[1], x, scratch)
-            dev.matmul_add(res, f[2], h)
+            dev.matmul(part, f[2], h); reduce_part()
         dev.resize(x, m * hidden)
         dev.matmul(logits, head, x)
 
@@ -589,18 +621,27 @@ def run_decoder(args, m):
         token()
     dev.sync()
     steps = max(3, min(args.steps, 20))
-    with ClockSampler(0) as clocks:
+    with ClockSampler(local) as clocks:
+        if dist:
+            torch.cuda.synchronize()
+            dist.barrier()
         launches0 = dev.launches
         dev.timer_begin()
         for _ in range(steps):
             token()
         seconds = dev.timer_end() / 1e3 / steps
         launches = (dev.launches - launches0) // steps
+        if dist:
+            torch.cuda.synchronize()
+            t = torch.tensor([seconds], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            seconds = float(t.item())
     # the same pass replayed as one CUDA graph (captured from the library's stream; everything
     # it allocates lazily exists by now): what is left of the time when the host issues nothing
     graph = None
     try:
-        ext = torch.cuda.ExternalStream(dev.stream)
+        if world > 1:
+            raise RuntimeError("one GPU only: the reductions are not captured")
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=ext):
             token()
@@ -620,20 +661,32 @@ def run_decoder(args, m):
     dev.sync()
     # end to end: the token's embedding row in, the logits out
     hx = torch.empty(m * hidden, dtype=torch.float32, pin_memory=True).numpy(); hx[:] = 0.5
-    hl = torch.empty(m * 151936, dtype=torch.float32, pin_memory=True).numpy()
+    hl = torch.empty(m * my_vocab, dtype=torch.float32, pin_memory=True).numpy()
     def e2e():
         dev.write(x, hx); token(); dev.read(logits, hl)
     e2e()
+    if dist:
+        dist.barrier()
     e2e_s, _ = timed_e2e(lambda i: e2e(), 5)
+    if dist:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
     pk = peaks()
     achieved = total / seconds / 1e9
+    if rank != 0:
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     print(json.dumps({
-        "metric": "decode_matmul_tok_per_s", "value": m / seconds, "unit": "tok/s", "n_gpus": 1, "steps": steps,
+        "metric": "decode_matmul_tok_per_s", "value": m / seconds, "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": max(2, args.warmup // 2), "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8/f16 (exact integer weights), f32 accumulate", "data": "synthetic",
         "config": {"workload": f"all matrix products of one decoder pass, {m} token(s): 64 layers Q4_K + Q6_K head, "
                                f"{total / 1e9:.2f} GB of weights resident, each read once per pass",
-                   "tokens": m, "products_per_pass": 16 * 7 + 48 * 6 + 1, "l2": "every layer has its own weights in HBM"},
+                   "tokens": m, "products_per_pass": 16 * 7 + 48 * 6 + 1, "l2": "every layer has its own weights in HBM",
+                   "sharding": (f"tensor parallel over {world}: q/k/v-type products, gate/up and the head by rows, o/out and down "
+                                f"along K; two reductions per layer: {reduction}; weight GB are this rank's") if world > 1 else "none"},
         "e2e": {"value": m / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(hx.nbytes), "d2h_bytes_per_step": int(hl.nbytes),
                 "ms_per_step": e2e_s * 1e3},
         "gpu_launches": int(launches), "clocks": clocks.summary(), "graph_replay": graph,
@@ -642,6 +695,10 @@ def run_decoder(args, m):
                      "note": "weight bytes of the whole pass over its time: all kernels, prologues and launch gaps included"},
         "device": dev.name(),
     }))
+    sys.stdout.flush()
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def cpu_baseline(fmt, rows, cols, m, act):
