@@ -591,9 +591,16 @@ def run_decoder(args, m):
             except Exception as exc:   # noqa: BLE001 - NCCL takes over
                 reduction = f"NCCL all-reduce (peer set-up failed: {exc!r})"[:200]
 
-    def reduce_part():
+    def closing(w, src):
+        """o / out and down: on one GPU the engine's matmul_add into the residual stream;
+        tensor parallel the rank's partial product, summed over the ranks."""
         if world == 1:
-            return
+            dev.matmul_add(part, w, src)
+        else:
+            dev.matmul(part, w, src)
+            reduce_part()
+
+    def reduce_part():
         if peer is not None:
             peer(part, m * hidden)
         else:
@@ -605,15 +612,15 @@ def run_decoder(args, m):
             dev.resize(x, m * hidden)                       # the layer's normalized input
             if l % 4 == 3:
                 dev.matmul(outs["qg"], w[0], x); dev.matmul(outs["kv"], w[1], x); dev.matmul(outs["kv"], w[2], x)
-                dev.resize(a, m * my_attn); dev.matmul(part, w[3], a); reduce_part()
+                dev.resize(a, m * my_attn); closing(w[3], a)
                 f = w[4:]
             else:
                 dev.matmul(outs["qkv"], w[0], x); dev.matmul(outs["z"], w[1], x)
-                dev.resize(a, m * my_attn); dev.matmul(part, w[2], a); reduce_part()
+                dev.resize(a, m * my_attn); closing(w[2], a)
                 f = w[3:]
             dev.resize(x, m * hidden)                       # normalized again before the feed-forward block
             dev.swiglu(h, f[0], f[1], x, scratch)
-            dev.matmul(part, f[2], h); reduce_part()
+            closing(f[2], h)
         dev.resize(x, m * hidden)
         dev.matmul(logits, head, x)
 
