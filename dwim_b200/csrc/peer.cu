@@ -16,7 +16,7 @@
 //      word and goes on, so that the kernel always ends),
 //   4. adds the world slots' chunk in rank order (the same order, hence the
 //      same bits, on every rank) into the local vector.
-// No rank reads another's memory, nothing is multicast, and a slot is reused
+// No rank reads another's memory (plain one-to-one stores only), and a slot is reused
 // only two calls later: a rank can be writing call e+1 while a slower peer
 // still adds up call e, but not call e+2, which needs that peer's flag of e+1.
 #include "common.cuh"
