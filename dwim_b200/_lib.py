@@ -22,6 +22,7 @@ _f32p, _u16p = C.POINTER(C.c_float), C.POINTER(C.c_uint16)
 # name -> (restype, argtypes); every symbol the header declares
 SIGNATURES = {
     "dwim_b200_open": (C.c_int, [C.c_int, C.POINTER(_vp)]),
+    "dwim_b200_open_on_stream": (C.c_int, [C.c_int, _vp, C.POINTER(_vp)]),
     "dwim_b200_close": (C.c_int, [_vp]),
     "dwim_b200_last_error": (C.c_char_p, [_vp]),
     "dwim_b200_name": (C.c_int, [_vp, C.c_char_p, _sz]),
@@ -36,6 +37,7 @@ SIGNATURES = {
     "dwim_b200_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp)]),
     "dwim_b200_wrap": (C.c_int, [_vp, _vp, _sz, C.POINTER(_vp)]),
     "dwim_b200_resize": (C.c_int, [_vp, _vp, _sz]),
+    "dwim_b200_touch": (C.c_int, [_vp, _vp]),
     "dwim_b200_write": (C.c_int, [_vp, _vp, _vp, _sz]),
     "dwim_b200_write_bf16": (C.c_int, [_vp, _vp, _vp, _sz]),
     "dwim_b200_read": (C.c_int, [_vp, _vp, _vp, _sz]),
@@ -52,6 +54,10 @@ SIGNATURES = {
     "dwim_b200_matmul_add": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "dwim_b200_swiglu": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "dwim_b200_matmul_static": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
+    "dwim_b200_shared_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp), _vp, _sz]),
+    "dwim_b200_shared_connect": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _sz]),
+    "dwim_b200_matmul_gather": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _sz]),
+    "dwim_b200_shared_barrier": (C.c_int, [_vp, _vp]),
     "dwim_b200_shard_rows": (C.c_int, [_sz, C.c_int, C.c_int, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "dwim_b200_gather_rows": (C.c_int, [_vp, _vp, _vp, _sz, _sz, C.c_int, _sz]),
     "dwim_b200_peer_handle_bytes": (_sz, []),

@@ -22,16 +22,14 @@ static constexpr size_t SMALL_M_MAX = 16;
 
 namespace dwim {
 // gemm.cu
-bool gemm_available();
 bool gemm_supports(const WeightView &w);
-int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue);
-void gemm_release(dwim_b200_ctx *ctx);
 }  // namespace dwim
 
 extern "C" {
 
-int dwim_b200_open(int device, dwim_b200_ctx **out) {
+static int open_impl(int device, cudaStream_t adopt, bool adopting, dwim_b200_ctx **out) {
     if (!out) return DWIM_B200_EINVAL;
     *out = nullptr;
     int count = 0;
@@ -64,13 +62,26 @@ int dwim_b200_open(int device, dwim_b200_ctx **out) {
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     snprintf(ctx->name, sizeof ctx->name, "%s", prop.name);
-    bool ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess &&
-              cudaEventCreate(&ctx->ev0) == cudaSuccess && cudaEventCreate(&ctx->ev1) == cudaSuccess &&
-              cudaMalloc(&ctx->status, sizeof(uint32_t)) == cudaSuccess &&
-              cudaMallocHost(&ctx->status_host, sizeof(uint32_t)) == cudaSuccess &&
-              cudaMemset(ctx->status, 0, sizeof(uint32_t)) == cudaSuccess;
+    bool ok = true;
+    if (adopting) {
+        ctx->stream = adopt;
+        ctx->stream_owned = false;
+    } else {
+        ok = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) == cudaSuccess;
+    }
+    ok = ok && cudaEventCreate(&ctx->ev0) == cudaSuccess && cudaEventCreate(&ctx->ev1) == cudaSuccess &&
+         cudaMalloc(&ctx->status, sizeof(uint32_t)) == cudaSuccess &&
+         cudaMallocHost(&ctx->status_host, sizeof(uint32_t)) == cudaSuccess &&
+         cudaMemset(ctx->status, 0, sizeof(uint32_t)) == cudaSuccess &&
+         // the fixed scratch array of dwim_b200_matmul_static: its device address is looked up here,
+         // with the device current and before anything could be capturing the stream
+         static_scratch_prepare(ctx) == 0;
     if (!ok) {
-        snprintf(g_open_error, sizeof g_open_error, "creating the context: %s", cudaGetErrorString(cudaGetLastError()));
+        cudaError_t last = cudaGetLastError();
+        if (last != cudaSuccess || !ctx->err[0])
+            snprintf(g_open_error, sizeof g_open_error, "creating the context: %s", cudaGetErrorString(last));
+        else
+            snprintf(g_open_error, sizeof g_open_error, "creating the context: %s", ctx->err);
         dwim_b200_close(ctx);
         return DWIM_B200_ECUDA;
     }
@@ -78,17 +89,22 @@ int dwim_b200_open(int device, dwim_b200_ctx **out) {
     return 0;
 }
 
+int dwim_b200_open(int device, dwim_b200_ctx **out) { return open_impl(device, nullptr, false, out); }
+
+int dwim_b200_open_on_stream(int device, void *cuda_stream, dwim_b200_ctx **out) {
+    return open_impl(device, static_cast<cudaStream_t>(cuda_stream), true, out);
+}
+
 int dwim_b200_close(dwim_b200_ctx *ctx) {
     if (!ctx) return DWIM_B200_EINVAL;
     cudaSetDevice(ctx->device);
-    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-    gemm_release(ctx);
+    if (ctx->stream || !ctx->stream_owned) cudaStreamSynchronize(ctx->stream);
     peer_release(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
-    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->stream && ctx->stream_owned) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return 0;
 }
@@ -199,6 +215,13 @@ int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t len) {
     return 0;
 }
 
+int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    if (!ctx || !buf) return DWIM_B200_EINVAL;
+    buf->shadow_kind = SHADOW_NONE;
+    buf->bf16_exact = false;
+    return 0;
+}
+
 int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len) {
     if (!ctx || !buf || (!data && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == buf->len, DWIM_B200_EINVAL, "write of %zu floats to a buffer of %zu", len, buf->len);
@@ -243,6 +266,7 @@ int dwim_b200_read(dwim_b200_ctx *ctx, const dwim_b200_buffer *buf, float *out, 
 int dwim_b200_buffer_free(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     cudaStreamSynchronize(ctx->stream);
+    if (buf->sh_world) shared_release(buf);
     if (buf->owned && buf->data) cudaFree(buf->data);
     if (buf->shadow) cudaFree(buf->shadow);
     delete buf;
@@ -291,9 +315,10 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
         } else {
             e = cudaMalloc(&staging, bytes);
             if (e == cudaSuccess) e = cudaMemcpyAsync(staging, blocks, bytes, cudaMemcpyHostToDevice, ctx->stream);
-            if (e == cudaSuccess)
+            if (e == cudaSuccess) {
                 rc = repack_to_device(ctx, fmt, rows, cols, staging, (uint8_t *)w->quants_alloc, (__half *)w->scales_alloc);
                 ctx->weights_written = true;
+            }
         }
     }
     // The host memory is the caller's again when this returns.
@@ -410,18 +435,18 @@ static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size
     return 0;
 }
 
-static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b200_weight *w, dwim_b200_buffer *x,
+static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const dwim_b200_weight *w, dwim_b200_buffer *x,
                    const float *aux, int epilogue, const char *what) {
     const WeightView &v = w->v;
     REQUIRE(ctx, x->len % v.cols == 0, DWIM_B200_EINVAL, "%s: input of %zu floats is not rows of %zu", what, x->len, v.cols);
     size_t n = x->len / v.cols;
-    REQUIRE(ctx, out_len == n * v.rows, DWIM_B200_EINVAL, "%s: output of %zu floats for %zu tokens of %zu rows", what,
-            out_len, n, v.rows);
+    REQUIRE(ctx, out_len == n * out.pitch, DWIM_B200_EINVAL, "%s: output of %zu floats for %zu tokens of %zu rows", what,
+            out_len, n, out.pitch);
     if (n == 0 || v.rows == 0) return 0;
-    REQUIRE(ctx, out != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
+    REQUIRE(ctx, out.dst[0] != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
     // bf16 activations are exact in one f16 column; f32 ones travel as two
     // (value and rounding remainder), summed again in the epilogue.
-    if (n > SMALL_M_MAX && gemm_available() && gemm_supports(v)) {
+    if (n > SMALL_M_MAX && gemm_supports(v)) {
         int split = x->bf16_exact ? 0 : 1;
         int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
         if (rc) return rc;
@@ -449,7 +474,27 @@ static int product(dwim_b200_ctx *ctx, float *out, size_t out_len, const dwim_b2
 
 int dwim_b200_matmul(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w, dwim_b200_buffer *x) {
     if (!ctx || !out || !w || !x) return DWIM_B200_EINVAL;
-    int rc = product(ctx, out->data, out->len, w, x, nullptr, EPI_STORE, "matmul");
+    int rc = product(ctx, out_local(out->data, w->v.rows), out->len, w, x, nullptr, EPI_STORE, "matmul");
+    out->shadow_kind = SHADOW_NONE;
+    out->bf16_exact = false;
+    return rc;
+}
+
+int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w, dwim_b200_buffer *x,
+                            size_t row_begin, size_t total_rows) {
+    if (!ctx || !out || !w || !x) return DWIM_B200_EINVAL;
+    REQUIRE(ctx, out->sh_world >= 1, DWIM_B200_EINVAL, "matmul_gather: the output is not a connected shared buffer");
+    REQUIRE(ctx, row_begin + w->v.rows <= total_rows, DWIM_B200_EINVAL, "matmul_gather: rows [%zu, %zu) of %zu", row_begin,
+            row_begin + w->v.rows, total_rows);
+    OutSpec o{};
+    o.world = out->sh_world;
+    o.pitch = total_rows;
+    o.row0 = row_begin;
+    // this rank's copy first: the fused add / SwiGLU forms read it; the peers' follow
+    o.dst[0] = out->data;
+    for (int r = 0, k = 1; r < out->sh_world; r++)
+        if (r != out->sh_rank) o.dst[k++] = out->sh_peer[r];
+    int rc = product(ctx, o, out->len, w, x, nullptr, EPI_STORE, "matmul_gather");
     out->shadow_kind = SHADOW_NONE;
     out->bf16_exact = false;
     return rc;
@@ -459,7 +504,7 @@ int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, const dwim_b20
                          dwim_b200_buffer *scratch) {
     if (!ctx || !x || !w || !input) return DWIM_B200_EINVAL;
     if (scratch) REQUIRE(ctx, scratch->len == x->len, DWIM_B200_EINVAL, "matmul_add: scratch of %zu for x of %zu", scratch->len, x->len);
-    int rc = product(ctx, x->data, x->len, w, input, nullptr, EPI_ADD, "matmul_add");
+    int rc = product(ctx, out_local(x->data, w->v.rows), x->len, w, input, nullptr, EPI_ADD, "matmul_add");
     x->shadow_kind = SHADOW_NONE;
     x->bf16_exact = false;
     return rc;
@@ -479,12 +524,12 @@ int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_
         // one and two tokens: both matrices in one launch, the activation applied where the two sums meet
         rc = ensure_shadow(ctx, x, SHADOW_PANEL_I8, gate->v.cols, 0);
         if (rc == 0)
-            rc = gemv_small_i8(ctx, gate->v, (const uint8_t *)x->shadow, (int)n, out->data, nullptr, EPI_STORE, &up->v);
+            rc = gemv_small_i8(ctx, gate->v, (const uint8_t *)x->shadow, (int)n, out_local(out->data, gate->v.rows), nullptr, EPI_STORE, &up->v);
     } else {
         // up . x into scratch, then gate . x with the activation fused into the
         // epilogue, as the reference's CUDA device does (gpu/cuda/mod.rs:1148-1175).
-        rc = product(ctx, scratch->data, scratch->len, up, x, nullptr, EPI_STORE, "swiglu");
-        if (rc == 0) rc = product(ctx, out->data, out->len, gate, x, scratch->data, EPI_SWIGLU, "swiglu");
+        rc = product(ctx, out_local(scratch->data, up->v.rows), scratch->len, up, x, nullptr, EPI_STORE, "swiglu");
+        if (rc == 0) rc = product(ctx, out_local(out->data, gate->v.rows), out->len, gate, x, scratch->data, EPI_SWIGLU, "swiglu");
     }
     out->shadow_kind = scratch->shadow_kind = SHADOW_NONE;
     out->bf16_exact = scratch->bf16_exact = false;

@@ -21,10 +21,20 @@ enum ShadowKind : int {
     SHADOW_PANEL_I8         // int8 digit planes per 256-wide unit, for the one- and two-token Q4_K kernel
 };
 
+constexpr int DWIM_MAX_WORLD = 8;
+
 struct dwim_b200_buffer {
     float *data = nullptr;
     size_t len = 0, cap = 0;
     bool owned = true;
+    // A buffer shared with the other ranks of a group (dwim_b200_shared_alloc /
+    // _connect, peer.cu): every rank's copy as mapped into this process
+    // (sh_peer[sh_rank] == data), and behind this rank's data its flag block
+    // (the barrier's epoch counter and one arrival word per source rank).
+    int sh_world = 0, sh_rank = 0;
+    float *sh_peer[DWIM_MAX_WORLD] = {};
+    bool sh_opened[DWIM_MAX_WORLD] = {};
+    size_t sh_flag_offset = 0;   // bytes from data to the flag block (the same on every rank)
     bool bf16_exact = false;     // every value is exactly a bf16 (write_bf16)
     // shadow
     void *shadow = nullptr;
@@ -44,6 +54,7 @@ struct dwim_b200_ctx {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
+    bool stream_owned = true;        // false: the caller's stream, adopted by dwim_b200_open_on_stream
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     uint32_t *status = nullptr;      // device word: bounded waits report here
     uint32_t *status_host = nullptr; // pinned
@@ -58,9 +69,29 @@ struct dwim_b200_ctx {
     bool weights_written = false;
     // the peer all-reduce's mailbox and mappings (peer.cu), created on request
     void *peer_state = nullptr;
+    // device address of the fixed scratch array of dwim_b200_matmul_static (static_scratch.cu)
+    void *static_scratch = nullptr;
 };
 
 namespace dwim {
+
+// Where a product's rows go: the same rows of one destination (the usual case)
+// or of every rank's copy of a shared buffer (the row-sharded product writes
+// its slice of the full result straight into its peers' memory).
+struct OutSpec {
+    float *dst[DWIM_MAX_WORLD];
+    int world;        // destinations in use
+    size_t pitch;     // floats between consecutive tokens in a destination
+    size_t row0;      // destination row of the product's first row
+};
+inline OutSpec out_local(float *out, size_t rows) {
+    OutSpec o{};
+    o.dst[0] = out;
+    o.world = 1;
+    o.pitch = rows;
+    o.row0 = 0;
+    return o;
+}
 
 inline int fail(dwim_b200_ctx *ctx, int code, const char *fmt, ...) {
     if (ctx) {
@@ -140,11 +171,14 @@ enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 // One launch: tokens [t0, t0 + n_tokens) of a panel array holding ncols_total
 // columns, the launch's first at col0.  aux is the `up` product for EPI_SWIGLU.
 bool gemv_takes_i8(const WeightView &w, size_t n);
-int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, const OutSpec &out, const float *aux,
                   int epilogue, const WeightView *up = nullptr);
 void peer_release(dwim_b200_ctx *ctx);
+void shared_release(dwim_b200_buffer *buf);
+// static_scratch.cu
+int static_scratch_prepare(dwim_b200_ctx *ctx);
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
-               size_t t0, int split, float *out, const float *aux, int epilogue);
+               size_t t0, int split, const OutSpec &out, const float *aux, int epilogue);
 int gemv_max_tokens(int split);
 
 }  // namespace dwim

@@ -69,26 +69,11 @@ constexpr int BAR_BYTES = 1024;
 struct GemmArgs {
     size_t rows, n, ncols, units;   // weight rows, tokens, operand columns, 256-weight units of K
     int split;                      // 1: columns 2t, 2t+1 are token t's hi and lo halves
-    float *out;
-    const float *aux;
+    OutSpec out;
+    const float *aux;               // EPI_SWIGLU: the `up` product, token-major [n][rows]
     int epi;
     uint32_t *status;
-    unsigned long long *trace;   // debugging only: clock stamps of CTA (0,0), null in normal use
 };
-
-// Debug trace, compiled in with -DDWIM_B200_GEMM_TRACE_BUILD only: (clock, tag,
-// index) stamps of CTA (0,0), 400 slots per warp.
-#define GEMM_TRACE_SLOTS 400
-__device__ __forceinline__ void gtrace(const GemmArgs &a, int &n, int tag, int idx) {
-#ifdef DWIM_B200_GEMM_TRACE_BUILD
-    if (a.trace && blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && n < GEMM_TRACE_SLOTS) {
-        unsigned long long *p = a.trace + 2 * ((threadIdx.x >> 5) * GEMM_TRACE_SLOTS + n);
-        p[0] = clock64();
-        p[1] = ((unsigned long long)tag << 32) | (unsigned)idx;
-        n++;
-    }
-#endif
-}
 
 // Per tile width.  Up to 128 columns everything is double-buffered by units:
 // the B ring has one stage per K block like the A ring, and K blocks change
@@ -222,6 +207,15 @@ __device__ __forceinline__ uint32_t f16x2_rn(float lo, float hi) {
 }
 __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
+// One finished element: the operator's epilogue, then the store (to every rank's copy of a shared result).
+__device__ __forceinline__ void gemm_emit(const GemmArgs &a, size_t t, size_t row, float x) {
+    const size_t i = t * a.out.pitch + a.out.row0 + row;
+    if (a.epi == EPI_ADD) x += a.out.dst[0][i];
+    else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[t * a.rows + row]);
+    a.out.dst[0][i] = x;
+    for (int p = 1; p < a.out.world; p++) a.out.dst[p][i] = x;
+}
+
 constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_64 = 0x54005400u, H2_M64 = 0xD400D400u;
 
 // ---- dequantizer: the 64 weights of one row and K block as exact sc*q halves ----------
@@ -329,7 +323,6 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
     const int units = (int)a.units;
-    int tn = 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NHAND; s++) {
@@ -374,7 +367,6 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                         if (prev >= 0)
                             mbar_wait_parked(empty0 + 8 * ((prev % KBLOCKS) / C::HAND), (prev / KBLOCKS) & 1, a.status, 0x20u);
                     }
-                    gtrace(a, tn, 1, KBLOCKS * u + h * C::HAND);
                     mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES);
                     for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
                         const int kb = KBLOCKS * u + g;
@@ -422,12 +414,9 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 const uint32_t s1 = tm + ab * BN;
                 const uint32_t upar = (u0 >> 1) & 1;
                 mbar_wait_parked(accempty0 + 8 * ab, upar ^ 1, a.status, 0x80u);   // the drain of unit u-2 is done
-                gtrace(a, tn, 12, u);
 #pragma unroll
                 for (int h = 0; h < C::NHAND; h++) {
-                    gtrace(a, tn, 2, KBLOCKS * u + h * C::HAND);
                     mbar_wait_parked(full0 + 8 * h, ab, a.status, 0x100u);
-                    gtrace(a, tn, 3, KBLOCKS * u + h * C::HAND);
                     tc_fence_after();
 #pragma unroll
                     for (int gg = 0; gg < C::HAND; gg++) {
@@ -447,9 +436,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                     __syncwarp();
                 }
                 const int ms = u % C::MIN_STAGES;
-                gtrace(a, tn, 11, u);
                 mbar_wait_parked(minfull0 + 8 * ms, (u / C::MIN_STAGES) & 1, a.status, 0x200u);
-                gtrace(a, tn, 13, u);
                 tc_fence_after();
                 if (lane == 0) {
                     // the minimums: terms (hi, hi | lo, lo) against the means' (hi, lo) twice
@@ -482,9 +469,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             const int ab = u & 1;
             // the unit's sum is complete; its last MMAs waited for the minimums'
             // stage, which the row scales were written before
-            gtrace(a, tn, 8, u);
             mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);
-            gtrace(a, tn, 9, u);
             tc_fence_after();
             const uint32_t sc = __float_as_uint(lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4));
             const uint64_t sc2 = pack2(sc, sc);
@@ -499,27 +484,20 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
-            gtrace(a, tn, 10, u);
         };
 
         for (int u = 0; u < units; u++) {
             const int rs = u % C::RAW_STAGES, ms = u % C::MIN_STAGES;
-            gtrace(a, tn, 14, u);
             mbar_wait_parked(rawfull0 + 8 * rs, (u / C::RAW_STAGES) & 1, a.status, 0x400u);
-            gtrace(a, tn, 15, u);
             const uint32_t raw_row = raw0 + rs * RAW_BYTES + rl * 144;
             const uint4 hdr = lds128(raw_row);
             Q4kBlock blk;
             load_q4k_block(hdr, raw_row, g, blk);
-            gtrace(a, tn, 4, 4 * u + g);
             mbar_wait_parked(empty0 + 8 * (g / C::HAND), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
-            gtrace(a, tn, 5, 4 * u + g);
             store_q4k_block(blk, a_row_sw);
-            gtrace(a, tn, 6, 4 * u + g);
             fence_async_smem();          // the tensor core reads shared memory through the async proxy
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8 * (g / C::HAND));
-            gtrace(a, tn, 7, 4 * u + g);
             if (g >= 2) {
                 // the minimums' A operand [K group][row][16 B]: groups (hi, hi, lo, lo) of the
                 // two f16 terms of -(32*dmin/s)*m_j; K block 2's warp writes m_0..m_3, K block 3's m_4..m_7
@@ -559,25 +537,13 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j += 2) {
                         const size_t t = (cbase + j) >> 1;
-                        if (t < a.n) {
-                            const size_t i = t * a.rows + row;
-                            float x = acc[j] + acc[j + 1];
-                            if (a.epi == EPI_ADD) x += a.out[i];
-                            else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
-                            a.out[i] = x;
-                        }
+                        if (t < a.n) gemm_emit(a, t, row, acc[j] + acc[j + 1]);
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j++) {
                         const size_t t = cbase + j;
-                        if (t < a.n) {
-                            const size_t i = t * a.rows + row;
-                            float x = acc[j];
-                            if (a.epi == EPI_ADD) x += a.out[i];
-                            else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[i]);
-                            a.out[i] = x;
-                        }
+                        if (t < a.n) gemm_emit(a, t, row, acc[j]);
                     }
                 }
             }
@@ -618,7 +584,7 @@ int encode_2d(dwim_b200_ctx *ctx, CUtensorMap *map, CUtensorMapDataType type, co
 }
 
 template <int BN>
-int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                 const float *aux, int epi) {
     using C = Cfg<BN>;
     const size_t ncols = n * (split ? 2 : 1), units = w.cols / 256;
@@ -636,17 +602,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     if ((rc = encode_2d(ctx, &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand + ncols * w.cols, units * 16, ncols, units * 32, 8,
                         BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
         return rc;
-    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status, nullptr};
-#ifdef DWIM_B200_GEMM_TRACE_BUILD
-    static unsigned long long *tbuf = nullptr;
-    static int traced = 0;
-    const char *tenv = getenv("DWIM_B200_GEMM_TRACE");
-    if (tenv) {
-        if (!tbuf) cudaMalloc(&tbuf, 2 * 32 * GEMM_TRACE_SLOTS * sizeof(unsigned long long));
-        cudaMemsetAsync(tbuf, 0, 2 * 32 * GEMM_TRACE_SLOTS * sizeof(unsigned long long), ctx->stream);
-        a.trace = tbuf;
-    }
-#endif
+    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status};
     auto kern = gemm_q4k_kernel<BN>;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {
@@ -658,42 +614,23 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, tm, a));
     ctx->weights_written = false;
     DWIM_LAUNCHED(ctx);
-#ifdef DWIM_B200_GEMM_TRACE_BUILD
-    if (tenv && ++traced == atoi(tenv)) {
-        static unsigned long long host[2 * 32 * GEMM_TRACE_SLOTS];
-        cudaStreamSynchronize(ctx->stream);
-        cudaMemcpy(host, tbuf, sizeof host, cudaMemcpyDeviceToHost);
-        unsigned long long t0 = ~0ull;
-        for (int i = 0; i < 32 * GEMM_TRACE_SLOTS; i++)
-            if (host[2 * i + 1] && host[2 * i] < t0) t0 = host[2 * i];
-        for (int wv = 0; wv < 32; wv++)
-            for (int i = 0; i < GEMM_TRACE_SLOTS; i++) {
-                unsigned long long v = host[2 * (wv * GEMM_TRACE_SLOTS + i) + 1];
-                if (v) fprintf(stderr, "GTRACE %llu tag=%llu warp=%d idx=%llu\n", host[2 * (wv * GEMM_TRACE_SLOTS + i)] - t0, v >> 32, wv, v & 0xffffffffull);
-            }
-    }
-#endif
     return 0;
 }
 
 }  // namespace
 
-bool gemm_available() { return true; }
-
 // Formats the tensor-core kernel takes; the rest goes through the small-M
 // kernel in groups of tokens.
 bool gemm_supports(const WeightView &w) { return w.fmt == Q4_K && w.cols % 256 == 0; }
 
-int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, float *out,
+int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue) {
     if (!gemm_supports(w)) return fail(ctx, DWIM_B200_EFORMAT, "the tensor-core GEMM does not take format %d", w.fmt);
     const size_t ncols = n * (split ? 2 : 1);
     if (ncols <= 32) return launch_gemm<32>(ctx, w, operand, n, split, out, aux, epilogue);
     if (ncols <= 64) return launch_gemm<64>(ctx, w, operand, n, split, out, aux, epilogue);
-    if (ncols <= 128 || getenv("DWIM_B200_GEMM_NARROW")) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
+    if (ncols <= 128) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
     return launch_gemm<256>(ctx, w, operand, n, split, out, aux, epilogue);
 }
-
-void gemm_release(dwim_b200_ctx *) {}
 
 }  // namespace dwim

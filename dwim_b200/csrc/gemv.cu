@@ -54,8 +54,8 @@ struct GemvArgs {
     int split;               // 1: columns are (hi, lo) pairs of a token
     int n_tokens;            // tokens of this launch
     size_t t0;               // first token's index in out
-    float *out;
-    const float *aux;        // EPI_SWIGLU: the `up` product, same layout as out
+    OutSpec out;
+    const float *aux;        // EPI_SWIGLU: the `up` product, token-major [n][rows]
     int epi;
     int units;               // ceil(cols / 256)
     int kc;                  // units per stage
@@ -69,19 +69,7 @@ struct GemvArgs {
     int x_resident;          // 1: the launch's panels sit in shared memory for the CTA's whole life
     int xres_bytes;
     uint32_t *status;
-    unsigned long long *trace;   // debugging only: clock stamps of CTA 0 (null in normal use)
 };
-
-// Debug trace: (clock, tag, iteration) stamps of CTA 0, 200 slots per warp.
-#define TRACE_SLOTS 200
-__device__ __forceinline__ void trace(const GemvArgs &a, int &n, int tag, uint32_t it) {
-    if (a.trace && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && n < TRACE_SLOTS) {
-        unsigned long long *p = a.trace + 2 * ((threadIdx.x >> 5) * TRACE_SLOTS + n);
-        p[0] = clock64();
-        p[1] = ((unsigned long long)tag << 32) | it;
-        n++;
-    }
-}
 
 constexpr uint32_t H2_1024 = 0x64006400u;   // half2(1024, 1024)
 constexpr uint32_t H2_1056 = 0x64206420u;   // half2(1056, 1056)
@@ -416,14 +404,16 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 __device__ __forceinline__ void emit(const GemvArgs &a, size_t t, size_t r, float v) {
     if (r >= a.w.rows) return;
-    size_t i = (a.t0 + t) * a.w.rows + r;
-    if (a.epi == EPI_ADD) v += a.out[i];
-    else if (a.epi == EPI_SWIGLU) v = silu_mul(v, a.aux[i]);
-    a.out[i] = v;
+    const size_t i = (a.t0 + t) * a.out.pitch + a.out.row0 + r;
+    if (a.epi == EPI_ADD) v += a.out.dst[0][i];
+    else if (a.epi == EPI_SWIGLU) v = silu_mul(v, a.aux[(a.t0 + t) * a.w.rows + r]);
+    a.out.dst[0][i] = v;
+    // a shared result: the same element of every peer's copy (plain stores over NVLink)
+    for (int p = 1; p < a.out.world; p++) a.out.dst[p][i] = v;
 }
 
 template <int FMT, int NT, int RT, int KS>
-__global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(const GemvArgs a) {
     constexpr int NW = RT * KS;
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
@@ -455,7 +445,6 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 
     const int n_chunks = (a.units + a.kc - 1) / a.kc;
     const uint32_t stage0 = smem_u32(stages);
-    int tn = 0;   // trace slots used by this warp
 
     if (warp == NW) {
         // ------------------------------ producer ------------------------------
@@ -478,9 +467,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
             for (int ch = 0; ch < n_chunks; ch++, it++) {
                 const int s = it % S;
                 const uint32_t ph = (it / S) & 1;
-                trace(a, tn, 1, it);
                 mbar_wait(empty0 + 8 * s, ph ^ 1, a.status, 0x1u);
-                trace(a, tn, 2, it);
                 const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
                 const uint32_t qbytes = UNIT_Q * kcc;
                 uint32_t sbytes = 0;
@@ -525,7 +512,6 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                 for (int u = lane; u < kcc && !a.x_resident; u += 32)
                     bulk_g2s(st + a.x_off + u * xbytes,
                              a.panels + (size_t)(u0 + u) * a.xsrc_stride + (size_t)a.col0 * PANEL_BYTES, xbytes, bar);
-                trace(a, tn, 3, it);
             }
         }
         // Drain: the copies this warp issued must have landed before the CTA's
@@ -575,9 +561,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
         for (int ch = 0; ch < n_chunks; ch++, it++) {
             const int s = it % S;
             const uint32_t ph = (it / S) & 1;
-            trace(a, tn, 4, it);
             mbar_wait(full0 + 8 * s, ph, a.status, 0x2u);
-            trace(a, tn, 5, it);
             const int u0 = ch * a.kc, kcc = min(a.kc, a.units - u0);
             const uint32_t st = stage0 + s * a.stage_bytes;
             L.row_a = st + (rt * 16 + grow) * a.q_stride;
@@ -598,7 +582,6 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
-            trace(a, tn, 6, it);
         }
 
         // ---- sum the K-split warps of this row tile, in warp order ----
@@ -621,7 +604,6 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
                 }
         }
 
-        trace(a, tn, 7, it);
         if (!out_ready) {   // the kernel ahead may still be writing `out` or `aux`
             griddep_wait();
             out_ready = true;
@@ -665,18 +647,6 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) gemv_kernel(const GemvA
 // ---------------------------------------------------------------------------
 int gemv_max_tokens(int split) { return split ? 8 : 16; }
 
-// DWIM_B200_GEMV_TUNE="rt,ks,kc,stages,ctas_per_sm" overrides the launch shape
-// (0 = keep the default), for sweeps on the device.  Read once.
-struct Tune { int rt = 0, ks = 0, kc = 0, stages = 0, cps = 0; };
-static const Tune &tune() {
-    static Tune t = [] {
-        Tune v;
-        if (const char *e = getenv("DWIM_B200_GEMV_TUNE")) sscanf(e, "%d,%d,%d,%d,%d", &v.rt, &v.ks, &v.kc, &v.stages, &v.cps);
-        return v;
-    }();
-    return t;
-}
-
 template <int FMT, int NT, int RT, int KS>
 static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int R = RT * 16;
@@ -684,7 +654,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NT * 4 * 32 * 4 + 127) & ~127) : 0;
     constexpr int SMEM_LIMIT = 227 * 1024;
     // CTAs per SM: two smaller CTAs overlap one's fill and drain with the other's steady state
-    const int cps = tune().cps > 0 ? tune().cps : a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
+    const int cps = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
     const int SMEM_MAX = cps > 1 ? (228 * 1024) / cps - 1024 : SMEM_LIMIT;
     const int fixed = 256 + RED_BYTES;
     // Panels stay resident when the launch covers the whole panel array (one
@@ -702,7 +672,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     auto whole_stage = [&]() {
         return (int)((R * (a.w.qpitch + srow_bytes) + (a.x_resident ? 0 : a.units * a.xunit) + 127) & ~127);
     };
-    a.whole_rows = tune().kc <= 0 && 2 * whole_stage() <= budget;
+    a.whole_rows = 2 * whole_stage() <= budget;
     if (a.whole_rows) {
         a.kc = a.units;
         a.q_stride = (int)a.w.qpitch;
@@ -715,7 +685,6 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
         int chunks = 2;
         for (;; chunks++) {
             a.kc = (a.units + chunks - 1) / chunks;
-            if (tune().kc > 0) a.kc = tune().kc < a.units ? tune().kc : a.units;
             int qs = UNIT_Q * a.kc;
             if ((qs / 16) % 2 == 0) qs += 16;   // an odd number of 16-byte steps between rows: no bank conflicts
             a.q_stride = qs;
@@ -724,50 +693,25 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
             a.x_off = a.s_off + R * a.s_stride;
             a.stage_bytes = (a.x_off + (a.x_resident ? 0 : a.kc * a.xunit) + 127) & ~127;
             a.stages = budget / a.stage_bytes;
-            if (a.stages >= 2 || a.kc == 1 || tune().kc > 0) break;
+            if (a.stages >= 2 || a.kc == 1) break;
         }
     }
     if (a.stages > MAX_STAGES) a.stages = MAX_STAGES;
-    if (tune().stages > 0 && tune().stages < a.stages) a.stages = tune().stages;
     if (a.stages < 2) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: a stage of %d bytes does not fit", a.stage_bytes);
     a.n_tiles = (int)((a.w.rows + R - 1) / R);
     const int smem = fixed + a.xres_bytes + a.stages * a.stage_bytes;
-    auto kern = gemv_kernel<FMT, NT, RT, KS>;
+    auto kern = dwim_smallm_kernel<FMT, NT, RT, KS>;
     static bool configured[64] = {false};   // per instantiation, per device
     if (!configured[ctx->device & 63]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
         configured[ctx->device & 63] = true;
     }
     int grid = a.n_tiles < cps * ctx->sm_count ? a.n_tiles : cps * ctx->sm_count;
-    static unsigned long long *tbuf = nullptr;
-    static int traced = 0;
-    const bool tracing = getenv("DWIM_B200_GEMV_TRACE") != nullptr;
     const int nwarps = RT * KS + 1;
-    if (tracing) {
-        if (!tbuf) cudaMallocManaged(&tbuf, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
-        cudaStreamSynchronize(ctx->stream);
-        memset(tbuf, 0, 2 * 32 * TRACE_SLOTS * sizeof(unsigned long long));
-        a.trace = tbuf;
-    }
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
     ctx->weights_written = false;
     DWIM_CUDA(ctx, launch_dependent(dependent, kern, dim3((unsigned)grid), dim3((unsigned)(nwarps * 32)), (size_t)smem, ctx->stream, a));
     DWIM_LAUNCHED(ctx);
-    if (tracing) {
-        cudaStreamSynchronize(ctx->stream);
-        if (++traced == atoi(getenv("DWIM_B200_GEMV_TRACE"))) {
-            unsigned long long t0 = ~0ull;
-            for (int i = 0; i < nwarps * TRACE_SLOTS; i++)
-                if (tbuf[2 * i + 1] && tbuf[2 * i] < t0) t0 = tbuf[2 * i];
-            fprintf(stderr, "TRACE rt=%d ks=%d stages=%d kc=%d whole=%d stage_bytes=%d tiles=%d grid=%d xres=%d\n", RT, KS, a.stages,
-                    a.kc, a.whole_rows, a.stage_bytes, a.n_tiles, grid, a.xres_bytes);
-            for (int w = 0; w < nwarps; w++)
-                for (int i = 0; i < TRACE_SLOTS; i++) {
-                    unsigned long long v = tbuf[2 * (w * TRACE_SLOTS + i) + 1];
-                    if (v) fprintf(stderr, "TRACE %llu tag=%llu warp=%d it=%llu\n", tbuf[2 * (w * TRACE_SLOTS + i)] - t0, v >> 32, w, v & 0xffffffffull);
-                }
-        }
-    }
     return 0;
 }
 
@@ -780,22 +724,13 @@ static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
     // 16-row tiles (their stages are larger); eight K-split warps throughout.
     const size_t tiles32 = (a.w.rows + 31) / 32;
     int rt = (FMT == Q4_K || FMT == Q4K_I8) && tiles32 >= (size_t)2 * ctx->sm_count ? 2 : 1;
-    int ks = 8;
-    if (tune().rt > 0) rt = tune().rt;
-    if (tune().ks > 0) ks = tune().ks;
-    if (NT == 2 && rt == 2 && ks >= 8) ks /= 2;   // 17+ warps of the two-group kernel would spill registers
-    if (rt == 2 && ks == 10) return launch<FMT, NT, 2, 10>(ctx, a);
-    if (rt == 2 && ks == 8) return launch<FMT, NT, 2, 8>(ctx, a);
-    if (rt == 2 && ks == 5) return launch<FMT, NT, 2, 5>(ctx, a);
-    if (rt == 2 && ks == 4) return launch<FMT, NT, 2, 4>(ctx, a);
-    if (rt == 1 && ks == 10) return launch<FMT, NT, 1, 10>(ctx, a);
-    if (rt == 1 && ks == 5) return launch<FMT, NT, 1, 5>(ctx, a);
-    if (rt == 1 && ks == 4) return launch<FMT, NT, 1, 4>(ctx, a);
+    // 17+ warps of the two-group kernel would spill registers: four K-split warps there
+    if (rt == 2) return NT == 2 ? launch<FMT, NT, 2, 4>(ctx, a) : launch<FMT, NT, 2, 8>(ctx, a);
     return launch<FMT, NT, 1, 8>(ctx, a);
 }
 
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
-               size_t t0, int split, float *out, const float *aux, int epilogue) {
+               size_t t0, int split, const OutSpec &out, const float *aux, int epilogue) {
     if (w.rows == 0 || n_tokens == 0) return 0;
     GemvArgs a{};
     a.w = w;
@@ -833,7 +768,7 @@ bool gemv_takes_i8(const WeightView &w, size_t n) {
 // One or two tokens of a Q4_K matrix through the int8 routine; `panels` from
 // build_panels_i8.
 // `up`, when given, makes it the SwiGLU of the pair (w = gate) in one launch.
-int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, float *out, const float *aux,
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, const OutSpec &out, const float *aux,
                   int epilogue, const WeightView *up) {
     if (w.rows == 0 || n_tokens == 0) return 0;
     if (w.fmt != Q4_K || n_tokens > I8_MAX_TOKENS || w.cols % 256 != 0)

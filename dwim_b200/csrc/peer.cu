@@ -59,6 +59,15 @@ __device__ __forceinline__ uint32_t *flag_of(uint8_t *box, const PeerArgs &a, in
     return flags + ((size_t)set * a.world + src) * a.chunks + chunk;
 }
 
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const PeerArgs a) {
     // a programmatic dependent: the vector comes from the product just ahead
     dwim::griddep_launch();
@@ -70,18 +79,19 @@ __global__ void __launch_bounds__(PEER_THREADS) peer_allreduce_kernel(const Peer
         float *dst = slot_of(a.box[p], a, set, a.rank) + first;
         for (size_t i = threadIdx.x; i < PEER_CHUNK && first + i < a.n; i += PEER_THREADS) dst[i] = a.x[first + i];
     }
-    // 2. visible everywhere before the flags say so
+    // 2. visible everywhere before the flags say so: every thread fences its own stores, the
+    //    block meets, and the threads that write the flags release what they have seen
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x < (unsigned)a.world) {
-        volatile uint32_t *f = flag_of(a.box[threadIdx.x], a, set, a.rank, chunk);
-        *f = a.epoch;
+        __threadfence_system();
+        st_release_sys(flag_of(a.box[threadIdx.x], a, set, a.rank, chunk), a.epoch);
     }
     // 3. every rank's chunk has arrived here (bounded wait)
     if (threadIdx.x < (unsigned)a.world) {
-        volatile uint32_t *f = flag_of(a.box[a.rank], a, set, (int)threadIdx.x, chunk);
+        const uint32_t *f = flag_of(a.box[a.rank], a, set, (int)threadIdx.x, chunk);
         const uint64_t start = dwim::globaltimer();
-        while (*f != a.epoch) {
+        while (ld_acquire_sys(f) != a.epoch) {
             if (dwim::globaltimer() - start > dwim::WAIT_LIMIT_NS) {
                 atomicOr(a.status, 0x10000u);
                 break;
@@ -173,6 +183,12 @@ extern "C" int dwim_b200_peer_allreduce(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
     for (int r = 0; r < p->world; r++)
         if (!p->box[r]) return fail(ctx, DWIM_B200_EINVAL, "peer_allreduce: rank %d is not connected", r);
     if (n == 0) return 0;
+    // The call's epoch is a kernel argument: a captured launch would replay one epoch for ever
+    // and stop waiting for its peers.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    DWIM_CUDA(ctx, cudaStreamIsCapturing(ctx->stream, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+        return fail(ctx, DWIM_B200_EINVAL, "peer_allreduce: not inside a stream capture (the epoch is a launch argument)");
     PeerArgs a{};
     a.x = buf->data;
     a.n = n;
@@ -188,5 +204,147 @@ extern "C" int dwim_b200_peer_allreduce(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
     DWIM_LAUNCHED(ctx);
     buf->shadow_kind = SHADOW_NONE;
     buf->bf16_exact = false;
+    return 0;
+}
+
+// ---- buffers shared by the ranks of a group, and their barrier ------------------------
+// A row-sharded product writes its rows of the full, token-major result into
+// every rank's copy of the output (dwim_b200_matmul_gather: plain stores from
+// the product's epilogue, over NVLink for the peers' copies), so the exchange
+// runs while the rest of the product is still being computed.  What remains
+// of the all-gather is a barrier: every rank must know that all slices have
+// arrived in its copy.
+//
+// A shared buffer is `len` floats followed (256-byte aligned) by a flag block:
+//   word 0        this rank's barrier count (advanced by the barrier kernel
+//                 itself, so a captured launch can be replayed)
+//   words 16..23  arrival word of source rank q: the highest barrier count q
+//                 has signalled here
+// The barrier kernel (one block) runs after the product in stream order: it
+// waits for the kernel ahead (all its stores, remote ones included, are then
+// complete), fences, writes its new count into its arrival word on every rank
+// with a system-scope release, and waits (bounded) until every arrival word of
+// its own block has reached that count.
+namespace {
+
+constexpr size_t SH_FLAG_BYTES = 256;
+constexpr int SH_ARRIVE_WORD = 16;
+
+struct BarrierArgs {
+    uint32_t *flags[DWIM_MAX_WORLD];   // every rank's flag block as mapped here
+    int world, rank;
+    uint32_t *status;
+};
+
+__global__ void __launch_bounds__(32) shared_barrier_kernel(const BarrierArgs a) {
+    dwim::griddep_launch();
+    dwim::griddep_wait();           // the product ahead has completed: its stores have left this GPU
+    __shared__ uint32_t count;
+    if (threadIdx.x == 0) {
+        count = a.flags[a.rank][0] + 1;
+        a.flags[a.rank][0] = count;
+    }
+    __syncwarp();
+    const uint32_t c = *(volatile uint32_t *)&count;
+    if (threadIdx.x < (unsigned)a.world) {
+        __threadfence_system();
+        st_release_sys(a.flags[threadIdx.x] + SH_ARRIVE_WORD + a.rank, c);
+        const uint32_t *f = a.flags[a.rank] + SH_ARRIVE_WORD + threadIdx.x;
+        const uint64_t start = dwim::globaltimer();
+        // a peer may already be a barrier ahead: at least c, not exactly c
+        while ((int32_t)(ld_acquire_sys(f) - c) < 0) {
+            if (dwim::globaltimer() - start > dwim::WAIT_LIMIT_NS) {
+                atomicOr(a.status, 0x20000u);
+                break;
+            }
+        }
+    }
+    __syncwarp();
+    __threadfence_system();
+}
+
+}  // namespace
+
+namespace dwim {
+void shared_release(dwim_b200_buffer *b) {
+    for (int r = 0; r < b->sh_world; r++)
+        if (b->sh_opened[r]) cudaIpcCloseMemHandle(b->sh_peer[r]);
+    b->sh_world = 0;
+}
+}  // namespace dwim
+
+extern "C" int dwim_b200_shared_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out, void *handle, size_t handle_bytes) {
+    using namespace dwim;
+    if (!ctx || !out || !handle) return DWIM_B200_EINVAL;
+    *out = nullptr;
+    if (len == 0) return fail(ctx, DWIM_B200_EINVAL, "shared_alloc: empty buffer");
+    if (handle_bytes < sizeof(cudaIpcMemHandle_t))
+        return fail(ctx, DWIM_B200_EINVAL, "shared_alloc: the handle needs %zu bytes", sizeof(cudaIpcMemHandle_t));
+    dwim_b200_buffer *b = new dwim_b200_buffer();
+    b->len = b->cap = len;
+    b->sh_flag_offset = (len * sizeof(float) + 255) / 256 * 256;
+    const size_t bytes = b->sh_flag_offset + SH_FLAG_BYTES;
+    cudaError_t e = cudaMalloc(&b->data, bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(b->data, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, b->data);
+    if (e != cudaSuccess) {
+        if (b->data) cudaFree(b->data);
+        delete b;
+        cudaGetLastError();
+        return fail(ctx, e == cudaErrorMemoryAllocation ? DWIM_B200_ENOMEM : DWIM_B200_ECUDA, "shared_alloc: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, sizeof h);
+    *out = b;
+    return 0;
+}
+
+extern "C" int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank, const void *handles,
+                                        size_t handle_bytes) {
+    using namespace dwim;
+    if (!ctx || !buf) return DWIM_B200_EINVAL;
+    if (world < 1 || world > DWIM_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(ctx, DWIM_B200_EINVAL, "shared_connect: world %d rank %d", world, rank);
+    if (buf->sh_flag_offset == 0) return fail(ctx, DWIM_B200_EINVAL, "shared_connect: not a buffer of shared_alloc");
+    if (buf->sh_world) return fail(ctx, DWIM_B200_EINVAL, "shared_connect: connected already");
+    if (world > 1 && (!handles || handle_bytes < sizeof(cudaIpcMemHandle_t)))
+        return fail(ctx, DWIM_B200_EINVAL, "shared_connect: short handles");
+    for (int r = 0; r < world; r++) {
+        if (r == rank) {
+            buf->sh_peer[r] = buf->data;
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const uint8_t *>(handles) + (size_t)r * handle_bytes, sizeof h);
+        void *ptr = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            buf->sh_world = r;          // what has been opened so far
+            buf->sh_rank = rank;
+            shared_release(buf);
+            cudaGetLastError();
+            return fail(ctx, DWIM_B200_ECUDA, "shared_connect: mapping rank %d's copy: %s", r, cudaGetErrorString(e));
+        }
+        buf->sh_peer[r] = static_cast<float *>(ptr);
+        buf->sh_opened[r] = true;
+    }
+    buf->sh_world = world;
+    buf->sh_rank = rank;
+    return 0;
+}
+
+extern "C" int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    using namespace dwim;
+    if (!ctx || !buf) return DWIM_B200_EINVAL;
+    if (buf->sh_world < 1) return fail(ctx, DWIM_B200_EINVAL, "shared_barrier: not a connected shared buffer");
+    BarrierArgs a{};
+    a.world = buf->sh_world;
+    a.rank = buf->sh_rank;
+    a.status = ctx->status;
+    for (int r = 0; r < buf->sh_world; r++)
+        a.flags[r] = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(buf->sh_peer[r]) + buf->sh_flag_offset);
+    DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, shared_barrier_kernel, dim3(1), dim3(32), 0, ctx->stream, a));
+    DWIM_LAUNCHED(ctx);
     return 0;
 }

@@ -8,13 +8,15 @@
 // buffer it allocates on first use; here that scratch is a fixed array in the
 // library's own image instead.
 //
-// The array lives in every GPU's memory from the moment the library is loaded
-// there until the process ends (STATIC_SCRATCH_BYTES per device).  All calls
-// share it and it keeps the last call's contents: every byte a call reads it
-// has written itself first (the prologue rewrites each panel in full), so
-// nothing has to start at zero — but two calls that overlap on the GPU (two
-// contexts, two streams) would race on it.  Calls on one context are ordered
-// by its stream.
+// Every GPU on which a context is opened holds the array from then until the
+// process ends (STATIC_SCRATCH_BYTES per device: the module that contains it is
+// loaded, and the array's address looked up, by dwim_b200_open, so that no
+// call of this entry point allocates or loads anything).  All calls share it
+// and it keeps the last call's contents: every byte a call reads it has
+// written itself first (the prologue rewrites each panel in full), so nothing
+// has to start at zero — but two calls that overlap on the GPU (two contexts,
+// two streams) would race on it.  Calls on one context are ordered by its
+// stream.
 #include "common.cuh"
 
 namespace {
@@ -23,26 +25,19 @@ constexpr size_t STATIC_SCRATCH_BYTES = 1u << 20;   // 1 MiB
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
-// Device address of the array, per device.  In host code the array's name is
-// only a handle for the runtime, not an address a kernel could use.
-void *g_scratch_addr[64] = {nullptr};
+}  // namespace
 
-int scratch_address(dwim_b200_ctx *ctx, void **out) {
-    const int d = ctx->device;
-    if (d < 0 || d >= 64) return dwim::fail(ctx, DWIM_B200_EINVAL, "device %d out of range", d);
-    if (!g_scratch_addr[d]) {
-        int current = -1;
-        DWIM_CUDA(ctx, cudaGetDevice(&current));
-        if (current != d) DWIM_CUDA(ctx, cudaSetDevice(d));
-        void *p = nullptr;
-        DWIM_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_scratch));
-        g_scratch_addr[d] = p;
-    }
-    *out = g_scratch_addr[d];
+namespace dwim {
+// Called by dwim_b200_open with the context's device current.  In host code the
+// array's name is only a handle for the runtime, not an address a kernel could
+// use: the device address comes from cudaGetSymbolAddress, per device.
+int static_scratch_prepare(dwim_b200_ctx *ctx) {
+    void *p = nullptr;
+    DWIM_CUDA(ctx, cudaGetSymbolAddress(&p, g_static_scratch));
+    ctx->static_scratch = p;
     return 0;
 }
-
-}  // namespace
+}  // namespace dwim
 
 extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwim_b200_weight *w, const float *x, size_t n) {
     using namespace dwim;
@@ -58,12 +53,10 @@ extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwi
             return fail(ctx, DWIM_B200_EINVAL,
                         "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
                         v.cols, need, STATIC_SCRATCH_BYTES);
-        void *scratch = nullptr;
-        int rc = scratch_address(ctx, &scratch);
+        void *scratch = ctx->static_scratch;
+        int rc = build_panels_i8(ctx, x, n, v.cols, (uint8_t *)scratch);
         if (rc) return rc;
-        rc = build_panels_i8(ctx, x, n, v.cols, (uint8_t *)scratch);
-        if (rc) return rc;
-        return gemv_small_i8(ctx, v, (const uint8_t *)scratch, (int)n, out, nullptr, EPI_STORE);
+        return gemv_small_i8(ctx, v, (const uint8_t *)scratch, (int)n, out_local(out, v.rows), nullptr, EPI_STORE);
     }
     const int split = 1;                                  // f32 activations: value + remainder columns
     if (n > (size_t)gemv_max_tokens(split))
@@ -74,10 +67,8 @@ extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwi
         return fail(ctx, DWIM_B200_EINVAL,
                     "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
                     v.cols, need, STATIC_SCRATCH_BYTES);
-    void *scratch = nullptr;
-    int rc = scratch_address(ctx, &scratch);
+    void *scratch = ctx->static_scratch;
+    int rc = build_panels(ctx, x, n, v.cols, v.fmt == Q4_K ? SHADOW_PANEL_Q4K : SHADOW_PANEL_NATURAL, split, (__half *)scratch);
     if (rc) return rc;
-    rc = build_panels(ctx, x, n, v.cols, v.fmt == Q4_K ? SHADOW_PANEL_Q4K : SHADOW_PANEL_NATURAL, split, (__half *)scratch);
-    if (rc) return rc;
-    return gemv_small(ctx, v, (const __half *)scratch, ncols, 0, (int)n, 0, split, out, nullptr, EPI_STORE);
+    return gemv_small(ctx, v, (const __half *)scratch, ncols, 0, (int)n, 0, split, out_local(out, v.rows), nullptr, EPI_STORE);
 }

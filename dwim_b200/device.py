@@ -48,10 +48,16 @@ class Weight:
 
 
 class B200:
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, stream: int | None = None):
+        """Opens GPU ``device``.  ``stream``: a ``cudaStream_t`` (as an integer,
+        e.g. ``torch.cuda.current_stream().cuda_stream``) to run on instead of a
+        stream of the context's own; 0 is the legacy default stream."""
         self._L = _lib.lib()
         h = C.c_void_p()
-        rc = self._L.dwim_b200_open(device, C.byref(h))
+        if stream is None:
+            rc = self._L.dwim_b200_open(device, C.byref(h))
+        else:
+            rc = self._L.dwim_b200_open_on_stream(device, stream, C.byref(h))
         if rc != 0:
             raise DeviceError(rc, (self._L.dwim_b200_last_error(None) or b"").decode())
         self._ctx = h.value
@@ -108,6 +114,11 @@ class B200:
         self._check(self._L.dwim_b200_wrap(self._ctx, device_ptr, length, C.byref(h)))
         return Buffer(self, h.value)
 
+    def touch(self, buf: Buffer) -> None:
+        """Tells the library that someone else wrote ``buf`` (a kernel of the
+        caller's, a collective): its cached operand form is dropped."""
+        self._check(self._L.dwim_b200_touch(self._ctx, buf._h))
+
     def resize(self, buf: Buffer, length: int) -> None:
         self._check(self._L.dwim_b200_resize(self._ctx, buf._h, length))
 
@@ -148,7 +159,10 @@ class B200:
         """``matmul`` for up to 8 tokens that allocates nothing: the operand
         scratch is a fixed array inside the library, shared by every call on
         the GPU.  For callers that must not allocate device memory."""
-        n = len(x) // w.shape[1]
+        rows, cols = w.shape
+        n = len(x) // cols
+        if len(x) != n * cols or len(out) != n * rows:
+            raise DeviceError(_lib.EINVAL, f"matmul_static: x of {len(x)} and out of {len(out)} floats for a [{rows}, {cols}] matrix")
         self._check(self._L.dwim_b200_matmul_static(self._ctx, out.ptr, w._h, x.ptr, n))
 
     # -- beside the trait -----------------------------------------------------
@@ -173,6 +187,28 @@ class B200:
 
     def gather_rows(self, out: Buffer, parts: Buffer, n: int, rows: int, world: int, align: int) -> None:
         self._check(self._L.dwim_b200_gather_rows(self._ctx, out._h, parts._h, n, rows, world, align))
+
+    # -- a result shared by the ranks of a group (one process per GPU) -----------
+    def shared_alloc(self, length: int):
+        """This rank's copy of a buffer the group shares, and its inter-process
+        handle (``bytes``), to be exchanged among the ranks."""
+        nb = int(self._L.dwim_b200_peer_handle_bytes())
+        h, hb = C.c_void_p(), C.create_string_buffer(nb)
+        self._check(self._L.dwim_b200_shared_alloc(self._ctx, length, C.byref(h), hb, nb))
+        return Buffer(self, h.value), hb.raw
+
+    def shared_connect(self, buf: Buffer, world: int, rank: int, handles) -> None:
+        """Maps the peers' copies of ``buf``; ``handles`` in rank order."""
+        nb = int(self._L.dwim_b200_peer_handle_bytes())
+        blob = b"".join(bytes(h)[:nb].ljust(nb, b"\0") for h in handles)
+        self._check(self._L.dwim_b200_shared_connect(self._ctx, buf._h, world, rank, blob, nb))
+
+    def matmul_gather(self, out: Buffer, w: Weight, x: Buffer, row_begin: int, total_rows: int) -> None:
+        """The row-sharded product, its rows stored into every rank's copy of ``out``."""
+        self._check(self._L.dwim_b200_matmul_gather(self._ctx, out._h, w._h, x._h, row_begin, total_rows))
+
+    def shared_barrier(self, buf: Buffer) -> None:
+        self._check(self._L.dwim_b200_shared_barrier(self._ctx, buf._h))
 
     # -- the small all-reduce over peer memory (one process per GPU) ------------
     def peer_create(self, world: int, rank: int, cap: int) -> bytes:

@@ -64,6 +64,15 @@ typedef struct dwim_b200_weight dwim_b200_weight;
 /* Cuda::new (gpu/cuda/mod.rs:210-238): opens device `device`, creates the
  * context's stream.  Fails with ENODEV on anything but compute capability 10.x. */
 DWIM_B200_API int dwim_b200_open(int device, dwim_b200_ctx **out);
+/* The same, on a stream the caller owns (a cudaStream_t; it is neither
+ * synchronized against others nor destroyed here).  The reference's device runs
+ * everything on one in-order stream (gpu/cuda/mod.rs:5-9, 238): an engine that
+ * keeps its other operators (norms, attention, rope ...) on its own CUDA device
+ * opens this library on that device's stream, and the two sets of kernels are
+ * ordered as if they were one device's.  Without it, work of the caller that
+ * touches a buffer of this library must be fenced against dwim_b200_stream()
+ * with events. */
+DWIM_B200_API int dwim_b200_open_on_stream(int device, void *cuda_stream, dwim_b200_ctx **out);
 DWIM_B200_API int dwim_b200_close(dwim_b200_ctx *ctx);
 
 /* The message of the last failure on this context ("" if none).  With a null
@@ -104,6 +113,15 @@ DWIM_B200_API int dwim_b200_wrap(dwim_b200_ctx *ctx, float *device_ptr, size_t l
 /* Device::resize (gpu/mod.rs:216-219; gpu/cuda/mod.rs:986-993): sets the
  * length, up to the allocated one; never reallocates. */
 DWIM_B200_API int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t len);
+/* "Someone else wrote this buffer."  A buffer caches the 16-bit operand form
+ * of its contents between products (after `Form`, gpu/cuda/mod.rs:108-126,
+ * which the reference invalidates in its own write paths, :313-384).  This
+ * library drops the cache whenever one of its own calls writes the buffer; a
+ * write it cannot see (a kernel of the caller's through dwim_b200_buffer_ptr, a
+ * collective into a wrapped buffer) must be followed by touch before the next
+ * product reads the buffer, or that product multiplies the old contents.  It
+ * also forgets that the contents were exact in 16 bits (write_bf16). */
+DWIM_B200_API int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
 /* Device::write (gpu/mod.rs:224-225): `len` must equal the buffer's length. */
 DWIM_B200_API int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len);
 /* As write, from bf16 bits (gpu/float.rs:5-8): the buffer holds the same
@@ -162,15 +180,48 @@ DWIM_B200_API int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, co
  * operand form of x goes to a fixed 1 MiB array inside the library instead of
  * a buffer allocated on first use.  For callers whose device memory is an
  * arena sized once, or that run where cudaMalloc is not allowed.  Sizes whose
- * operand form does not fit (n * cols beyond about 246 000) are refused with
- * EINVAL.  The array is shared by all calls on a GPU: calls that overlap there
- * race; calls on one context are ordered.  The first call on a device looks
- * the array's address up (cudaGetSymbolAddress) and should come before any
- * stream capture. */
+ * operand form does not fit the array are refused with EINVAL: with `units` =
+ * cols / 256 rounded up, n * units may be at most 949 for one or two tokens of
+ * Q4_K (1104 bytes per token and unit) and 963 otherwise (1088 bytes): about
+ * 243 000 and 246 000 activations per call.  The array is shared by all calls on
+ * a GPU: calls that overlap there race; calls on one context are ordered.  Its
+ * device address is looked up (cudaGetSymbolAddress) when the context is
+ * opened, so dwim_b200_open is the call that should come before any stream
+ * capture; no call of matmul_static sets anything up. */
 DWIM_B200_API int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwim_b200_weight *w, const float *x,
                                           size_t n);
 
 /* ---- sharding across GPUs (no counterpart in the reference) -------------- */
+
+/* A buffer of `len` f32 that the ranks of a group (one process per GPU) share:
+ * every rank allocates its copy with shared_alloc, which also writes the
+ * copy's inter-process handle (dwim_b200_peer_handle_bytes() bytes); the
+ * handles are exchanged by the caller's own means and given, in rank order
+ * and `handle_bytes` apart, to shared_connect, which maps the peers' copies
+ * (a world of 1 needs no handles).  Freed with dwim_b200_buffer_free. */
+DWIM_B200_API int dwim_b200_shared_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out, void *handle,
+                                         size_t handle_bytes);
+DWIM_B200_API int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank,
+                                           const void *handles, size_t handle_bytes);
+/* The row-sharded product with the all-gather fused into it: `w` holds rows
+ * [row_begin, row_begin + rows(w)) of a matrix of `total_rows`; the kernel's
+ * epilogue stores out[t * total_rows + row_begin + r] = w[r] . x[t] into EVERY
+ * rank's copy of the shared buffer `out` (n * total_rows f32), the peers'
+ * copies by plain stores over NVLink while other tiles still multiply.  When
+ * every rank has made the call and passed dwim_b200_shared_barrier(out), every
+ * copy holds the full token-major result.  A copy must not be written again
+ * (the next matmul_gather into it, by any rank) before its owner has finished
+ * reading it: alternate two shared buffers, as a barrier lets a rank run at
+ * most one step ahead of its peers. */
+DWIM_B200_API int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w,
+                                          dwim_b200_buffer *x, size_t row_begin, size_t total_rows);
+/* One small kernel on the context's stream: tells every rank that this rank's
+ * stores into the shared buffer (everything queued before the call) have
+ * landed, and waits, on the device and bounded by the library's wait limit,
+ * until every rank has said so.  Every rank must call it the same number of
+ * times.  The barrier's count lives in device memory, so the call may be
+ * captured in a CUDA graph and replayed. */
+DWIM_B200_API int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
 
 /* The rows rank `rank` of `world` holds when a matrix is split by output
  * rows at multiples of `align`: [*begin, *end). */
@@ -193,7 +244,9 @@ DWIM_B200_API int dwim_b200_gather_rows(dwim_b200_ctx *ctx, dwim_b200_buffer *ou
  * n floats of `buf` on every rank by their sum over the ranks, added in rank
  * order (the same bits everywhere).  Every rank must make the same calls in the
  * same order; a rank that waits for its peers longer than the library's wait
- * limit gives up, and the next sync reports DWIM_B200_ETIMEOUT. */
+ * limit gives up, and the next sync reports DWIM_B200_ETIMEOUT.  The call's
+ * epoch is a launch argument: peer_allreduce refuses (EINVAL) while the
+ * context's stream is being captured into a CUDA graph. */
 DWIM_B200_API size_t dwim_b200_peer_handle_bytes(void);
 DWIM_B200_API int dwim_b200_peer_create(dwim_b200_ctx *ctx, int world, int rank, size_t cap, void *handle,
                                         size_t handle_bytes);

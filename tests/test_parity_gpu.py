@@ -470,3 +470,157 @@ def test_gemm_above_the_batch_size(dev, oracle):
     out = dev.alloc(n * rows)
     dev.matmul(out, upload(dev, "q4_k", rows, cols, blocks), dev.buffer(x))
     assert max_rel_err(dev.read(out), oracle.matmul("q4_k", blocks, rows, cols, x)) <= 2e-5
+
+
+# ---- the benchmarked GEMM configurations at full size -----------------------------------------
+def bf16_rows(oracle, rng, n, cols):
+    """Config 2's activations: rows of N(0,1) scaled to RMS 1, rounded to bf16."""
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    x /= np.sqrt((x * x).mean(1, keepdims=True))
+    bits = oracle.to_bf16(x)
+    return bits, oracle.bf16(bits).reshape(n, cols)
+
+
+def sampled_rows(rows, rng, count=384):
+    """First, last and a ragged middle stretch of the 128-row tiles, plus random rows."""
+    picks = set(range(min(rows, 130))) | set(range(max(0, rows - 130), rows)) | set(range(rows // 2 - 3, min(rows, rows // 2 + 64)))
+    picks |= set(int(r) for r in rng.choice(rows, min(rows, count), replace=False))
+    return np.array(sorted(picks))
+
+
+_full_weights = {}
+
+
+def full_weight(dev, rows, cols, seed):
+    """A full-size Q4_K matrix, quantized on the device once per session."""
+    key = (rows, cols, seed)
+    if key not in _full_weights:
+        w = 0.02 * np.random.default_rng(seed).standard_normal((rows, cols), dtype=np.float32)
+        t = dev.quantize("q4_k", w)
+        _full_weights.clear()                      # one at a time: 50 MB of blocks, 356 MB of f32 behind them
+        _full_weights[key] = (t, dev.upload(t))
+    return _full_weights[key]
+
+
+@pytest.mark.parametrize("rows,cols,n", [
+    (17408, 5120, 128), (17408, 5120, 512), (17408, 5120, 2048),       # config 2: gate / up
+    (5120, 17408, 128), (5120, 17408, 2048),                            # the transposed down projection
+    (17401, 5120, 512)])                                                # a ragged last row tile
+def test_config2_gemm_full_size(dev, oracle, rows, cols, n):
+    """BASELINE config 2 as the benchmark runs it: Q4_K W x bf16 X through the
+    256-column tensor-core kernel, against the oracle on a row sample that covers
+    the first, last and middle row tiles and every token; plus run-to-run bit
+    equality over the whole output."""
+    rng = np.random.default_rng(2000 + n)
+    t, weight = full_weight(dev, rows, cols, seed=0 if rows != 17401 else 9)
+    bits, x = bf16_rows(oracle, rng, n, cols)
+    xb, out = dev.alloc(n * cols), dev.alloc(n * rows)
+    dev.write_bf16(xb, bits)
+    dev.matmul(out, weight, xb)
+    got = dev.read(out).reshape(n, rows)
+    assert np.isfinite(got).all()
+    sample = sampled_rows(rows, rng)
+    want = oracle.matmul("q4_k", t.select_rows(sample).data, sample.size, cols, x)
+    err = max_rel_err(got[:, sample], want)
+    assert err <= TOL, f"max relative error {err:.2e}"
+    assert err <= 2e-5, f"exact products: only summation order may differ, got {err:.2e}"
+    close_batch(got[:, sample], want, f"q4_k {rows}x{cols} n={n}")
+    dev.matmul(out, weight, xb)
+    assert np.array_equal(dev.read(out).reshape(n, rows), got)
+
+
+@pytest.mark.parametrize("n", [17, 33, 130, 300])
+def test_gemm_bf16_token_counts(dev, oracle, n):
+    """bf16 activations (one f16 column per token) at every tile width of the
+    tensor-core kernel: 32, 64, 256 columns, ragged against each."""
+    rng = np.random.default_rng(3000 + n)
+    rows, cols = 1000, 5120
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    bits, x = bf16_rows(oracle, rng, n, cols)
+    xb, out = dev.alloc(n * cols), dev.alloc(n * rows)
+    dev.write_bf16(xb, bits)
+    dev.matmul(out, upload(dev, "q4_k", rows, cols, blocks), xb)
+    assert max_rel_err(dev.read(out).reshape(n, rows), oracle.matmul("q4_k", blocks, rows, cols, x)) <= 2e-5
+
+
+@pytest.mark.parametrize("bf16", [True, False])
+def test_gemm_fused_epilogues_at_256_columns(dev, oracle, bf16):
+    """matmul_add and swiglu through the 256-column kernel (300 tokens of bf16
+    input, or 150 of f32 travelling as two columns each)."""
+    rng = np.random.default_rng(3100 + bf16)
+    rows, cols, n = 1030, 5120, 300 if bf16 else 150
+    gate = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    up = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    xb = dev.alloc(n * cols)
+    if bf16:
+        bits, x = bf16_rows(oracle, rng, n, cols)
+        dev.write_bf16(xb, bits)
+    else:
+        x = rng.standard_normal((n, cols)).astype(np.float32)
+        dev.write(xb, x)
+    wg, wu = upload(dev, "q4_k", rows, cols, gate), upload(dev, "q4_k", rows, cols, up)
+    out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
+    dev.swiglu(out, wg, wu, xb, scratch)
+    assert max_rel_err(dev.read(out), oracle.swiglu("q4_k", gate, up, rows, cols, x)) <= 1e-4
+    res = rng.standard_normal((n, rows)).astype(np.float32)
+    acc = dev.buffer(res)
+    dev.matmul_add(acc, wg, xb)
+    got, want = dev.read(acc).reshape(n, rows), oracle.matmul_add("q4_k", gate, rows, cols, x, res)
+    assert max_rel_err(got - res, want - res) <= 1e-4
+
+
+# ---- the boundary: a caller's stream, a caller's writes -----------------------------------------
+def test_adopted_stream_and_touch(oracle):
+    """The composition an engine would use: the library opened on the caller's
+    stream, a buffer wrapped over the caller's memory, a kernel of the caller's
+    (torch, on that stream) rewriting it between two products.  After touch the
+    second product sees the new data; the stream orders everything."""
+    import torch
+    from dwim_b200 import B200, Tensor
+    stream = torch.cuda.Stream()
+    d = B200(0, stream=stream.cuda_stream)
+    try:
+        rng = np.random.default_rng(97)
+        rows, cols, n = 640, 1024, 3
+        blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+        weight = d.upload(Tensor("q4_k", (rows, cols), blocks))
+        x1 = rng.standard_normal((n, cols)).astype(np.float32)
+        x2 = rng.standard_normal((n, cols)).astype(np.float32)
+        with torch.cuda.stream(stream):
+            xt = torch.from_numpy(x1).cuda(non_blocking=False)
+            x2t = torch.from_numpy(x2).cuda(non_blocking=False)
+            ot = torch.empty(n * rows, dtype=torch.float32, device="cuda")
+        stream.synchronize()
+        xb, out = d.wrap(xt.data_ptr(), n * cols), d.wrap(ot.data_ptr(), n * rows)
+        d.matmul(out, weight, xb)
+        with torch.cuda.stream(stream):
+            first = ot.clone()
+            xt.copy_(x2t)                    # the caller's kernel, ordered by the shared stream
+        d.touch(xb)
+        d.matmul(out, weight, xb)
+        with torch.cuda.stream(stream):
+            second = ot.clone()
+        stream.synchronize()
+        d.sync()
+        assert max_rel_err(first.cpu().numpy(), oracle.matmul("q4_k", blocks, rows, cols, x1)) <= 2e-5
+        assert max_rel_err(second.cpu().numpy(), oracle.matmul("q4_k", blocks, rows, cols, x2)) <= 2e-5
+    finally:
+        d.close()
+
+
+def test_shared_buffer_in_a_world_of_one(dev, oracle):
+    """matmul_gather and the barrier with a single rank: two row shards written
+    into one shared result at their offsets, as two ranks would."""
+    rng = np.random.default_rng(99)
+    rows, cols = 1000, 1024
+    from dwim_b200 import Tensor
+    t = Tensor("q4_k", (rows, cols), oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)))
+    for n in (1, 5, 40):
+        x = rng.standard_normal((n, cols)).astype(np.float32)
+        out, handle = dev.shared_alloc(n * rows)
+        dev.shared_connect(out, 1, 0, [handle])
+        xb = dev.buffer(x)
+        for b, e in ((0, 496), (496, 1000)):
+            dev.matmul_gather(out, dev.upload(t.slice_rows(b, e)), xb, b, rows)
+        dev.shared_barrier(out)
+        assert max_rel_err(dev.read(out), oracle.matmul("q4_k", t.data, rows, cols, x)) <= 2e-5

@@ -33,6 +33,24 @@ def test_static_scratch_matmul_matches_the_allocating_one(dev, oracle, fmt):
         ref = oracle.matmul(fmt, blocks, rows, cols, x).ravel()
         den = np.maximum(np.abs(ref), np.sqrt(np.mean(ref * ref)))
         assert np.max(np.abs(got - ref) / den) <= 2e-5
+        # and it allocates nothing: the device's free memory is the same before and after
+        dev.sync()
+        free_before = dev.memory()
+        dev.matmul_static(got_b, weight, xb)
+        dev.sync()
+        assert dev.memory() == free_before
+        assert np.array_equal(dev.read(got_b), want)
+
+
+def test_static_scratch_wrapper_checks_lengths(dev, oracle):
+    """A short output buffer must be refused on the host, not written past on the device."""
+    from dwim_b200 import DeviceError, Tensor
+    blocks = oracle.quantize("q8_0", np.ones((16, 256), np.float32))
+    weight = dev.upload(Tensor("q8_0", (16, 256), blocks))
+    with pytest.raises(DeviceError):
+        dev.matmul_static(dev.alloc(2 * 16 - 1), weight, dev.alloc(2 * 256))
+    with pytest.raises(DeviceError):
+        dev.matmul_static(dev.alloc(2 * 16), weight, dev.alloc(2 * 256 + 3))
 
 
 def test_static_scratch_refuses_what_does_not_fit(dev, oracle):
