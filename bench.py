@@ -7,15 +7,20 @@ A step is one matmul of the workload's weight matrix with one batch of M
 synthetic token rows.  The default workload is the prefill GEMM the headline
 metric is quoted on: Q4_K W[17408, 5120] (0.02*N(0,1), quantized by the
 library's own quantizer) times bf16 X[M=2048, 5120] (rows of N(0,1) at RMS 1),
-fp32 accumulate; `--m 1 --workload c1` is the decode GEMV.  With --gpus N the
-weight rows are split over the ranks (one process per GPU), every rank
-multiplies its rows, and the slices are re-assembled on every rank with an
-NCCL all-gather: the total work is fixed (strong scaling).
+fp32 accumulate; `--workload c1` is the decode GEMV.  With --gpus N the weight
+rows are split over the ranks (one process per GPU, total work fixed: strong
+scaling) and, inside the timed step, every rank's product stores its rows of
+the result into every rank's copy of a shared output from its epilogue (plain
+stores over NVLink) and a barrier kernel closes the exchange; `--exchange
+nccl` does the same with an NCCL all-gather after the product, `--exchange
+none` leaves a rank's rows on the rank.
 
 One JSON line is printed by rank 0.  `value` is measured with inputs resident
-in HBM; `e2e` goes through the public API from pinned host memory and back.
-`--impl reference` times the CPU restatement of the reference's own path
-(oracle/, all host threads) on a bounded sample of the same workload.
+in HBM; `e2e` goes through the public API from pinned host memory and back;
+`parity` compares the output that was timed with the CPU oracle on sampled
+rows, on every rank.  `--impl reference` times the CPU restatement of the
+reference's own path (oracle/, all host threads) on a bounded sample of the
+same workload.
 """
 from __future__ import annotations
 
@@ -179,7 +184,7 @@ def run_reference(args, fmt, rows, cols, m, act, ffn=False, decoder=False):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": (ffn_config(rows, cols, m, act, args.gpus) if ffn else
                    {"workload": f"all matrix products of one decoder pass, {m} token(s): 64 layers Q4_K + Q6_K head", "tokens": m}
-                   if decoder else workload_config(fmt, rows, cols, m, act, args.gpus)),
+                   if decoder else workload_config(fmt, rows, cols, m, act, args.gpus, args.exchange)),
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "tok_per_s": m / full,
@@ -205,21 +210,48 @@ def headline(fmt, rows, cols, m, seconds):
     return ("q4k_decode_gemv_hbm_gbs" if fmt == "q4_k" else f"{fmt}_gemv_hbm_gbs"), "GB/s", algorithmic_bytes(fmt, rows, cols, m) / seconds / 1e9
 
 
-def workload_config(fmt, rows, cols, m, act, gpus, gather=False):
+LINK_GBS = 770.0   # measured peer copy per direction on this pool's NVLink 5 (900 nominal)
+
+
+def workload_config(fmt, rows, cols, m, act, gpus, exchange="none"):
     if gpus > 1:
-        sharding = (f"rows/{gpus} + all-gather of the f32 result" if gather else
-                    f"rows/{gpus}; a rank's rows of the result stay on it (they are the K slice its part of the "
-                    "down projection multiplies): no collective on this product; --gather adds the exchange")
+        sharding = {
+            "push": (f"rows/{gpus}; every rank's product stores its rows of the f32 result into all {gpus} copies of a shared "
+                     "output from its epilogue (plain stores over NVLink, while other tiles multiply), then one barrier "
+                     "kernel: the all-gather is inside the timed step"),
+            "nccl": f"rows/{gpus} + NCCL all-gather of the f32 result + re-assembly kernel, inside the timed step",
+            "none": (f"rows/{gpus}; a rank's rows of the result stay on it (they are the K slice its part of the "
+                     "down projection multiplies): no exchange in the step"),
+        }[exchange]
     else:
         sharding = "none"
     return {"workload": f"{fmt.upper()} W[{rows},{cols}] x {act} X[{m},{cols}], fp32 accumulate",
             "format": fmt, "rows": rows, "cols": cols, "tokens": m, "activations": act,
-            "sharding": sharding,
+            "sharding": sharding, "exchange": exchange if gpus > 1 else "none",
             "l2": "weights rotate over copies totalling more than the 126 MB L2"}
 
 
+def conftest_max_rel_err(got, want) -> float:
+    """max |got - want| / max(|want|, rms(want)), the parity tests' measure."""
+    got, want = np.asarray(got, np.float64).ravel(), np.asarray(want, np.float64).ravel()
+    rms = np.sqrt(np.mean(want * want)) if want.size else 0.0
+    den = np.maximum(np.abs(want), max(rms, 1e-30))
+    return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
+
+
+def parity_of(fmt, cols, x, got_rows, w_rows):
+    """The timed output against the oracle on sampled weight rows, all tokens.
+    `got_rows` is [tokens, sample], `w_rows` the f32 weights of the sampled rows
+    (the oracle quantizes them itself: the device quantizer is byte-exact with it)."""
+    import oracle
+    oracle.build()
+    blocks = oracle.quantize(fmt, w_rows)
+    want = oracle.matmul(fmt, blocks, w_rows.shape[0], cols, x)
+    return conftest_max_rel_err(got_rows, want)
+
+
 # ---------------------------------------------------------------------------------------
-def run_gpu(args, name, fmt, rows, cols, m, act):
+def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
     import torch
     from dwim_b200 import B200, Tensor, shard_rows
 
@@ -230,7 +262,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = B200(local)
     ext = torch.cuda.ExternalStream(dev.stream, device=local)
 
@@ -240,7 +273,6 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     my_rows = r1 - r0
     part_rows = shard_rows(rows, 0, world, align)[1]
     t_w = dev.quantize(fmt, w[r0:r1])
-    del w
     # rotate over enough copies of the weights that a pass cannot be served from L2
     wbytes = max(t_w.data.size, 1)
     copies = int(min(16, max(2, -(-3 * L2_BYTES // wbytes))))
@@ -248,28 +280,48 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
 
     xb = dev.alloc(m * cols)
     (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
-    gather = world > 1 and args.gather
-    if gather:
+    exchange = args.exchange if world > 1 else "none"
+    outs = []
+    if exchange == "push":
+        # two shared results, alternating: a rank may run one step ahead of its peers
+        for _ in range(2):
+            buf, handle = dev.shared_alloc(m * rows)
+            handles = [None] * world
+            dist.all_gather_object(handles, handle)
+            dev.shared_connect(buf, world, rank, handles)
+            outs.append(buf)
+        dist.barrier()
+    elif exchange == "nccl":
         if my_rows != part_rows:
             raise SystemExit(f"{rows} rows do not split evenly over {world} ranks at multiples of {align}")
-        parts_t = torch.empty(world * m * part_rows, dtype=torch.float32, device="cuda")
+        with torch.cuda.stream(ext):
+            parts_t = torch.empty(world * m * part_rows, dtype=torch.float32, device=f"cuda:{local}")
         mine_t = parts_t[rank * m * part_rows:(rank + 1) * m * part_rows]
         out_local = dev.wrap(mine_t.data_ptr(), m * my_rows)
         parts = dev.wrap(parts_t.data_ptr(), parts_t.numel())
-        out = dev.alloc(m * rows)
+        outs.append(dev.alloc(m * rows))
     else:
-        out_local = out = dev.alloc(m * my_rows)
+        outs.append(dev.alloc(m * my_rows))
 
     per_rank = []
 
-    def step(i, fresh_input=True):
-        if fresh_input:
-            dev.resize(xb, m * cols)          # marks the input as rewritten: its 16-bit operand form is rebuilt
-        dev.matmul(out_local, weights[i % copies], xb)
-        if gather:
+    def product(i):
+        if exchange == "push":
+            out = outs[i % 2]
+            dev.matmul_gather(out, weights[i % copies], xb, r0, rows)
+            dev.shared_barrier(out)
+        elif exchange == "nccl":
+            dev.matmul(out_local, weights[i % copies], xb)
             with torch.cuda.stream(ext):
                 dist.all_gather_into_tensor(parts_t, mine_t)
-            dev.gather_rows(out, parts, m, rows, world, align)
+            dev.gather_rows(outs[0], parts, m, rows, world, align)
+        else:
+            dev.matmul(outs[0], weights[i % copies], xb)
+
+    def step(i, fresh_input=True):
+        if fresh_input:
+            dev.touch(xb)                     # the input counts as rewritten: its 16-bit operand form is rebuilt
+        product(i)
 
     def timed(n_steps, fresh_input=True):
         if dist:
@@ -301,11 +353,70 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     with ClockSampler(local) as clocks:
         seconds, launches = timed(args.steps)
         ranks_report = list(per_rank)
-        # the dominant kernel alone (operand form cached): what the roofline is about
-        kernel_seconds, _ = timed(args.steps, fresh_input=False)
+        # the dominant kernel alone (operand form cached, no exchange): what the roofline is about
+        saved = exchange
+        kernel_seconds = None
+        if exchange == "none":
+            kernel_seconds, _ = timed(args.steps, fresh_input=False)
     per_step = seconds / args.steps
+    if kernel_seconds is None:
+        # N > 1 with an exchange: the product alone on this rank's rows, into a local buffer
+        local_out = dev.alloc(m * my_rows)
+        dev.sync()
+        for i in range(3):
+            dev.matmul(local_out, weights[i % copies], xb)
+        dev.timer_begin()
+        for i in range(args.steps):
+            dev.matmul(local_out, weights[i % copies], xb)
+        kernel_seconds = dev.timer_end() / 1e3
+        del local_out
     per_kernel = kernel_seconds / args.steps
     metric, unit, value = headline(fmt, rows, cols, m, per_step)
+
+    # ---- a long timed region: clocks settle under sustained load (the short one above runs in the boost window) ----
+    sustained = None
+    if args.sustain > 0 and not quiet:
+        n_long = int(max(args.steps, min(200000, args.sustain / max(per_step, 1e-6))))
+        with ClockSampler(local) as long_clocks:
+            long_s, _ = timed(n_long)
+        _, _, long_value = headline(fmt, rows, cols, m, long_s / n_long)
+        sustained = {"value": long_value, "unit": unit, "steps": n_long, "seconds": long_s, "ms_per_step": long_s / n_long * 1e3,
+                     "clocks": long_clocks.summary()}
+
+    # ---- parity of what was just timed: sampled weight rows, every token, against the oracle ----
+    dev.touch(xb)
+    product(0)
+    product(1)                                       # both shared results, when there are two
+    dev.sync()
+    if dist:
+        dist.barrier()
+    rng = np.random.default_rng(1234 + rank)
+    worst, sampled = 0.0, 0
+    for out in outs:
+        got = dev.read(out)
+        if exchange == "none":
+            sample = np.unique(np.concatenate([np.arange(min(my_rows, 130)), np.arange(max(0, my_rows - 130), my_rows),
+                                               rng.choice(my_rows, min(my_rows, 128), replace=False)]))
+            got_rows, w_rows = got.reshape(m, my_rows)[:, sample], w[r0:r1][sample]
+        else:
+            # the assembled result on this rank: rows from every rank's shard, the cuts included
+            cuts = np.concatenate([np.arange(max(0, b - 8), min(rows, b + 8)) for b in
+                                   (shard_rows(rows, r, world, align)[0] for r in range(world))])
+            sample = np.unique(np.concatenate([cuts, np.arange(rows - 64, rows), rng.choice(rows, min(rows, 320), replace=False)]))
+            got_rows, w_rows = got.reshape(m, rows)[:, sample], w[sample]
+        tok = np.arange(m) if m <= 256 else np.unique(np.concatenate([np.arange(130), np.arange(m - 130, m), rng.choice(m, 64, replace=False)]))
+        worst = max(worst, parity_of(fmt, cols, x[tok], got_rows[tok], w_rows))
+        sampled = int(sample.size)
+        n_tok = int(tok.size)
+        del got
+    del w
+    if dist:
+        t = torch.tensor([worst], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = float(t.item())
+    parity = {"max_rel_err": worst, "tolerance": 1e-3, "ok": bool(worst <= 1e-3), "rows_sampled_per_rank": sampled,
+              "tokens_checked": n_tok, "checked": "every rank's copy of the timed output against the CPU oracle"
+              if exchange != "none" else "every rank's rows of the timed output against the CPU oracle"}
 
     # ---- end to end: pinned host memory -> device -> product -> pinned host memory ----
     if bits is not None:
@@ -314,20 +425,13 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
     else:
         hx = torch.empty(m * cols, dtype=torch.float32, pin_memory=True).numpy()
         hx[:] = x.ravel()
-    hout = torch.empty(len(out), dtype=torch.float32, pin_memory=True).numpy()
+    hout = torch.empty(len(outs[0]), dtype=torch.float32, pin_memory=True).numpy()
     e2e_steps = max(3, min(args.steps, 20))
 
     def e2e_step(i):
         (dev.write_bf16(xb, hx) if bits is not None else dev.write(xb, hx))
-        step_no_resize(i)
-        dev.read(out, hout)
-
-    def step_no_resize(i):
-        dev.matmul(out_local, weights[i % copies], xb)
-        if gather:
-            with torch.cuda.stream(ext):
-                dist.all_gather_into_tensor(parts_t, mine_t)
-            dev.gather_rows(out, parts, m, rows, world, align)
+        product(i)
+        dev.read(outs[i % len(outs)], hout)
 
     for i in range(2):
         e2e_step(i)
@@ -340,6 +444,7 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
         e2e_s, e2e_mean_s = float(t[0].item()), float(t[1].item())
     _, _, e2e_value = headline(fmt, rows, cols, m, e2e_s)
 
+    line = None
     if rank == 0:
         pk = peaks()
         gemm = m > 16
@@ -360,7 +465,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
                     "frac": achieved / pk["tflops"], "traffic": traffic, "traffic_source": traffic_note,
                     "peak_source": pk["source"],
-                    "frac_of_sustained": achieved / pk["tflops_sustained"] if pk["tflops_sustained"] else None}
+                    "frac_of_sustained": achieved / pk["tflops_sustained"] if pk["tflops_sustained"] else None,
+                    "frac_of_nominal_2250": achieved / 2250.0}
         else:
             by = algorithmic_bytes(fmt, my_rows, cols, m)
             achieved = by / per_kernel / 1e9
@@ -369,11 +475,21 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
                     "peak_source": pk["source"],
                     "frac_of_nominal_8tbs": achieved / 8000.0}
         roof["kernel_us"] = per_kernel * 1e6
+        if exchange != "none":
+            # the fused step: no faster than the slower of its product at the measured peak and its
+            # bytes over NVLink at the measured per-direction rate
+            link_bytes = (world - 1) * m * my_rows * 4
+            t_link = link_bytes / (LINK_GBS * 1e9)
+            t_math = (2.0 * m * my_rows * cols / (pk["tflops"] * 1e12)) if gemm else algorithmic_bytes(fmt, my_rows, cols, m) / (pk["hbm_gbs"] * 1e9)
+            roof["step"] = {"bound": "nvlink" if t_link > t_math else roof["bound"], "target_us": max(t_link, t_math) * 1e6,
+                            "achieved_us": per_step * 1e6, "frac": max(t_link, t_math) / per_step,
+                            "nvlink_bytes_out_per_rank": int(link_bytes), "nvlink_gbs_out_per_rank": link_bytes / per_step / 1e9,
+                            "nvlink_peak_gbs": LINK_GBS, "nvlink_frac": link_bytes / per_step / 1e9 / LINK_GBS}
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 (exact integer weights x f16 activations), f32 accumulate", "data": "synthetic",
-            "config": workload_config(fmt, rows, cols, m, act, world, gather),
+            "config": workload_config(fmt, rows, cols, m, act, world, exchange),
             "tok_per_s": m / per_step,
             "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(hx.nbytes),
                     "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3, "ms_per_step_mean": e2e_mean_s * 1e3,
@@ -381,16 +497,18 @@ def run_gpu(args, name, fmt, rows, cols, m, act):
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": roof,
+            "parity": parity,
             "device": dev.name(),
             "ranks": ranks_report,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(fmt, rows, cols, m, act)
-        print(json.dumps(line))
-        sys.stdout.flush()
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
+        if sustained:
+            if gemm and pk["tflops_sustained"]:
+                sustained["frac_of_sustained_peak"] = sustained["value"] / world / pk["tflops_sustained"]
+            line["sustained"] = sustained
+    # release everything before another workload runs in this process
+    del weights, outs
+    dev.close()
+    return line
 
 
 def ffn_config(inner, hidden, m, act, gpus):
@@ -413,7 +531,8 @@ def run_ffn(args, fmt, inner, hidden, m, act):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = B200(local)
 
     # every rank draws the same block (seed 5) and keeps its shard
@@ -452,7 +571,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
     (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
 
     def step(i):
-        dev.resize(xb, m * hidden)            # the input counts as rewritten: its operand form is rebuilt
+        dev.touch(xb)                         # the input counts as rewritten: its operand form is rebuilt
         return blocks[i % copies].forward(xb)
 
     def timed(n_steps):
@@ -497,6 +616,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
 
+    line = None
     if rank == 0:
         pk = peaks()
         if m > 16:
@@ -522,11 +642,8 @@ def run_ffn(args, fmt, inner, hidden, m, act):
             dt = cb["ms_per_step"] * 3 / 1e3
             line["cpu_baseline"] = {"value": m / dt, "unit": "tok/s", "cores": cb["cores"], "kind": "port",
                                     "sample": cb["sample"] + ", times three for gate, up and down", "ms_per_step": dt * 1e3}
-        print(json.dumps(line))
-        sys.stdout.flush()
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
+        return line
+    return None
 
 
 def run_decoder(args, m):
@@ -555,7 +672,8 @@ def run_decoder(args, m):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = B200(local)
     rng = np.random.default_rng(4)
     hidden, inner, attn, vocab = 5120, 17408, 6144, 151936
@@ -609,19 +727,19 @@ def run_decoder(args, m):
 
     def token():
         for l, w in enumerate(layers):
-            dev.resize(x, m * hidden)                       # the layer's normalized input
+            dev.touch(x)                                    # the layer's normalized input
             if l % 4 == 3:
                 dev.matmul(outs["qg"], w[0], x); dev.matmul(outs["kv"], w[1], x); dev.matmul(outs["kv"], w[2], x)
-                dev.resize(a, m * my_attn); closing(w[3], a)
+                dev.touch(a); closing(w[3], a)
                 f = w[4:]
             else:
                 dev.matmul(outs["qkv"], w[0], x); dev.matmul(outs["z"], w[1], x)
-                dev.resize(a, m * my_attn); closing(w[2], a)
+                dev.touch(a); closing(w[2], a)
                 f = w[3:]
-            dev.resize(x, m * hidden)                       # normalized again before the feed-forward block
+            dev.touch(x)                                    # normalized again before the feed-forward block
             dev.swiglu(h, f[0], f[1], x, scratch)
             closing(f[2], h)
-        dev.resize(x, m * hidden)
+        dev.touch(x)
         dev.matmul(logits, head, x)
 
     for _ in range(max(2, args.warmup // 2)):
@@ -682,10 +800,8 @@ def run_decoder(args, m):
     pk = peaks()
     achieved = total / seconds / 1e9
     if rank != 0:
-        dist.barrier()
-        dist.destroy_process_group()
-        return
-    print(json.dumps({
+        return None
+    return {
         "metric": "decode_matmul_tok_per_s", "value": m / seconds, "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": max(2, args.warmup // 2), "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8/f16 (exact integer weights), f32 accumulate", "data": "synthetic",
@@ -701,11 +817,7 @@ def run_decoder(args, m):
                      "traffic": None, "peak_source": pk["source"],
                      "note": "weight bytes of the whole pass over its time: all kernels, prologues and launch gaps included"},
         "device": dev.name(),
-    }))
-    sys.stdout.flush()
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
+    }
 
 
 def cpu_baseline(fmt, rows, cols, m, act):
@@ -746,8 +858,11 @@ def main():
     ap.add_argument("--m", "--tokens", dest="m", type=int, default=None, help="tokens per step (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--nccl", action="store_true", help="c5, N > 1: NCCL for the partial sums even for a few tokens")
-    ap.add_argument("--gather", action="store_true",
-                    help="N > 1: all-gather the row-sharded result onto every rank inside the step")
+    ap.add_argument("--exchange", default="push", choices=["push", "nccl", "none"],
+                    help="N > 1: how the row-sharded result reaches every rank inside the step: stores from the product's "
+                         "epilogue into every rank's copy (push, default), an NCCL all-gather, or not at all (rows stay sharded)")
+    ap.add_argument("--sustain", type=float, default=2.0, help="seconds of the second, long timed region (0: skip)")
+    ap.add_argument("--no-also", action="store_true", help="N = 1, default workload: skip the decode GEMV line embedded under 'also'")
     args = ap.parse_args()
     fmt, rows, cols, m, act = WORKLOADS[args.workload]
     if args.m:
@@ -756,15 +871,42 @@ def main():
         run_reference(args, fmt, rows, cols, m, act, ffn=args.workload == "c5", decoder=args.workload == "c4")
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     if world != args.gpus:
         if args.gpus > 1:
             raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE is {world})")
     if args.workload == "c4":
-        run_decoder(args, m)
+        line = run_decoder(args, m)
     elif args.workload == "c5":
-        run_ffn(args, fmt, rows, cols, m, act)
+        line = run_ffn(args, fmt, rows, cols, m, act)
     else:
-        run_gpu(args, args.workload, fmt, rows, cols, m, act)
+        line = run_gpu(args, args.workload, fmt, rows, cols, m, act)
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(fmt, rows, cols, m, act)
+        if world == 1 and args.workload == "c2" and args.m is None and not args.no_also:
+            # the other half of the headline metric, measured in the same process: the decode GEMV
+            # (config 1) and every matrix product of a decoded token (config 4)
+            also = {}
+            f1, r1, c1, m1, a1 = WORKLOADS["c1"]
+            l1 = run_gpu(args, "c1", f1, r1, c1, m1, a1, quiet=True)
+            also["c1"] = {"metric": l1["metric"], "gbs_per_step": l1["value"], "us_per_step": l1["ms_per_step"] * 1e3,
+                          "kernel_us": l1["roofline"]["kernel_us"], "kernel_gbs": l1["roofline"]["achieved"],
+                          "frac": l1["roofline"]["frac"], "frac_of_nominal_8tbs": l1["roofline"]["frac_of_nominal_8tbs"],
+                          "parity": l1["parity"], "config": l1["config"]["workload"]}
+            for tokens in (1, 4):
+                l4 = run_decoder(args, tokens)
+                also[f"c4_m{tokens}"] = {"metric": l4["metric"], "tok_per_s": l4["value"], "ms_per_pass": l4["ms_per_step"],
+                                         "hbm_frac": l4["roofline"]["frac"], "graph_replay": l4["graph_replay"],
+                                         "launches_per_pass": l4["gpu_launches"], "config": l4["config"]["workload"]}
+            line["also"] = also
+    if rank == 0 and line is not None:
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if world > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":

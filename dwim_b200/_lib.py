@@ -10,7 +10,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libdwim_b200.so"
 
-Q8_0, Q4_K, Q6_K = 8, 12, 14
+Q8_0, Q4_K, Q6_K, BF16 = 8, 12, 14, 30
 
 OK, EINVAL, EFORMAT, ENOMEM, ECUDA, ENODEV, ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 ERROR_NAMES = {EINVAL: "EINVAL", EFORMAT: "EFORMAT", ENOMEM: "ENOMEM", ECUDA: "ECUDA", ENODEV: "ENODEV",
@@ -53,6 +53,8 @@ SIGNATURES = {
     "dwim_b200_matmul": (C.c_int, [_vp, _vp, _vp, _vp]),
     "dwim_b200_matmul_add": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "dwim_b200_swiglu": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "dwim_b200_normalize": (C.c_int, [_vp, _vp, _vp, _vp, _sz, C.c_float]),
+    "dwim_b200_argmax": (C.c_int, [_vp, _vp, _sz, C.POINTER(C.c_uint32), _sz]),
     "dwim_b200_matmul_static": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "dwim_b200_shared_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp), _vp, _sz]),
     "dwim_b200_shared_connect": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _sz]),

@@ -16,7 +16,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libdwim_b200.so"
-SOURCES = ["abi.cu", "codec.cu", "prologue.cu", "gemv.cu", "gemm.cu", "static_scratch.cu", "peer.cu"]
+SOURCES = ["abi.cu", "codec.cu", "prologue.cu", "gemv.cu", "gemm.cu", "static_scratch.cu", "peer.cu", "neighbours.cu"]
 
 
 def nvcc() -> str:

@@ -17,8 +17,7 @@ static thread_local char g_open_error[512] = "";
 // whole 256-weight units and may read past the last row's end.
 static constexpr size_t WEIGHT_SLACK = 1024;
 
-// Tokens above which the tensor-core GEMM takes over from the small-M kernel.
-static constexpr size_t SMALL_M_MAX = 16;
+static constexpr size_t SMALL_M_MAX = DWIM_SMALL_M_MAX;
 
 namespace dwim {
 // gemm.cu
@@ -102,6 +101,8 @@ int dwim_b200_close(dwim_b200_ctx *ctx) {
     peer_release(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->argmax_dev) cudaFree(ctx->argmax_dev);
+    if (ctx->argmax_host) cudaFreeHost(ctx->argmax_host);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->stream && ctx->stream_owned) cudaStreamDestroy(ctx->stream);
@@ -284,7 +285,7 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
                      dwim_b200_weight **out) {
     if (!ctx || !out) return DWIM_B200_EINVAL;
     *out = nullptr;
-    REQUIRE(ctx, fmt == Q8_0 || fmt == Q4_K || fmt == Q6_K, DWIM_B200_EFORMAT, "unknown weight format %d", fmt);
+    REQUIRE(ctx, fmt == Q8_0 || fmt == Q4_K || fmt == Q6_K || fmt == BF16, DWIM_B200_EFORMAT, "unknown weight format %d", fmt);
     size_t rb = file_row_bytes(fmt, cols);
     REQUIRE(ctx, cols > 0 && rb > 0, DWIM_B200_EFORMAT, "%zu columns are not whole blocks of %d weights", cols,
             block_weights(fmt));
@@ -310,7 +311,7 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
     if (e == cudaSuccess) e = cudaMemsetAsync((uint8_t *)w->quants_alloc + rows * w->v.qpitch, 0, WEIGHT_SLACK, ctx->stream);
     int rc = 0;
     if (e == cudaSuccess && bytes) {
-        if (fmt == Q4_K) {
+        if (fmt == Q4_K || fmt == BF16) {
             e = cudaMemcpy2DAsync(w->quants_alloc, w->v.qpitch, blocks, rb, rb, rows, cudaMemcpyHostToDevice, ctx->stream);
         } else {
             e = cudaMalloc(&staging, bytes);
@@ -411,7 +412,7 @@ int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, co
 static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size_t cols, int split) {
     if (x->shadow_kind == kind && x->shadow_cols == cols && x->shadow_split == split) return 0;
     size_t n = x->len / cols;
-    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n * (split ? 2 : 1))
+    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n, split)
                   : kind == SHADOW_PANEL_I8 ? panel_i8_bytes(cols, n)
                                             : panel_bytes(cols, (int)n * (split ? 2 : 1));
     if (need > x->shadow_cap) {
@@ -444,6 +445,8 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
             out_len, n, out.pitch);
     if (n == 0 || v.rows == 0) return 0;
     REQUIRE(ctx, out.dst[0] != x->data, DWIM_B200_EINVAL, "%s: output aliases input", what);
+    // bf16 weights (the small gate matrices): f32 activations as they are, fp32 throughout
+    if (v.fmt == BF16) return matmul_bf16(ctx, v, x->data, n, out, aux, epilogue);
     // bf16 activations are exact in one f16 column; f32 ones travel as two
     // (value and rounding remainder), summed again in the epilogue.
     if (n > SMALL_M_MAX && gemm_supports(v)) {

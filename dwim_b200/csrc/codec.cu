@@ -70,6 +70,8 @@ __global__ void dequantize_kernel(WeightView w, float *__restrict__ out) {
         } else if (w.fmt == Q6_K) {
             float d = __half2float(w.scales[r * w.srow + (k >> 8)]);
             v = q6k_weight(row + (k >> 8) * Q6_K_DEV, d, (int)(k & 255));
+        } else if (w.fmt == BF16) {
+            v = __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(row)[k] << 16);   // gpu/float.rs:5-8
         } else {
             // gpu/quant.rs:48-62: q as f32 * d
             float d = __half2float(w.scales[r * w.srow + (k >> 5)]);

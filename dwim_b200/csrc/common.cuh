@@ -67,6 +67,9 @@ struct dwim_b200_ctx {
     // (an upload's repack): that launch must be an ordinary one, because a
     // programmatic dependent streams weights before it waits for the kernels ahead.
     bool weights_written = false;
+    // argmax's result slots: device keys, their pinned host copy (neighbours.cu), created on request
+    unsigned long long *argmax_dev = nullptr, *argmax_host = nullptr;
+    size_t argmax_cap = 0;
     // the peer all-reduce's mailbox and mappings (peer.cu), created on request
     void *peer_state = nullptr;
     // device address of the fixed scratch array of dwim_b200_matmul_static (static_scratch.cu)
@@ -154,17 +157,22 @@ int quantize_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const
 constexpr int PANEL_STRIDE = 272;
 size_t panel_bytes(size_t cols, int ncols);
 int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels);
-// int8 panels: per unit of 256 activations one blob of i8_unit_bytes(nc), nc = 4 * tokens columns
-// (column = 4*token + plane):
+// int8 panels: per unit of 256 activations one blob of i8_unit_bytes(nc), nc = planes * tokens columns
+// (column = 4*token + plane for one and two tokens, plane*tokens + token for three to eight):
 //   [sub-block j (8)][column][32 digits]        256*nc B
 //   [column][a_0..a_7 | b_0..b_7]                16*nc B   the digits' sums per sub-block, 128*a + b
 //   [column] float                                4*nc B   what one unit of the plane's digit is worth
-constexpr int I8_MAX_TOKENS = 2;
+constexpr int I8_MAX_TOKENS = 8;
+constexpr int i8_planes(int n) { return n <= 2 ? 4 : 3; }   // digit planes per token
 constexpr int i8_unit_bytes(int nc) { return 276 * nc; }
 size_t panel_i8_bytes(size_t cols, size_t n);
-int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, uint8_t *panels);
-size_t gemm_operand_bytes(size_t cols, size_t ncols);
-int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out);
+int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, uint8_t *panels, const float *weight = nullptr,
+                    float eps = 0.0f, float *xout = nullptr);
+// Tokens above which the tensor-core GEMM takes over from the small-M kernel.
+constexpr size_t DWIM_SMALL_M_MAX = 16;
+size_t gemm_operand_bytes(size_t cols, size_t n, int split);
+int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out,
+                       const float *weight = nullptr, float eps = 0.0f, float *xout = nullptr);
 
 // gemv.cu
 enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
@@ -175,6 +183,8 @@ int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels
                   int epilogue, const WeightView *up = nullptr);
 void peer_release(dwim_b200_ctx *ctx);
 void shared_release(dwim_b200_buffer *buf);
+// neighbours.cu
+int matmul_bf16(dwim_b200_ctx *ctx, const WeightView &w, const float *x, size_t n, const OutSpec &out, const float *aux, int epi);
 // static_scratch.cu
 int static_scratch_prepare(dwim_b200_ctx *ctx);
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,

@@ -23,7 +23,7 @@
 
 namespace dwim {
 
-enum Format : int { Q8_0 = 8, Q4_K = 12, Q6_K = 14 };
+enum Format : int { Q8_0 = 8, Q4_K = 12, Q6_K = 14, BF16 = 30 };   // GGUF's type ids (inference/gguf.rs:28-33)
 
 constexpr int Q8_0_FILE = 34, Q4_K_FILE = 144, Q6_K_FILE = 210;
 constexpr int Q6_K_DEV = 208;
@@ -31,12 +31,13 @@ constexpr int Q6_K_DEV = 208;
 __host__ __device__ inline size_t pad8(size_t n) { return (n + 7) & ~size_t(7); }
 
 // Weights per scale unit along K.
-__host__ __device__ inline int block_weights(int fmt) { return fmt == Q8_0 ? 32 : 256; }
+__host__ __device__ inline int block_weights(int fmt) { return fmt == BF16 ? 1 : fmt == Q8_0 ? 32 : 256; }
 __host__ __device__ inline size_t file_row_bytes(int fmt, size_t cols) {
     switch (fmt) {
     case Q8_0: return cols % 32 ? 0 : cols / 32 * Q8_0_FILE;
     case Q4_K: return cols % 256 ? 0 : cols / 256 * Q4_K_FILE;
     case Q6_K: return cols % 256 ? 0 : cols / 256 * Q6_K_FILE;
+    case BF16: return cols * 2;
     default: return 0;
     }
 }
@@ -46,11 +47,13 @@ __host__ __device__ inline size_t dev_quant_row_bytes(int fmt, size_t cols) {
     switch (fmt) {
     case Q8_0: return cols;
     case Q4_K: return cols / 256 * Q4_K_FILE;
+    case BF16: return cols * 2;
     default: return cols / 256 * Q6_K_DEV;
     }
 }
 __host__ __device__ inline size_t dev_quant_pitch(int fmt, size_t cols) {
     size_t b = dev_quant_row_bytes(fmt, cols);
+    if (fmt == BF16) return b;   // plain rows (cols is a multiple of 8: 16-byte aligned)
     return (b / 16) % 2 == 0 ? b + 16 : b;
 }
 __host__ __device__ inline size_t dev_scale_row_elems(int fmt, size_t cols) {

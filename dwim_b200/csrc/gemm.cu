@@ -70,6 +70,7 @@ struct GemmArgs {
     size_t rows, n, ncols, units;   // weight rows, tokens, operand columns, 256-weight units of K
     int split;                      // 1: columns 2t, 2t+1 are token t's hi and lo halves
     OutSpec out;
+    const float *tok_scale;         // per token: the power of two its activations were divided by (prologue.cu)
     const float *aux;               // EPI_SWIGLU: the `up` product, token-major [n][rows]
     int epi;
     uint32_t *status;
@@ -210,6 +211,7 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f
 // One finished element: the operator's epilogue, then the store (to every rank's copy of a shared result).
 __device__ __forceinline__ void gemm_emit(const GemmArgs &a, size_t t, size_t row, float x) {
     const size_t i = t * a.out.pitch + a.out.row0 + row;
+    x *= __ldg(a.tok_scale + t);
     if (a.epi == EPI_ADD) x += a.out.dst[0][i];
     else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[t * a.rows + row]);
     a.out.dst[0][i] = x;
@@ -602,7 +604,8 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     if ((rc = encode_2d(ctx, &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand + ncols * w.cols, units * 16, ncols, units * 32, 8,
                         BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
         return rc;
-    GemmArgs a{w.rows, n, ncols, units, split, out, aux, epi, ctx->status};
+    const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
+    GemmArgs a{w.rows, n, ncols, units, split, out, tok_scale, aux, epi, ctx->status};
     auto kern = gemm_q4k_kernel<BN>;
     static bool configured[64] = {false};
     if (!configured[ctx->device & 63]) {

@@ -81,10 +81,16 @@ constexpr uint32_t H2_SIXTEENTH = 0x2C002C00u;  // half2(1/16, 1/16)
 // Q4_K through the int8 tensor-core path (one or two tokens): the same blocks,
 // another activation operand and unit routine.
 constexpr int Q4K_I8 = 1012;
+constexpr int Q8_I8 = 1008;     // Q8_0 and Q6_K through the same int8 path (up to eight tokens)
+constexpr int Q6K_I8 = 1014;
+constexpr bool is_i8(int fmt) { return fmt == Q4K_I8 || fmt == Q8_I8 || fmt == Q6K_I8; }
+constexpr int base_of(int fmt) { return fmt == Q4K_I8 ? (int)Q4_K : fmt == Q8_I8 ? (int)Q8_0 : fmt == Q6K_I8 ? (int)Q6_K : fmt; }
 
 template <int FMT> struct Traits;
 template <> struct Traits<Q4_K> { static constexpr int UNIT_Q = 144; };
 template <> struct Traits<Q4K_I8> { static constexpr int UNIT_Q = 144; };
+template <> struct Traits<Q8_I8> { static constexpr int UNIT_Q = 256; };
+template <> struct Traits<Q6K_I8> { static constexpr int UNIT_Q = 208; };
 template <> struct Traits<Q6_K> { static constexpr int UNIT_Q = 208; };
 template <> struct Traits<Q8_0> { static constexpr int UNIT_Q = 256; };
 
@@ -224,58 +230,215 @@ __device__ __forceinline__ float2 lds64f2(uint32_t a) {
     return v;
 }
 
-// Lane (g, c) owns bytes [8c, 8c+8) of each 32-byte group of its two rows: MMA
+__device__ __forceinline__ void imma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// 16 rows x 16 k: one 16-weight scale group of Q6_K
+__device__ __forceinline__ void imma16_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+__device__ __forceinline__ float lds32f(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+
+// The digit planes' columns as the int8 routines see them: NTILE column tiles
+// of the MMA (8 columns each).  Tile p's column g is blob column
+// p*tile_stride + g, present when g < tile_cols.
+//   one and two tokens:  one tile, column = 4*token + plane, tile_cols = 4n
+//   three to eight:      a tile per plane, column g = token g, tile_stride = tile_cols = n
+// In both a lane's accumulators are (row a | row b) x (tile column 2c, 2c+1).
+struct I8Cols {
+    int nc;           // columns in a unit's blob
+    int tile_stride;
+    int tile_cols;
+};
+
+// Q4_K.  Lane (g, c) owns bytes [8c, 8c+8) of each 32-byte group of its two rows: MMA
 // k-slots 4c..4c+3 and 16+4c..16+4c+3, matched by the same eight digits of the
-// lane's column.  acc: (row a, col 2c), (row a, col 2c+1), (row b, ..), (row b, ..).
-__device__ __forceinline__ void unit_q4k_i8(const Lane &L, int ul, int xu, int nc, float (&acc)[4]) {
+// lane's column.  acc: (row a, col 2c), (row a, col 2c+1), (row b, ..), (row b, ..),
+// summed over the tiles (the planes of a token, in the layout of three to eight tokens).
+template <int NTILE>
+__device__ __forceinline__ void unit_q4k_i8(const Lane &L, const I8Cols X, int ul, int xu, float (&acc)[4]) {
     const uint32_t ba = L.row_a + ul * 144, bb = L.row_b + ul * 144;
     const uint4 ha = lds128(ba), hb = lds128(bb);
-    const uint32_t blob = L.xbase + xu * i8_unit_bytes(nc);
-    const bool bcol = L.g < nc, ccol = 2 * L.c < nc;   // this lane's B column / accumulator columns exist
+    const uint32_t blob = L.xbase + xu * i8_unit_bytes(X.nc);
+    const bool bcol = L.g < X.tile_cols;   // this lane's B column exists
     // the 6-bit scales and minimums as bytes: entries 0..3 and 4..7
     const uint32_t sa[2] = {ha.y & 0x3f3f3f3fu, (ha.w & 0x0f0f0f0fu) | ((ha.y >> 2) & 0x30303030u)};
     const uint32_t sb[2] = {hb.y & 0x3f3f3f3fu, (hb.w & 0x0f0f0f0fu) | ((hb.y >> 2) & 0x30303030u)};
-    int ilo[4] = {0, 0, 0, 0}, ihi[4] = {0, 0, 0, 0};
+    int ilo[NTILE][4], ihi[NTILE][4];
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) ilo[p][i] = ihi[p][i] = 0;
     const uint32_t qa = ba + 16 + 8 * L.c, qb = bb + 16 + 8 * L.c;
-    uint32_t xcol = blob + L.g * 32 + 8 * L.c;      // this lane's column, sub-block 0; a sub-block further on is 32*nc
-    const uint32_t xstep = 32 * nc;
+    uint32_t xcol = blob + L.g * 32 + 8 * L.c;      // this lane's column of tile 0, sub-block 0
+    const uint32_t xstep = 32 * X.nc;                // a sub-block further on
+    const uint32_t tstep = 32 * X.tile_stride;       // a tile further on
 #pragma unroll
     for (int G = 0; G < 4; G++) {   // group G: low nibbles = sub-block 2G, high nibbles = 2G+1
         const uint2 wa = lds64(qa + 32 * G), wb = lds64(qb + 32 * G);
-        uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
-        if (bcol) {
-            x0 = lds64(xcol);
-            x1 = lds64(xcol + xstep);
-        }
-        xcol += 2 * xstep;
-        int c0[4], c1[4];
-        imma_u8s8(c0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, x0.x, x0.y);
-        imma_u8s8(c1, wa.x & 0xf0f0f0f0u, wb.x & 0xf0f0f0f0u, wa.y & 0xf0f0f0f0u, wb.y & 0xf0f0f0f0u, x1.x, x1.y);
         // the two sub-blocks' scales: bytes 2(G&1) and 2(G&1)+1 of the word, each by one byte permute
         const int s0a = (int)prmt(sa[G >> 1], 0u, 0x4440u + 2 * (G & 1)), s1a = (int)prmt(sa[G >> 1], 0u, 0x4441u + 2 * (G & 1));
         const int s0b = (int)prmt(sb[G >> 1], 0u, 0x4440u + 2 * (G & 1)), s1b = (int)prmt(sb[G >> 1], 0u, 0x4441u + 2 * (G & 1));
-        ilo[0] += s0a * c0[0]; ilo[1] += s0a * c0[1]; ilo[2] += s0b * c0[2]; ilo[3] += s0b * c0[3];
-        ihi[0] += s1a * c1[0]; ihi[1] += s1a * c1[1]; ihi[2] += s1b * c1[2]; ihi[3] += s1b * c1[3];
+#pragma unroll
+        for (int p = 0; p < NTILE; p++) {
+            uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
+            if (bcol) {
+                x0 = lds64(xcol + p * tstep);
+                x1 = lds64(xcol + p * tstep + xstep);
+            }
+            int c0[4], c1[4];
+            imma_u8s8(c0, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, x0.x, x0.y);
+            imma_u8s8(c1, wa.x & 0xf0f0f0f0u, wb.x & 0xf0f0f0f0u, wa.y & 0xf0f0f0f0u, wb.y & 0xf0f0f0f0u, x1.x, x1.y);
+            ilo[p][0] += s0a * c0[0]; ilo[p][1] += s0a * c0[1]; ilo[p][2] += s0b * c0[2]; ilo[p][3] += s0b * c0[3];
+            ihi[p][0] += s1a * c1[0]; ihi[p][1] += s1a * c1[1]; ihi[p][2] += s1b * c1[2]; ihi[p][3] += s1b * c1[3];
+        }
+        xcol += 2 * xstep;
     }
     // minimums: sum_j m_j * (128*a_j + b_j) per column
     const uint32_t ma[2] = {ha.z & 0x3f3f3f3fu, ((ha.w >> 4) & 0x0f0f0f0fu) | ((ha.z >> 2) & 0x30303030u)};
     const uint32_t mb[2] = {hb.z & 0x3f3f3f3fu, ((hb.w >> 4) & 0x0f0f0f0fu) | ((hb.z >> 2) & 0x30303030u)};
-    uint4 t0 = make_uint4(0, 0, 0, 0), t1 = t0;
-    float2 worth = make_float2(0.0f, 0.0f);
-    if (ccol) {
-        t0 = lds128(blob + 256 * nc + (2 * L.c) * 16);
-        t1 = lds128(blob + 256 * nc + (2 * L.c + 1) * 16);
-        worth = lds64f2(blob + 272 * nc + 8 * L.c);
-    }
-    const int m0 = (dp4a_us(ma[1], t0.y, dp4a_us(ma[0], t0.x, 0)) << 7) + dp4a_us(ma[1], t0.w, dp4a_us(ma[0], t0.z, 0));
-    const int m1 = (dp4a_us(ma[1], t1.y, dp4a_us(ma[0], t1.x, 0)) << 7) + dp4a_us(ma[1], t1.w, dp4a_us(ma[0], t1.z, 0));
-    const int m2 = (dp4a_us(mb[1], t0.y, dp4a_us(mb[0], t0.x, 0)) << 7) + dp4a_us(mb[1], t0.w, dp4a_us(mb[0], t0.z, 0));
-    const int m3 = (dp4a_us(mb[1], t1.y, dp4a_us(mb[0], t1.x, 0)) << 7) + dp4a_us(mb[1], t1.w, dp4a_us(mb[0], t1.z, 0));
     const float da = h2f_lo(ha.x), dma = h2f_hi(ha.x), db = h2f_lo(hb.x), dmb = h2f_hi(hb.x);
-    acc[0] += worth.x * (da * (float)(ilo[0] + (ihi[0] >> 4)) - dma * (float)m0);
-    acc[1] += worth.y * (da * (float)(ilo[1] + (ihi[1] >> 4)) - dma * (float)m1);
-    acc[2] += worth.x * (db * (float)(ilo[2] + (ihi[2] >> 4)) - dmb * (float)m2);
-    acc[3] += worth.y * (db * (float)(ilo[3] + (ihi[3] >> 4)) - dmb * (float)m3);
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            uint4 t = make_uint4(0, 0, 0, 0);
+            float worth = 0.0f;
+            if (2 * L.c + i < X.tile_cols) {
+                const int col = p * X.tile_stride + 2 * L.c + i;
+                t = lds128(blob + 256 * X.nc + col * 16);
+                worth = lds32f(blob + 272 * X.nc + 4 * col);
+            }
+            const int m_a = (dp4a_us(ma[1], t.y, dp4a_us(ma[0], t.x, 0)) << 7) + dp4a_us(ma[1], t.w, dp4a_us(ma[0], t.z, 0));
+            const int m_b = (dp4a_us(mb[1], t.y, dp4a_us(mb[0], t.x, 0)) << 7) + dp4a_us(mb[1], t.w, dp4a_us(mb[0], t.z, 0));
+            acc[i] += worth * (da * (float)(ilo[p][i] + (ihi[p][i] >> 4)) - dma * (float)m_a);
+            acc[2 + i] += worth * (db * (float)(ilo[p][2 + i] + (ihi[p][2 + i] >> 4)) - dmb * (float)m_b);
+        }
+}
+
+// Q8_0.  A 32-weight block is one MMA (s8 x s8); its f16 scale weighs the block's
+// integer sums in fp32.  Lane c owns bytes [8c, 8c+8) of each block.
+template <int NTILE>
+__device__ __forceinline__ void unit_q8_i8(const Lane &L, const I8Cols X, int ul, int xu, float (&acc)[4]) {
+    const uint32_t qa = L.row_a + ul * 256 + 8 * L.c, qb = L.row_b + ul * 256 + 8 * L.c;
+    const uint4 sa = lds128(L.srow_a + ul * 16), sb = lds128(L.srow_b + ul * 16);
+    const uint32_t sca[4] = {sa.x, sa.y, sa.z, sa.w}, scb[4] = {sb.x, sb.y, sb.z, sb.w};
+    const uint32_t blob = L.xbase + xu * i8_unit_bytes(X.nc);
+    const bool bcol = L.g < X.tile_cols;
+    float fs[NTILE][4];
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) fs[p][i] = 0.0f;
+    uint32_t xcol = blob + L.g * 32 + 8 * L.c;
+    const uint32_t xstep = 32 * X.nc, tstep = 32 * X.tile_stride;
+#pragma unroll
+    for (int blk = 0; blk < 8; blk++) {
+        const uint2 wa = lds64(qa + 32 * blk), wb = lds64(qb + 32 * blk);
+        const float da = (blk & 1) ? h2f_hi(sca[blk >> 1]) : h2f_lo(sca[blk >> 1]);
+        const float db = (blk & 1) ? h2f_hi(scb[blk >> 1]) : h2f_lo(scb[blk >> 1]);
+#pragma unroll
+        for (int p = 0; p < NTILE; p++) {
+            uint2 x = make_uint2(0, 0);
+            if (bcol) x = lds64(xcol + p * tstep);
+            int c[4];
+            imma_s8s8(c, wa.x, wb.x, wa.y, wb.y, x.x, x.y);
+            fs[p][0] += da * (float)c[0];
+            fs[p][1] += da * (float)c[1];
+            fs[p][2] += db * (float)c[2];
+            fs[p][3] += db * (float)c[3];
+        }
+        xcol += xstep;
+    }
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float worth = 0.0f;
+            if (2 * L.c + i < X.tile_cols) worth = lds32f(blob + 272 * X.nc + 4 * (p * X.tile_stride + 2 * L.c + i));
+            acc[i] += worth * fs[p][i];
+            acc[2 + i] += worth * fs[p][2 + i];
+        }
+}
+
+// Q6_K.  One MMA of k = 16 per 16-weight scale group: lane c holds weights
+// 4c..4c+3 of the group as signed bytes; the group's i8 sub-scale weighs its
+// integer sums, d the unit's.  For (half, lh) the lane reads two ql words and
+// one qh word per row and makes the four groups k = 0..3 from them.
+__device__ __forceinline__ uint32_t q6_signed(uint32_t low, uint32_t high2) {
+    // bytes low | high2 hold q + 32 in [0, 63]; flipping bit 5 gives q's 6-bit two's
+    // complement, whose sign bit is then copied into bits 6 and 7
+    const uint32_t t = (low | high2) ^ 0x20202020u, sgn = t & 0x20202020u;
+    return t | (sgn << 1) | (sgn << 2);
+}
+template <int NTILE>
+__device__ __forceinline__ void unit_q6k_i8(const Lane &L, const I8Cols X, int ul, int xu, int d_index, float (&acc)[4]) {
+    const uint32_t ba = L.row_a + ul * 208, bb = L.row_b + ul * 208;
+    const uint4 ta = lds128(ba + 192), tb = lds128(bb + 192);
+    const uint32_t sca[4] = {ta.x, ta.y, ta.z, ta.w}, scb[4] = {tb.x, tb.y, tb.z, tb.w};
+    const float da = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_a + 2 * d_index)));
+    const float db = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_b + 2 * d_index)));
+    const uint32_t blob = L.xbase + xu * i8_unit_bytes(X.nc);
+    const bool bcol = L.g < X.tile_cols;
+    int is[NTILE][4];
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) is[p][i] = 0;
+    const uint32_t xlane = blob + L.g * 32 + 4 * L.c;
+    const uint32_t xstep = 32 * X.nc, tstep = 32 * X.tile_stride;
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++)
+#pragma unroll
+        for (int lh = 0; lh < 2; lh++) {
+            const uint32_t o = 64 * hf + 16 * lh + 4 * L.c, oh = 128 + 32 * hf + 16 * lh + 4 * L.c;
+            const uint32_t la0 = lds32(ba + o), la1 = lds32(ba + o + 32), hha = lds32(ba + oh);
+            const uint32_t lb0 = lds32(bb + o), lb1 = lds32(bb + o + 32), hhb = lds32(bb + oh);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const uint32_t la = (k & 1) ? la1 : la0, lb = (k & 1) ? lb1 : lb0;
+                const uint32_t lowa = ((k >> 1) ? (la >> 4) : la) & 0x0f0f0f0fu;
+                const uint32_t lowb = ((k >> 1) ? (lb >> 4) : lb) & 0x0f0f0f0fu;
+                const uint32_t ha = (k == 0 ? hha << 4 : k == 1 ? hha << 2 : k == 2 ? hha : hha >> 2) & 0x30303030u;
+                const uint32_t hb = (k == 0 ? hhb << 4 : k == 1 ? hhb << 2 : k == 2 ? hhb : hhb >> 2) & 0x30303030u;
+                const uint32_t qa = q6_signed(lowa, ha), qb = q6_signed(lowb, hb);
+                const int sidx = 8 * hf + 2 * k + lh;
+                // byte sidx & 3 of the word, sign-extended (a selector nibble of 8 + b replicates byte b's sign)
+                constexpr uint32_t SEXT = 0x8880u;
+                const int fa = (int)prmt(sca[sidx >> 2], 0u, SEXT + (sidx & 3) * 0x1111u);
+                const int fb = (int)prmt(scb[sidx >> 2], 0u, SEXT + (sidx & 3) * 0x1111u);
+                // sub-block 4*hf + k of the unit, digits 16*lh + 4c .. +3
+                const uint32_t xo = (4 * hf + k) * xstep + 16 * lh;
+#pragma unroll
+                for (int p = 0; p < NTILE; p++) {
+                    uint32_t x = 0;
+                    if (bcol) x = lds32(xlane + xo + p * tstep);
+                    int c[4];
+                    imma16_s8s8(c, qa, qb, x);
+                    is[p][0] += fa * c[0];
+                    is[p][1] += fa * c[1];
+                    is[p][2] += fb * c[2];
+                    is[p][3] += fb * c[3];
+                }
+            }
+        }
+#pragma unroll
+    for (int p = 0; p < NTILE; p++)
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float worth = 0.0f;
+            if (2 * L.c + i < X.tile_cols) worth = lds32f(blob + 272 * X.nc + 4 * (p * X.tile_stride + 2 * L.c + i));
+            acc[i] += worth * (da * (float)is[p][i]);
+            acc[2 + i] += worth * (db * (float)is[p][2 + i]);
+        }
 }
 
 // ---------------------------------------------------------------------------
@@ -417,8 +580,12 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     constexpr int NW = RT * KS;
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
-    constexpr bool HAS_SCALES = FMT == Q6_K || FMT == Q8_0;   // scales kept apart from the quants
-    constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NT * 4 * 32 : 0;
+    constexpr int BASE = base_of(FMT);
+    constexpr bool I8 = is_i8(FMT);
+    constexpr bool HAS_SCALES = BASE == Q6_K || BASE == Q8_0;   // scales kept apart from the quants
+    // accumulator groups per lane: the int8 routines sum a token's planes as they go
+    constexpr int NACC = I8 ? 1 : NT;
+    constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NACC * 4 * 32 : 0;
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);   // full[MAX_STAGES], empty[MAX_STAGES], panels
@@ -472,8 +639,8 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
                 const uint32_t qbytes = UNIT_Q * kcc;
                 uint32_t sbytes = 0;
                 size_t s_first = 0;   // first f16 of the row's scales to copy
-                if (FMT == Q8_0) { sbytes = 16 * kcc; s_first = (size_t)8 * u0; }
-                if (FMT == Q6_K) {
+                if (BASE == Q8_0) { sbytes = 16 * kcc; s_first = (size_t)8 * u0; }
+                if (BASE == Q6_K) {
                     s_first = (size_t)(u0 & ~7);
                     size_t s_end = min((size_t)pad8(u0 + kcc), a.w.srow);
                     sbytes = (uint32_t)(s_end - s_first) * 2;
@@ -537,9 +704,11 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     // of 16-byte steps apart, the four rows of a half-warp must be two steps
     // apart to cover all banks, so lanes g = 0..3 take rows 0, 2, 4, 6 of the
     // eight and g = 4..7 rows 1, 3, 5, 7.
-    const int grow = FMT == Q4K_I8 ? ((L.g & 3) * 2 + (L.g >> 2)) : L.g;
+    const int grow = (FMT == Q4K_I8 || FMT == Q8_I8) ? ((L.g & 3) * 2 + (L.g >> 2)) : L.g;
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++) L.xv[nt] = nt < NT && (nt * 8 + L.g) < a.ncols;
+    for (int nt = 0; nt < 2; nt++) L.xv[nt] = !I8 && nt < NT && (nt * 8 + L.g) < a.ncols;
+    // the digit planes' columns: one tile of 4n columns (one and two tokens), or a tile of n columns per plane
+    const I8Cols X = {a.ncols, NT == 1 ? 0 : a.n_tokens, NT == 1 ? a.ncols : a.n_tokens};
     uint32_t xo[4];
 #pragma unroll
     for (int v = 0; v < 4; v++) xo[v] = 8 * (v ^ L.c);
@@ -549,12 +718,12 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     bool out_ready = false;
     if (a.x_resident && (int)blockIdx.x < a.n_tiles) mbar_wait(xbar, 0, a.status, 0x4u);
     const int n_mats = a.up_quants ? 2 : 1;
-    float gate_a = 0.0f, gate_b = 0.0f;   // SwiGLU in one launch: the gate's sums for this lane's rows, kept until up's arrive
+    float gate[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // SwiGLU in one launch: the gate's sums of this lane, kept until up's arrive
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x)
     for (int mat = 0; mat < n_mats; mat++, tile_parity ^= 1) {
-        float acc[NT][4];
+        float acc[NACC][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+        for (int nt = 0; nt < NACC; nt++)
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
 
@@ -570,14 +739,16 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
             L.srow_b = L.srow_a + 8 * a.s_stride;
             L.xbase = a.x_resident ? smem_u32(xres) : st + a.x_off;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) L.x[nt] = L.xbase + (nt * 8 + L.g) * PANEL_BYTES;
+            for (int nt = 0; nt < NACC; nt++) L.x[nt] = L.xbase + (nt * 8 + L.g) * PANEL_BYTES;
             const int xu0 = a.x_resident ? u0 : 0;
             // units are dealt to the K-split warps round-robin over the whole row,
             // so every warp gets the same number whatever the chunking
             for (int ul = (ks + KS - u0 % KS) % KS; ul < kcc; ul += KS) {
-                if (FMT == Q4K_I8) unit_q4k_i8(L, ul, xu0 + ul, a.ncols, acc[0]);
-                else if (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
-                else if (FMT == Q8_0) unit_q8_0<NT>(L, ul, xu0 + ul, a.ncols, acc);
+                if constexpr (FMT == Q4K_I8) unit_q4k_i8<NT>(L, X, ul, xu0 + ul, acc[0]);
+                else if constexpr (FMT == Q8_I8) unit_q8_i8<NT>(L, X, ul, xu0 + ul, acc[0]);
+                else if constexpr (FMT == Q6K_I8) unit_q6k_i8<NT>(L, X, ul, xu0 + ul, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc[0]);
+                else if constexpr (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
+                else if constexpr (FMT == Q8_0) unit_q8_0<NT>(L, ul, xu0 + ul, a.ncols, acc);
                 else unit_q6k<NT>(L, ul, xu0 + ul, a.ncols, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc);
             }
             __syncwarp();
@@ -586,20 +757,20 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
 
         // ---- sum the K-split warps of this row tile, in warp order ----
         if (KS > 1) {
-            float *buf = red + tile_parity * (KS * RT * NT * 128);
+            float *buf = red + tile_parity * (KS * RT * NACC * 128);
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
+            for (int nt = 0; nt < NACC; nt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) buf[(((ks * RT + rt) * NT + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+                for (int i = 0; i < 4; i++) buf[(((ks * RT + rt) * NACC + nt) * 4 + i) * 32 + lane] = acc[nt][i];
             asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
             if (ks != 0) continue;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
+            for (int nt = 0; nt < NACC; nt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     float v = 0.0f;
 #pragma unroll
-                    for (int k2 = 0; k2 < KS; k2++) v += buf[(((k2 * RT + rt) * NT + nt) * 4 + i) * 32 + lane];
+                    for (int k2 = 0; k2 < KS; k2++) v += buf[(((k2 * RT + rt) * NACC + nt) * 4 + i) * 32 + lane];
                     acc[nt][i] = v;
                 }
         }
@@ -610,23 +781,39 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
         }
         // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
         const size_t r0 = (size_t)tile * R + rt * 16 + grow, r1 = r0 + 8;
-        if (FMT == Q4K_I8) {
+        if constexpr (I8 && NT == 1) {
             // a token's four planes are columns 4t..4t+3: lanes c = 2t, 2t+1
             float va = acc[0][0] + acc[0][1], vb = acc[0][2] + acc[0][3];
             va += __shfl_xor_sync(0xffffffffu, va, 1);
             vb += __shfl_xor_sync(0xffffffffu, vb, 1);
             const int t = L.c >> 1;
             if (n_mats == 2 && mat == 0) {
-                gate_a = va;
-                gate_b = vb;
+                gate[0] = va;
+                gate[2] = vb;
             } else if (!(L.c & 1) && t < a.n_tokens) {
-                emit(a, t, r0, n_mats == 2 ? silu_mul(gate_a, va) : va);
-                emit(a, t, r1, n_mats == 2 ? silu_mul(gate_b, vb) : vb);
+                emit(a, t, r0, n_mats == 2 ? silu_mul(gate[0], va) : va);
+                emit(a, t, r1, n_mats == 2 ? silu_mul(gate[2], vb) : vb);
+            }
+            continue;
+        } else if constexpr (I8) {
+            // a tile per plane, summed by the unit routine: this lane holds tokens 2c and 2c+1 of its two rows
+            if (n_mats == 2 && mat == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) gate[i] = acc[0][i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int t = 2 * L.c + i;
+                    if (t < a.n_tokens) {
+                        emit(a, t, r0, n_mats == 2 ? silu_mul(gate[i], acc[0][i]) : acc[0][i]);
+                        emit(a, t, r1, n_mats == 2 ? silu_mul(gate[2 + i], acc[0][2 + i]) : acc[0][2 + i]);
+                    }
+                }
             }
             continue;
         }
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
+        for (int nt = 0; nt < NACC; nt++) {
             if (a.split) {
                 const int t = nt * 4 + L.c;   // columns 2t (hi), 2t+1 (lo)
                 if (t < a.n_tokens) {
@@ -651,7 +838,9 @@ template <int FMT, int NT, int RT, int KS>
 static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
-    constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NT * 4 * 32 * 4 + 127) & ~127) : 0;
+    constexpr int BASE = base_of(FMT);
+    constexpr int NACC = is_i8(FMT) ? 1 : NT;
+    constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NACC * 4 * 32 * 4 + 127) & ~127) : 0;
     constexpr int SMEM_LIMIT = 227 * 1024;
     // CTAs per SM: two smaller CTAs overlap one's fill and drain with the other's steady state
     const int cps = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
@@ -660,7 +849,11 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     // Panels stay resident when the launch covers the whole panel array (one
     // contiguous run) and it is small next to the ring.
     const int xall = a.units * a.xunit;
-    a.x_resident = a.col0 == 0 && a.ncols == a.ncols_total && xall <= 80 * 1024;
+    const bool covers = a.col0 == 0 && a.ncols == a.ncols_total;
+    // ... and next to two stages of whole rows where those fit beside it (the int8 planes of five
+    // tokens of a 5120-wide row are 83 KB)
+    const int two_whole = 2 * (int)((R * (a.w.qpitch + a.w.srow * 2) + 127) & ~127);
+    a.x_resident = covers && (xall <= 80 * 1024 || fixed + xall + two_whole <= SMEM_MAX);
     a.xres_bytes = a.x_resident ? xall : 0;
     // K per stage.  Whole rows when two stages of them fit: the tile is then one
     // contiguous run of HBM and moves with a single bulk copy (issuing a bulk
@@ -689,7 +882,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
             if ((qs / 16) % 2 == 0) qs += 16;   // an odd number of 16-byte steps between rows: no bank conflicts
             a.q_stride = qs;
             a.s_off = R * qs;
-            a.s_stride = FMT == Q8_0 ? 16 * a.kc + 16 : FMT == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
+            a.s_stride = BASE == Q8_0 ? 16 * a.kc + 16 : BASE == Q6_K ? ((2 * (a.kc + 14) + 15) & ~15) + 16 : 0;
             a.x_off = a.s_off + R * a.s_stride;
             a.stage_bytes = (a.x_off + (a.x_resident ? 0 : a.kc * a.xunit) + 127) & ~127;
             a.stages = budget / a.stage_bytes;
@@ -722,11 +915,22 @@ static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
     // Measured on B200 at the model's shapes: Q4_K runs best with 32-row tiles
     // when there are rows enough for two tiles per SM, the wider formats with
     // 16-row tiles (their stages are larger); eight K-split warps throughout.
+    // Three to eight tokens through the int8 planes (NT = 3) keep 16-row tiles:
+    // their planes then stay resident beside two stages of whole rows.
     const size_t tiles32 = (a.w.rows + 31) / 32;
-    int rt = (FMT == Q4_K || FMT == Q4K_I8) && tiles32 >= (size_t)2 * ctx->sm_count ? 2 : 1;
-    // 17+ warps of the two-group kernel would spill registers: four K-split warps there
-    if (rt == 2) return NT == 2 ? launch<FMT, NT, 2, 4>(ctx, a) : launch<FMT, NT, 2, 8>(ctx, a);
-    return launch<FMT, NT, 1, 8>(ctx, a);
+    const bool q4 = base_of(FMT) == Q4_K;
+    if constexpr (is_i8(FMT) && NT == 3) {
+        return launch<FMT, NT, 1, 8>(ctx, a);
+    } else if constexpr (base_of(FMT) == Q4_K && NT == 2) {
+        // 17+ warps of the two-group f16 kernel would spill registers: four K-split warps there
+        if (q4 && tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 4>(ctx, a);
+        return launch<FMT, NT, 1, 8>(ctx, a);
+    } else if constexpr (base_of(FMT) == Q4_K) {
+        if (q4 && tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 8>(ctx, a);
+        return launch<FMT, NT, 1, 8>(ctx, a);
+    } else {
+        return launch<FMT, NT, 1, 8>(ctx, a);
+    }
 }
 
 int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
@@ -758,25 +962,25 @@ int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, in
     }
 }
 
-// Whether a product of n tokens takes the int8 routine.  DWIM_B200_GEMV_F16 in
-// the environment keeps the f16 routine, for comparison.
+// Whether a product of n tokens takes the int8 routines: up to eight tokens of
+// any format.  (The f16 routines remain for nine to sixteen tokens, and above
+// that for the formats the tensor-core kernel does not take.)
 bool gemv_takes_i8(const WeightView &w, size_t n) {
-    static const bool off = getenv("DWIM_B200_GEMV_F16") != nullptr;
-    return !off && w.fmt == Q4_K && n >= 1 && n <= I8_MAX_TOKENS && w.cols % 256 == 0;
+    if (n < 1 || n > I8_MAX_TOKENS) return false;
+    return w.fmt == Q8_0 || ((w.fmt == Q4_K || w.fmt == Q6_K) && w.cols % 256 == 0);
 }
 
-// One or two tokens of a Q4_K matrix through the int8 routine; `panels` from
-// build_panels_i8.
+// Up to eight tokens through the int8 routines; `panels` from build_panels_i8.
 // `up`, when given, makes it the SwiGLU of the pair (w = gate) in one launch.
 int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, const OutSpec &out, const float *aux,
                   int epilogue, const WeightView *up) {
     if (w.rows == 0 || n_tokens == 0) return 0;
-    if (w.fmt != Q4_K || n_tokens > I8_MAX_TOKENS || w.cols % 256 != 0)
+    if (!gemv_takes_i8(w, (size_t)n_tokens))
         return fail(ctx, DWIM_B200_EINVAL, "int8 small-M kernel: format %d, %d tokens", w.fmt, n_tokens);
     GemvArgs a{};
     a.w = w;
     a.panels = panels;
-    a.ncols_total = a.ncols = 4 * n_tokens;
+    a.ncols_total = a.ncols = i8_planes(n_tokens) * n_tokens;
     a.col0 = 0;
     a.split = 0;
     a.n_tokens = n_tokens;
@@ -784,7 +988,7 @@ int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels
     a.out = out;
     a.aux = aux;
     a.epi = epilogue;
-    a.units = (int)(w.cols / 256);
+    a.units = (int)((w.cols + 255) / 256);
     a.xunit = a.xsrc_stride = i8_unit_bytes(a.ncols);
     if (up) {
         if (up->fmt != w.fmt || up->rows != w.rows || up->cols != w.cols || up->qpitch != w.qpitch || epilogue != EPI_STORE)
@@ -793,7 +997,13 @@ int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels
         a.up_scales = up->scales;
     }
     a.status = ctx->status;
-    return launch_shape<Q4K_I8, 1>(ctx, a);
+    const bool packed = n_tokens <= 2;   // one column tile (4 planes x 1-2 tokens), or a tile per plane (3 planes)
+    switch (w.fmt) {
+    case Q4_K: return packed ? launch_shape<Q4K_I8, 1>(ctx, a) : launch_shape<Q4K_I8, 3>(ctx, a);
+    case Q8_0: return packed ? launch_shape<Q8_I8, 1>(ctx, a) : launch_shape<Q8_I8, 3>(ctx, a);
+    case Q6_K: return packed ? launch_shape<Q6K_I8, 1>(ctx, a) : launch_shape<Q6K_I8, 3>(ctx, a);
+    default: return fail(ctx, DWIM_B200_EFORMAT, "unknown weight format %d", w.fmt);
+    }
 }
 
 }  // namespace dwim

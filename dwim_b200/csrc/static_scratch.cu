@@ -46,8 +46,9 @@ extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwi
     if (n == 0 || v.rows == 0) return 0;
     if (!out || !x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: null pointer");
     if (out == x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: output aliases input");
+    if (v.fmt == BF16) return fail(ctx, DWIM_B200_EFORMAT, "matmul_static: bf16 weights need no scratch: use matmul");
     if (gemv_takes_i8(v, n)) {
-        // one or two tokens of Q4_K: the int8 digit-plane operand, as dwim_b200_matmul
+        // up to eight tokens: the int8 digit-plane operand, as dwim_b200_matmul
         const size_t need = panel_i8_bytes(v.cols, n);
         if (need > STATIC_SCRATCH_BYTES)
             return fail(ctx, DWIM_B200_EINVAL,

@@ -155,6 +155,17 @@ class B200:
     def swiglu(self, out: Buffer, gate: Weight, up: Weight, x: Buffer, scratch: Buffer) -> None:
         self._check(self._L.dwim_b200_swiglu(self._ctx, out._h, gate._h, up._h, x._h, scratch._h))
 
+    def normalize(self, out: Buffer, x: Buffer, weight: Buffer, length: int, eps: float) -> None:
+        """``Device::normalize``: ``out = rmsnorm(x[:length]) * weight``."""
+        self._check(self._L.dwim_b200_normalize(self._ctx, out._h, x._h, weight._h, length, eps))
+
+    def argmax(self, logits: Buffer, length: int) -> np.ndarray:
+        """First index of the largest of every ``length`` logits (uint32 per row)."""
+        n = len(logits) // length if length else 0
+        out = np.zeros(n, np.uint32)
+        self._check(self._L.dwim_b200_argmax(self._ctx, logits._h, length, out.ctypes.data_as(C.POINTER(C.c_uint32)), n))
+        return out
+
     def matmul_static(self, out: Buffer, w: Weight, x: Buffer) -> None:
         """``matmul`` for up to 8 tokens that allocates nothing: the operand
         scratch is a fixed array inside the library, shared by every call on

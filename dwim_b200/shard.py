@@ -63,18 +63,23 @@ class RowSharded:
         assert mine.shape == (self.end - self.begin, self.cols)
         self.weight = dev.upload(mine)
         self._torch = torch
-        self._stream = torch.cuda.ExternalStream(dev.stream)
+        self._device = torch.device("cuda", torch.cuda.current_device())
+        self._stream = torch.cuda.ExternalStream(dev.stream, device=self._device)
         self._parts = None      # torch tensor [world * n * part_rows], and its device views
         self._views = None
+        self._short = None
 
     def _buffers(self, n: int):
         if self._parts is None or self._parts.numel() != self.world * n * self.part_rows:
             t = self._torch
-            self._parts = t.zeros(self.world * n * self.part_rows, dtype=t.float32, device="cuda")
-            mine = self._parts[self.rank * n * self.part_rows:(self.rank + 1) * n * self.part_rows]
             my_rows = self.end - self.begin
-            # a short last shard computes into a buffer of its own and is padded into the common slice
-            local = self.dev.wrap(mine.data_ptr(), n * my_rows) if my_rows == self.part_rows else self.dev.alloc(n * my_rows)
+            # allocated and zeroed on the library's own stream, which is the one that writes them next
+            with t.cuda.stream(self._stream):
+                self._parts = t.zeros(self.world * n * self.part_rows, dtype=t.float32, device=self._device)
+                # a short last shard computes into a buffer of its own and is padded into the common slice
+                self._short = None if my_rows == self.part_rows else t.zeros(n * my_rows, dtype=t.float32, device=self._device)
+            mine = self._parts[self.rank * n * self.part_rows:(self.rank + 1) * n * self.part_rows]
+            local = self.dev.wrap((mine if self._short is None else self._short).data_ptr(), n * my_rows)
             self._views = (mine, local, self.dev.wrap(self._parts.data_ptr(), self._parts.numel()))
         return self._views
 
@@ -86,11 +91,58 @@ class RowSharded:
         self.dev.matmul(local, self.weight, x)
         my_rows = self.end - self.begin
         with self._torch.cuda.stream(self._stream):
-            if my_rows != self.part_rows:
-                src = self._torch.as_tensor(self.dev.read(local)).reshape(n, my_rows).cuda()
-                mine.view(n, self.part_rows)[:, :my_rows] = src
+            if self._short is not None:
+                mine.view(n, self.part_rows)[:, :my_rows] = self._short.view(n, my_rows)
             dist.all_gather_into_tensor(self._parts, mine, group=self.group)
+        self.dev.touch(parts)               # written by the collective, not by the library
         self.dev.gather_rows(out, parts, n, self.rows, self.world, self.align)
+
+
+class RowShardedPush:
+    """The same split with the exchange fused into the product: every rank's
+    kernel stores its rows of the token-major result into every rank's copy of a
+    shared output from its epilogue (``B200.matmul_gather``: plain stores, over
+    NVLink for the peers' copies), and one barrier kernel tells every rank that
+    all slices have landed.  No collective library call, no re-assembly pass.
+
+    ``matmul`` returns the device buffer that holds the full result on this
+    rank.  Two buffers alternate: the result of a call stays valid until the
+    call after the next."""
+
+    def __init__(self, dev: B200, tensor: Tensor | None, rank: int, world: int, max_tokens: int, align: int = 16,
+                 group=None, local: Tensor | None = None, shape=None):
+        import torch.distributed as dist
+        self.dev, self.rank, self.world, self.align = dev, rank, world, align
+        self.rows, self.cols = tensor.shape if tensor is not None else shape
+        self.begin, self.end = shard_rows(self.rows, rank, world, align)
+        mine = local if local is not None else tensor.slice_rows(self.begin, self.end)
+        assert mine.shape == (self.end - self.begin, self.cols)
+        self.weight = dev.upload(mine)
+        self.max_tokens = max_tokens
+        self._outs, self._turn = [], 0
+        for _ in range(2):
+            buf, handle = dev.shared_alloc(max_tokens * self.rows)
+            handles = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, handle, group=group)
+            else:
+                handles = [handle]
+            dev.shared_connect(buf, world, rank, handles)
+            self._outs.append(buf)
+        if world > 1:
+            dist.barrier(group=group)       # nobody stores before everybody has mapped
+
+    def matmul(self, x):
+        n = len(x) // self.cols
+        if n > self.max_tokens:
+            raise ValueError(f"{n} tokens, the shared outputs hold {self.max_tokens}")
+        out = self._outs[self._turn]
+        self._turn ^= 1
+        self.dev.resize(out, n * self.rows)
+        if self.end > self.begin:
+            self.dev.matmul_gather(out, self.weight, x, self.begin, self.rows)
+        self.dev.shared_barrier(out)
+        return out
 
 
 # ---- the feed-forward block, tensor parallel ------------------------------------------
@@ -156,7 +208,8 @@ class ShardedFFN:
         self.my_inner = g.rows
         self.gate, self.up, self.down = dev.upload(g), dev.upload(u), dev.upload(d)
         self._torch = torch
-        self._stream = torch.cuda.ExternalStream(dev.stream)
+        self._device = torch.device("cuda", torch.cuda.current_device())
+        self._stream = torch.cuda.ExternalStream(dev.stream, device=self._device)
 
     # Activation buffers are shared by every block of the same shape on a device (a
     # decoder's layers use one residual stream, not one per layer): the all-reduce
@@ -168,7 +221,8 @@ class ShardedFFN:
         bufs = ShardedFFN._shared.get(key)
         if bufs is None:
             t = self._torch
-            out_t = t.zeros(n * self.hidden, dtype=t.float32, device="cuda")
+            with t.cuda.stream(self._stream):      # zeroed on the stream that writes it next
+                out_t = t.zeros(n * self.hidden, dtype=t.float32, device=self._device)
             bufs = (out_t, self.dev.wrap(out_t.data_ptr(), n * self.hidden), self.dev.alloc(n * self.my_inner),
                     self.dev.alloc(n * self.my_inner))
             ShardedFFN._shared[key] = bufs
@@ -194,4 +248,5 @@ class ShardedFFN:
                 import torch.distributed as dist
                 with self._torch.cuda.stream(self._stream):
                     dist.all_reduce(out_t, group=self.group)
+                self.dev.touch(out)         # written by the collective, not by the library
         return out

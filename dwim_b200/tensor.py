@@ -12,13 +12,14 @@ from dataclasses import dataclass
 
 import numpy as np
 
-from ._lib import Q4_K, Q6_K, Q8_0
+from ._lib import BF16, Q4_K, Q6_K, Q8_0
 
 # format id -> (name, weights per block, bytes per block)
 FORMATS = {
     Q8_0: ("Q8_0", 32, 34),
     Q4_K: ("Q4_K", 256, 144),
     Q6_K: ("Q6_K", 256, 210),
+    BF16: ("BF16", 1, 2),       # plain bf16 weights (Tensor::Bf16, gpu/mod.rs:46-50)
 }
 BY_NAME = {name.lower(): fmt for fmt, (name, _, _) in FORMATS.items()}
 

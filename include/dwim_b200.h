@@ -42,7 +42,8 @@ extern "C" {
 enum {
     DWIM_B200_Q8_0 = 8,  /* 32 weights: f16 d, 32 x i8            (34 B)  */
     DWIM_B200_Q4_K = 12, /* 256 weights: f16 d, dmin, 12 B of 6-bit scales/mins, 128 B of nibbles (144 B) */
-    DWIM_B200_Q6_K = 14  /* 256 weights: ql[128] qh[64] i8 scales[16] f16 d (210 B) */
+    DWIM_B200_Q6_K = 14, /* 256 weights: ql[128] qh[64] i8 scales[16] f16 d (210 B) */
+    DWIM_B200_BF16 = 30  /* plain bf16 weights, 2 B each (Tensor::Bf16, gpu/mod.rs:46-50): the small gate matrices */
 };
 
 enum {
@@ -174,6 +175,23 @@ DWIM_B200_API int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, 
 DWIM_B200_API int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *gate,
                                    const dwim_b200_weight *up, dwim_b200_buffer *x, dwim_b200_buffer *scratch);
 
+/* Device::normalize (gpu/mod.rs:290-305; Cuda::normalize, gpu/cuda/mod.rs:1177-1198,
+ * rmsnorm.cu:11-58): out = rmsnorm(x[0..len]) * weight, rows of len(weight);
+ * len(out) must be `len`.  The reference's CUDA device writes the f16 copy its
+ * tile kernels read; here the same launch writes the f32 result and, where rows
+ * are whole 256-weight units, the 16-bit operand form the next product of `out`
+ * will read (int8 digit planes for up to eight rows, the tensor-core kernel's
+ * f16 rows, means and scales above sixteen), so that no activation prologue
+ * runs before that product. */
+DWIM_B200_API int dwim_b200_normalize(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *x,
+                                      const dwim_b200_buffer *weight, size_t len, float eps);
+/* The first index of the largest of each of the n rows of `len` logits in
+ * `logits` (n * len f32), to host memory; waits.  Replaces reading the logits
+ * back and scanning them on the host (inference/qwen35/mod.rs:702-710,
+ * 1066-1068: 608 KB per drafted token); NaNs never win. */
+DWIM_B200_API int dwim_b200_argmax(dwim_b200_ctx *ctx, const dwim_b200_buffer *logits, size_t len, uint32_t *out,
+                                   size_t n);
+
 /* No counterpart in the reference.  out[t] = w . x[t] for n <= 8 token rows,
  * like dwim_b200_matmul, but without allocating anything: `out` (n * rows f32)
  * and `x` (n * cols f32) are device pointers the caller owns, and the 16-bit
@@ -181,9 +199,10 @@ DWIM_B200_API int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, co
  * a buffer allocated on first use.  For callers whose device memory is an
  * arena sized once, or that run where cudaMalloc is not allowed.  Sizes whose
  * operand form does not fit the array are refused with EINVAL: with `units` =
- * cols / 256 rounded up, n * units may be at most 949 for one or two tokens of
- * Q4_K (1104 bytes per token and unit) and 963 otherwise (1088 bytes): about
- * 243 000 and 246 000 activations per call.  The array is shared by all calls on
+ * cols / 256 rounded up, n * units may be at most 949 for one or two tokens
+ * (1104 bytes of int8 digit planes per token and unit: about 243 000
+ * activations per call) and 1266 for three to eight (828 bytes: about 324 000).
+ * bf16 weights are not taken.  The array is shared by all calls on
  * a GPU: calls that overlap there race; calls on one context are ordered.  Its
  * device address is looked up (cudaGetSymbolAddress) when the context is
  * opened, so dwim_b200_open is the call that should come before any stream

@@ -308,3 +308,34 @@ def threads() -> int:
 
 def set_threads(n: int) -> None:
     lib().orc_set_threads(int(n))
+
+
+# ---- the operators either side of the product ---------------------------
+def rmsnorm(x, weight, eps: float) -> np.ndarray:
+    """Rows of ``x`` normalized by their root mean square, times ``weight``
+    (gpu/cpu.rs:157-166; ``Device::normalize`` is a copy followed by this)."""
+    weight = _f32(weight).reshape(-1)
+    out = _f32(x).reshape(-1, weight.size).copy()
+    lib().orc_rmsnorm.restype = None
+    lib().orc_rmsnorm.argtypes = [_f32p, C.c_size_t, _f32p, C.c_size_t, C.c_float]
+    lib().orc_rmsnorm(_p(out, _f32p), out.shape[0], _p(weight, _f32p), weight.size, eps)
+    return out
+
+
+def matmul_bf16(w_bits, rows: int, cols: int, x) -> np.ndarray:
+    """out[t, r] = bf16 weights w[r] . x[t]  (gpu/cpu.rs:124-128, 370-384)."""
+    w_bits = np.ascontiguousarray(w_bits, dtype=np.uint16).reshape(-1)
+    x = _f32(x).reshape(-1, cols)
+    assert w_bits.size == rows * cols
+    out = np.empty((x.shape[0], rows), np.float32)
+    lib().orc_matmul_bf16.argtypes = [_u16p, C.c_size_t, C.c_size_t, _f32p, C.c_size_t, _f32p]
+    lib().orc_matmul_bf16(_p(w_bits, _u16p), rows, cols, _p(x, _f32p), x.shape[0], _p(out, _f32p))
+    return out
+
+
+def argmax(logits) -> int:
+    """First index of the largest value (inference/qwen35/mod.rs:702-710)."""
+    logits = _f32(logits).reshape(-1)
+    lib().orc_argmax.restype = C.c_uint32
+    lib().orc_argmax.argtypes = [_f32p, C.c_size_t]
+    return int(lib().orc_argmax(_p(logits, _f32p), logits.size))

@@ -660,3 +660,52 @@ ORC_API int orc_quantize(int fmt, const float *w, size_t rows, size_t cols, uint
     for_rows(rows, q_row, &c);
     return 0;
 }
+
+/* ---- the operators either side of the product ---------------------------------- */
+
+/* Cpu::rmsnorm, gpu/cpu.rs:157-166: per row of `dim`, mean_square = (left fold of
+ * v*v from 0.0) / dim; scale = 1.0 / sqrt(mean_square + eps); v *= scale * w.
+ * Device::normalize (gpu/mod.rs:295-305) is a copy followed by this. */
+ORC_API void orc_rmsnorm(float *x, size_t n, const float *weight, size_t dim, float eps) {
+    for (size_t t = 0; t < n; t++) {
+        float *row = x + t * dim;
+        float sum = 0.0f;
+        for (size_t i = 0; i < dim; i++) sum += row[i] * row[i];
+        float mean_square = sum / (float)dim;
+        float scale = 1.0f / sqrtf(mean_square + eps);
+        for (size_t i = 0; i < dim; i++) row[i] *= scale * weight[i];
+    }
+}
+
+/* gpu/cpu.rs:370-384: eight running sums over chunks of eight, the rest summed
+ * on its own, then (left fold of the eight from 0.0) + rest. */
+ORC_API float orc_dot_bf16(const uint16_t *w, const float *x, size_t cols) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    size_t done = cols / 8 * 8;
+    for (size_t k = 0; k < done; k += 8)
+        for (int i = 0; i < 8; i++) acc[i] += orc_bf16(w[k + i]) * x[k + i];
+    float rest = 0.0f;
+    for (size_t k = done; k < cols; k++) rest += orc_bf16(w[k]) * x[k];
+    return fold8(acc) + rest;
+}
+
+/* Cpu::matmul's Bf16 arm, gpu/cpu.rs:124-128, 144-148: token-major output. */
+typedef struct { const uint16_t *w; size_t rows, cols; const float *x; size_t n; float *out; } bf16_ctx;
+static void bf16_row(size_t r, void *p) {
+    bf16_ctx *c = (bf16_ctx *)p;
+    for (size_t t = 0; t < c->n; t++) c->out[t * c->rows + r] = orc_dot_bf16(c->w + r * c->cols, c->x + t * c->cols, c->cols);
+}
+ORC_API int orc_matmul_bf16(const uint16_t *w, size_t rows, size_t cols, const float *x, size_t n, float *out) {
+    bf16_ctx c = {w, rows, cols, x, n, out};
+    for_rows(rows, bf16_row, &c);
+    return 0;
+}
+
+/* inference/qwen35/mod.rs:702-710: the first index of the largest value
+ * (a later equal value does not replace it; index 0 if nothing compares greater). */
+ORC_API uint32_t orc_argmax(const float *logits, size_t n) {
+    size_t best = 0;
+    for (size_t i = 0; i < n; i++)
+        if (logits[i] > logits[best]) best = i;
+    return (uint32_t)best;
+}

@@ -251,3 +251,40 @@ def test_oracle_reproduces_its_committed_outputs(oracle):
         assert np.array_equal(oracle.dequantize(fmt, blocks, rows, cols).view(np.uint32), g[f"{fmt}_dequant"].view(np.uint32))
         assert np.array_equal(oracle.matmul(fmt, blocks, rows, cols, x), g[f"{fmt}_matmul"])
         assert np.array_equal(oracle.swiglu(fmt, blocks, g[f"{fmt}_up_blocks"], rows, cols, x), g[f"{fmt}_swiglu"])
+
+
+# ---- the operators either side of the product ------------------------------------------
+def test_rmsnorm_restates_the_cpu_device(oracle):
+    """gpu/cpu.rs:157-166 in numpy, step by step in f32, against the C restatement."""
+    rng = oracle.Lcg(5)
+    for dim, rows in [(128, 5), (1024, 3), (8, 1)]:      # gpu/tests.rs:611-622
+        w, x = rng.floats(dim), rng.floats(dim * rows).reshape(rows, dim)
+        want = x.copy()
+        for r in range(rows):
+            s = np.float32(0.0)
+            for v in x[r]:
+                s = np.float32(s + np.float32(v * v))
+            scale = np.float32(1.0) / np.sqrt(np.float32(s / np.float32(dim)) + np.float32(1e-6), dtype=np.float32)
+            want[r] = x[r] * (scale * w)
+        assert np.array_equal(oracle.rmsnorm(x, w, 1e-6), want)
+
+
+def test_bf16_dot_and_argmax(oracle):
+    rng = oracle.Lcg(4)
+    cols = 27                                            # three chunks of eight and a rest of three (gpu/cpu.rs:370-384)
+    wbits = (rng.floats(cols).view(np.uint32) >> 16).astype(np.uint16)
+    x = rng.floats(cols)
+    w = oracle.bf16(wbits)
+    acc = np.zeros(8, np.float32)
+    for k in range(0, 24, 8):
+        acc += w[k:k + 8] * x[k:k + 8]
+    rest = np.float32(0.0)
+    for k in range(24, cols):
+        rest = np.float32(rest + np.float32(w[k] * x[k]))
+    total = np.float32(0.0)
+    for a in acc:
+        total = np.float32(total + a)
+    assert oracle.matmul_bf16(wbits, 1, cols, x)[0, 0] == np.float32(total + rest)
+    assert oracle.argmax([1.0, 5.0, 5.0, 2.0]) == 1      # the first of equals (inference/qwen35/mod.rs:702-710)
+    assert oracle.argmax([np.nan, 1.0]) == 0             # nothing compares greater than a NaN at index 0
+    assert oracle.argmax([-np.inf, -np.inf]) == 0

@@ -140,7 +140,7 @@ def test_block_matmul_matches_cpu(dev, oracle, fmt):
 
 
 @pytest.mark.parametrize("fmt", FORMATS)
-@pytest.mark.parametrize("n", [1, 2, 4, 5, 8, 9, 15, 16, 17])
+@pytest.mark.parametrize("n", [1, 2, 3, 4, 5, 6, 7, 8, 9, 15, 16, 17])
 def test_matmul_token_counts_at_model_width(dev, oracle, fmt, n):
     rng = np.random.default_rng(31 + n)
     rows, cols = 333, 5120
@@ -257,18 +257,19 @@ def test_swiglu_matches_cpu(dev, oracle, fmt):
         assert max_rel_err(got, want) <= TOL
 
 
-@pytest.mark.parametrize("n", [1, 2, 3])
-def test_swiglu_one_launch_at_model_width(dev, oracle, n):
-    """One and two tokens of Q4_K take gate and up in a single launch; three go the
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n", [1, 2, 3, 5, 8, 9])
+def test_swiglu_one_launch_at_model_width(dev, oracle, fmt, n):
+    """Up to eight tokens take gate and up in a single launch; nine go the
     two-launch way.  Rows that are not a whole tile, both ways against the CPU."""
     rng = np.random.default_rng(53 + n)
     rows, cols = 1000, 5120
-    gate = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
-    up = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    gate = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    up = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
     x = rng.standard_normal((n, cols)).astype(np.float32)
     out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
-    dev.swiglu(out, upload(dev, "q4_k", rows, cols, gate), upload(dev, "q4_k", rows, cols, up), dev.buffer(x), scratch)
-    want = oracle.swiglu("q4_k", gate, up, rows, cols, x)
+    dev.swiglu(out, upload(dev, fmt, rows, cols, gate), upload(dev, fmt, rows, cols, up), dev.buffer(x), scratch)
+    want = oracle.swiglu(fmt, gate, up, rows, cols, x)
     assert max_rel_err(dev.read(out), want) <= 2e-5
 
 
@@ -422,14 +423,15 @@ def test_feed_forward_block_on_one_gpu(dev, oracle, n):
     assert max_rel_err(got, want) <= 5e-5
 
 
-@pytest.mark.parametrize("n", [1, 2])
-def test_int8_routine_activation_extremes(dev, oracle, n):
-    """One and two tokens of Q4_K go through int8 digit planes with one exponent per
-    256 activations: outliers, zeros, a zero unit, tiny and huge magnitudes."""
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("n", [1, 2, 5, 8])
+def test_int8_routine_activation_extremes(dev, oracle, fmt, n):
+    """Up to eight tokens go through int8 digit planes with one exponent per 256
+    activations: outliers, zeros, a zero unit, tiny and huge magnitudes."""
     rng = np.random.default_rng(71 + n)
     rows, cols = 96, 2048
-    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
-    weight = upload(dev, "q4_k", rows, cols, blocks)
+    blocks = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    weight = upload(dev, fmt, rows, cols, blocks)
     x = rng.standard_normal((n, cols)).astype(np.float32)
     x[:, 7] = 3.0e4                   # an outlier in the first unit
     x[:, 256:512] = 0.0               # a unit of zeros
@@ -439,9 +441,100 @@ def test_int8_routine_activation_extremes(dev, oracle, n):
     x[:, 1300] = -65504.0
     out = dev.alloc(n * rows)
     dev.matmul(out, weight, dev.buffer(x))
+    got, want = dev.read(out).reshape(n, rows), oracle.matmul(fmt, blocks, rows, cols, x)
+    assert np.isfinite(got).all()
+    # three digit planes (three to eight tokens) round an activation at 2^-23 of its unit's largest
+    assert max_rel_err(got, want) <= (2e-5 if n <= 2 else 1e-4)
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+@pytest.mark.parametrize("scale", [1e5, 1e20, 1e-30])
+def test_gemm_activation_range(dev, oracle, scale, bf16):
+    """Forty tokens through the tensor-core kernel with activations far outside
+    f16's range: every token's row is scaled by its own power of two on the way in
+    and back on the way out, so nothing is clamped or flushed."""
+    rng = np.random.default_rng(79)
+    rows, cols, n = 256, 1024, 40
+    blocks = oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
+    x = rng.standard_normal((n, cols)).astype(np.float32)
+    x[::2] *= np.float32(scale)               # every other token: neighbours keep their own range
+    x[1, 7] = 3.0e4
+    xb = dev.alloc(n * cols)
+    if bf16:
+        bits = oracle.to_bf16(x)
+        dev.write_bf16(xb, bits)
+        x = oracle.bf16(bits).reshape(n, cols)
+    else:
+        dev.write(xb, x)
+    out = dev.alloc(n * rows)
+    dev.matmul(out, upload(dev, "q4_k", rows, cols, blocks), xb)
     got, want = dev.read(out).reshape(n, rows), oracle.matmul("q4_k", blocks, rows, cols, x)
     assert np.isfinite(got).all()
-    assert max_rel_err(got, want) <= 2e-5
+    for t in range(n):                         # per token: the tokens' magnitudes differ by up to 10^30
+        assert max_rel_err(got[t], want[t]) <= 2e-5, (t, max_rel_err(got[t], want[t]))
+
+
+# ---- the operators either side of the product (SURVEY's "next" rows) -----------------------------
+def test_normalize_matches_cpu(dev, oracle):
+    """normalize_matches_cpu (gpu/tests.rs:788-812): the reference's shapes and
+    generator; then the model's width, where the same launch also writes the next
+    product's operand form: the product of the normalized rows must match too."""
+    rng = oracle.Lcg(21)
+    for dim, rows in KATS["normalize_shapes"]["shapes"]:
+        w, x = rng.floats(dim), rng.floats(dim * (rows + 1))
+        rng.floats(dim * rows)                 # the reference draws y for its add check here
+        out = dev.alloc(dim * rows)
+        dev.normalize(out, dev.buffer(x), dev.buffer(w), dim * rows, 1e-6)
+        close(dev.read(out), oracle.rmsnorm(x[: dim * rows], w, 1e-6), 1e-5)
+    g = np.random.default_rng(83)
+    cols, wrows = 5120, 320
+    blocks = oracle.quantize("q4_k", (0.02 * g.standard_normal((wrows, cols))).astype(np.float32))
+    weight = upload(dev, "q4_k", wrows, cols, blocks)
+    for n in (1, 2, 5, 8, 12, 40, 300):
+        x = (3.0 * g.standard_normal((n, cols))).astype(np.float32)
+        w = (1.0 + 0.1 * g.standard_normal(cols)).astype(np.float32)
+        normed, out = dev.alloc(n * cols), dev.alloc(n * wrows)
+        dev.normalize(normed, dev.buffer(x), dev.buffer(w), n * cols, 1e-6)
+        launches = dev.launches
+        dev.matmul(out, weight, normed)
+        want_n = oracle.rmsnorm(x, w, 1e-6)
+        close(dev.read(normed), want_n, 1e-5)
+        # the device's own normalized rows (they differ from the CPU's by summation order) through the oracle
+        want = oracle.matmul("q4_k", blocks, wrows, cols, dev.read(normed).reshape(n, cols))
+        assert max_rel_err(dev.read(out), want) <= (2e-5 if n <= 2 or n > 8 else 1e-4), n
+        if n <= 8 or n > 16:
+            assert dev.launches - launches == 1, "the product ran an activation prologue of its own"
+
+
+def test_bf16_matmul_matches_cpu(dev, oracle):
+    """matmul_matches_cpu (gpu/tests.rs:178-196): bf16 weights, the reference's
+    shapes, generator and tolerance; and the gate matrices' shape in the model."""
+    from dwim_b200 import Tensor
+    rng = oracle.Lcg(4)
+    shapes = [tuple(s) for s in KATS["bf16_matmul_shapes"]["shapes"]] + [(96, 5120, 1), (96, 5120, 5)]
+    for rows, cols, n in shapes:
+        wbits = (rng.floats(rows * cols).view(np.uint32) >> 16).astype(np.uint16)   # Rng::bf16, gpu/tests.rs:60-68
+        x = rng.floats(n * cols)
+        weight = dev.upload(Tensor("bf16", (rows, cols), wbits))
+        assert np.array_equal(dev.dequantize(weight), oracle.bf16(wbits).reshape(rows, cols))
+        out = dev.alloc(n * rows)
+        dev.matmul(out, weight, dev.buffer(x))
+        close(dev.read(out), oracle.matmul_bf16(wbits, rows, cols, x), 1e-4)
+
+
+def test_argmax_on_the_device(dev, oracle):
+    rng = np.random.default_rng(91)
+    vocab = 151936
+    for n in (1, 5):
+        logits = rng.standard_normal((n, vocab)).astype(np.float32)
+        logits[0, 777] = logits[0, 99999] = 9.0     # a tie: the first index wins (inference/qwen35/mod.rs:702-710)
+        if n > 1:
+            logits[1, :] = -np.inf
+            logits[2, 5] = np.nan
+            logits[3, 0] = 50.0
+        got = dev.argmax(dev.buffer(logits), vocab)
+        want = [oracle.argmax(row) for row in logits]
+        assert got.tolist() == want
 
 
 def test_back_to_back_products_see_their_own_inputs(dev, oracle):

@@ -1,7 +1,10 @@
-"""The small all-reduce over peer memory, on two GPUs of one box: two processes,
-one per GPU, exchange their mailbox handles over gloo and reduce vectors of
-several lengths many times over (slots are reused every other call); then the
-tensor-parallel feed-forward block with that reduction against the CPU."""
+"""The multi-GPU forms on two GPUs of one box: two processes, one per GPU,
+exchange their handles over gloo.  The small all-reduce over peer memory on
+vectors of several lengths many times over (slots are reused every other
+call); the tensor-parallel feed-forward block with that reduction against the
+CPU; the row-sharded product whose epilogue stores into every rank's copy of
+the result; and a wait that runs out (a peer that never arrives), reported as
+a status and an error code with nothing left hanging."""
 import os
 import socket
 import sys
@@ -52,7 +55,33 @@ def _rank(rank: int, world: int, port: int, queue):
             want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
             err = np.abs(got - want).max() / np.sqrt((want * want).mean())
             assert err < 5e-5, (n, rank, err)
+        # the row-sharded product with the all-gather fused into its epilogue: every rank's copy of
+        # the shared result must hold every rank's rows (uneven shards: 1000 rows over two ranks)
+        rows, cols = 1000, 1024
+        t = Tensor("q4_k", (rows, cols), oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)))
+        sharded = shard.RowShardedPush(dev, t, rank, world, max_tokens=40)
+        for n in (1, 5, 40, 2, 40):
+            x = rng.standard_normal((n, cols)).astype(np.float32)
+            got = dev.read(sharded.matmul(dev.buffer(x))).reshape(n, rows)
+            want = oracle.matmul("q4_k", t.data, rows, cols, x)
+            err = np.abs(got - want).max() / np.sqrt((want * want).mean())
+            assert err < 2e-5, ("push", n, rank, err)
         dev.sync()
+        # a peer that never arrives: rank 0 alone enters the all-reduce; its bounded wait runs out,
+        # the kernel ends, and the next sync reports the time-out.  The context stays usable.
+        dist.barrier()
+        if rank == 0:
+            from dwim_b200 import DeviceError
+            buf = dev.buffer(np.ones(8, np.float32))
+            peer(buf, 8)
+            try:
+                dev.sync()
+                raise AssertionError("the lone all-reduce did not time out")
+            except DeviceError as e:
+                assert e.code == -6, e
+            dev.sync()                                   # the status was cleared: usable again
+            assert np.array_equal(dev.read(dev.buffer(np.arange(4, dtype=np.float32))), np.arange(4, dtype=np.float32))
+        dist.barrier()
         queue.put((rank, "ok"))
     except Exception as e:   # noqa: BLE001 - reported to the parent
         queue.put((rank, repr(e)))
