@@ -61,9 +61,9 @@ def test_static_scratch_refuses_what_does_not_fit(dev, oracle):
     with pytest.raises(DeviceError) as e:              # more tokens than the small-M kernel takes at once
         dev.matmul_static(dev.alloc(9 * rows), weight, dev.alloc(9 * cols))
     assert "at most" in str(e.value)
-    wide = 8 * 32768                                   # 8 tokens of 32768 columns: 1.1 MB of operand scratch
-    blocks = oracle.quantize("q8_0", np.ones((1, 32768), np.float32))
-    weight = dev.upload(Tensor("q8_0", (1, 32768), blocks))
+    wide = 8 * 65536                                   # 8 tokens of 65536 columns: 1.7 MB of operand scratch
+    blocks = oracle.quantize("q8_0", np.ones((1, 65536), np.float32))
+    weight = dev.upload(Tensor("q8_0", (1, 65536), blocks))
     with pytest.raises(DeviceError) as e:
         dev.matmul_static(dev.alloc(8), weight, dev.alloc(wide))
     assert "fixed array" in str(e.value)
