@@ -93,8 +93,9 @@ template <int BN> struct Cfg {
     static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [K group of 8][column][16 B]: the means' hi and lo parts
     static constexpr int MIN_BYTES = AMIN_BYTES + ((BMIN_BYTES + 1023) / 1024) * 1024;
     static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 4;   // the unit's scale per row
+    static constexpr int TOK_BYTES = BN * 4;                       // the columns' token scales, for the epilogue
     static constexpr int SMEM = BAR_BYTES + KBLOCKS * A_BYTES + B_STAGES * B_BYTES + MIN_STAGES * MIN_BYTES +
-                                RAW_STAGES * RAW_BYTES + SCALE_BYTES + 1024;   // + alignment slack
+                                RAW_STAGES * RAW_BYTES + SCALE_BYTES + TOK_BYTES + 1024;   // + alignment slack
     static_assert(SMEM <= MAX_SMEM, "the tile does not fit shared memory");
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;    // two accumulator buffers
     static constexpr int DRAIN_COLS = BN / 4 < 16 ? 16 : BN / 4;   // accumulator columns per draining warp
@@ -211,7 +212,6 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f
 // One finished element: the operator's epilogue, then the store (to every rank's copy of a shared result).
 __device__ __forceinline__ void gemm_emit(const GemmArgs &a, size_t t, size_t row, float x) {
     const size_t i = t * a.out.pitch + a.out.row0 + row;
-    x *= __ldg(a.tok_scale + t);
     if (a.epi == EPI_ADD) x += a.out.dst[0][i];
     else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[t * a.rows + row]);
     a.out.dst[0][i] = x;
@@ -321,6 +321,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const uint32_t min0 = bstage0 + C::B_STAGES * C::B_BYTES;
     const uint32_t raw0 = min0 + C::MIN_STAGES * C::MIN_BYTES;
     const uint32_t scale0 = raw0 + C::RAW_STAGES * RAW_BYTES;
+    const uint32_t tok0 = scale0 + C::SCALE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
@@ -528,6 +529,14 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         }
         if (drains) {
             griddep_wait();   // the kernel ahead may still read or write `out` and `aux`
+            // this warp's columns' token scales through shared memory (the four quadrants' warps of a
+            // column group write the same values): a load from global memory ahead of every store
+            // would wait for the store before it
+            for (int j = lane; j < C::DRAIN_COLS; j += 32) {
+                const size_t t = ((size_t)col0 + g * C::DRAIN_COLS + j) >> (a.split ? 1 : 0);
+                sts32f(tok0 + (g * C::DRAIN_COLS + j) * 4, t < a.n ? a.tok_scale[t] : 0.0f);
+            }
+            __syncwarp();
             drain(units - 1);
             float acc[C::DRAIN_COLS];
 #pragma unroll
@@ -539,13 +548,13 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j += 2) {
                         const size_t t = (cbase + j) >> 1;
-                        if (t < a.n) gemm_emit(a, t, row, acc[j] + acc[j + 1]);
+                        if (t < a.n) gemm_emit(a, t, row, (acc[j] + acc[j + 1]) * lds32f(tok0 + (g * C::DRAIN_COLS + j) * 4));
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j++) {
                         const size_t t = cbase + j;
-                        if (t < a.n) gemm_emit(a, t, row, acc[j]);
+                        if (t < a.n) gemm_emit(a, t, row, acc[j] * lds32f(tok0 + (g * C::DRAIN_COLS + j) * 4));
                     }
                 }
             }
