@@ -162,14 +162,15 @@ int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int 
 //   [sub-block j (8)][column][32 digits]        256*nc B
 //   [column][a_0..a_7 | b_0..b_7]                16*nc B   the digits' sums per sub-block, 128*a + b
 //   [column] float                                4*nc B   what one unit of the plane's digit is worth
+// rounded up to 16 bytes.
 constexpr int I8_MAX_TOKENS = 8;
 constexpr int i8_planes(int n) { return n <= 2 ? 4 : 3; }   // digit planes per token
-constexpr int i8_unit_bytes(int nc) { return 276 * nc; }
+constexpr int i8_unit_bytes(int nc) { return (276 * nc + 15) & ~15; }   // whole 16-byte steps: bulk copies, 128-bit loads
 size_t panel_i8_bytes(size_t cols, size_t n);
 int build_panels_i8(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, uint8_t *panels, const float *weight = nullptr,
                     float eps = 0.0f, float *xout = nullptr);
-// Tokens above which the tensor-core GEMM takes over from the small-M kernel.
-constexpr size_t DWIM_SMALL_M_MAX = 16;
+// Tokens above which the tensor-core GEMM takes over from the small-M kernel (for the formats it takes).
+constexpr size_t DWIM_SMALL_M_MAX = I8_MAX_TOKENS;
 size_t gemm_operand_bytes(size_t cols, size_t n, int split);
 int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int split, __half *out,
                        const float *weight = nullptr, float eps = 0.0f, float *xout = nullptr);

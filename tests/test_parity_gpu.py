@@ -502,8 +502,7 @@ def test_normalize_matches_cpu(dev, oracle):
         # the device's own normalized rows (they differ from the CPU's by summation order) through the oracle
         want = oracle.matmul("q4_k", blocks, wrows, cols, dev.read(normed).reshape(n, cols))
         assert max_rel_err(dev.read(out), want) <= (2e-5 if n <= 2 or n > 8 else 1e-4), n
-        if n <= 8 or n > 16:
-            assert dev.launches - launches == 1, "the product ran an activation prologue of its own"
+        assert dev.launches - launches == 1, "the product ran an activation prologue of its own"
 
 
 def test_bf16_matmul_matches_cpu(dev, oracle):
