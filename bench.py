@@ -320,7 +320,9 @@ def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
 
     def step(i, fresh_input=True):
         if fresh_input:
-            dev.touch(xb)                     # the input counts as rewritten: its 16-bit operand form is rebuilt
+            # the input counts as rewritten (by a bf16 producer where the workload's activations are bf16):
+            # its 16-bit operand form is rebuilt inside the step
+            (dev.touch_bf16(xb) if bits is not None else dev.touch(xb))
         product(i)
 
     def timed(n_steps, fresh_input=True):
@@ -384,7 +386,7 @@ def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
                      "clocks": long_clocks.summary()}
 
     # ---- parity of what was just timed: sampled weight rows, every token, against the oracle ----
-    dev.touch(xb)
+    (dev.touch_bf16(xb) if bits is not None else dev.touch(xb))
     product(0)
     product(1)                                       # both shared results, when there are two
     dev.sync()
@@ -571,7 +573,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
     (dev.write_bf16(xb, bits) if bits is not None else dev.write(xb, x))
 
     def step(i):
-        dev.touch(xb)                         # the input counts as rewritten: its operand form is rebuilt
+        (dev.touch_bf16(xb) if bits is not None else dev.touch(xb))   # the input counts as rewritten: its operand form is rebuilt
         return blocks[i % copies].forward(xb)
 
     def timed(n_steps):

@@ -222,6 +222,13 @@ int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
     return 0;
 }
 
+int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    if (!ctx || !buf) return DWIM_B200_EINVAL;
+    buf->shadow_kind = SHADOW_NONE;
+    buf->bf16_exact = true;
+    return 0;
+}
+
 int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len) {
     if (!ctx || !buf || (!data && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == buf->len, DWIM_B200_EINVAL, "write of %zu floats to a buffer of %zu", len, buf->len);

@@ -280,10 +280,14 @@ __device__ __forceinline__ float block_sum_256(float v, float *scratch8) {
 //   by `weight` (Cpu::rmsnorm, gpu/cpu.rs:157-166: v * (scale * w) with
 //   scale = 1 / sqrt(sum(v^2) / dim + eps)); the f32 result goes to `xout`.
 // Then the row is scaled by a power of two 2^-e, chosen per token so that its
-// largest magnitude lands in [2^13, 2^14): whatever the activations' range,
-// the f16 value (and, for f32 inputs, the f16 remainder) keeps its full
-// precision, nothing is clamped or flushed, and the product's epilogue
-// multiplies the token's results by 2^e (tok_scale) again.  A thread takes
+// largest magnitude lands in [4, 8): whatever the activations' range, nothing
+// is clamped, an activation down to 2^-16 of the token's largest keeps its
+// full f16 precision (and, for f32 inputs, the f16 remainder its share), and
+// the product's epilogue multiplies the token's results by 2^e (tok_scale)
+// again.  (Rows of typical normalized activations, largest magnitude 4 to 8,
+// are not scaled at all.  Scaling them up instead, to just below f16's
+// maximum, was measured to slow the tensor-core kernel by half: the same
+// kernel on larger operand magnitudes runs into the power limit earlier.)  A thread takes
 // four consecutive activations per round, eight threads a 32-wide sub-block,
 // 64 a unit, the block four units.
 template <bool NORM, bool ALIGNED>   // ALIGNED: x (and xout, weight) are 16-byte aligned (a wrapped caller's pointer need not be)
@@ -327,9 +331,9 @@ __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *x, const
         }
     }
     amax = block_max_256(amax, scratch8);
-    // amax in [2^(b-127), 2^(b-126)) for its biased exponent b; e = b - 127 - 13, kept where 2^e and
+    // amax in [2^(b-127), 2^(b-126)) for its biased exponent b; e = b - 127 - 2, kept where 2^e and
     // 2^-e are normal floats (a row of zeros, subnormals or infinities takes the nearest end)
-    int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 140;
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 129;
     e = amax > 0.0f ? max(-100, min(100, e)) : 0;
     const float down = __uint_as_float((uint32_t)(127 - e) << 23);
     if (k == 0) tok_scale[t] = __uint_as_float((uint32_t)(127 + e) << 23);

@@ -119,6 +119,10 @@ class B200:
         caller's, a collective): its cached operand form is dropped."""
         self._check(self._L.dwim_b200_touch(self._ctx, buf._h))
 
+    def touch_bf16(self, buf: Buffer) -> None:
+        """``touch`` by a writer that vouches every value it wrote is exactly a bf16."""
+        self._check(self._L.dwim_b200_touch_bf16(self._ctx, buf._h))
+
     def resize(self, buf: Buffer, length: int) -> None:
         self._check(self._L.dwim_b200_resize(self._ctx, buf._h, length))
 

@@ -123,6 +123,11 @@ DWIM_B200_API int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, si
  * product reads the buffer, or that product multiplies the old contents.  It
  * also forgets that the contents were exact in 16 bits (write_bf16). */
 DWIM_B200_API int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
+/* The same, where the caller vouches that every value it wrote is exactly a
+ * bf16 (the output of a bf16 kernel widened to f32): the next product then
+ * carries a token as one 16-bit column instead of two, as after write_bf16.
+ * A value that is not a bf16 would be rounded to f16's 11 bits, silently. */
+DWIM_B200_API int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
 /* Device::write (gpu/mod.rs:224-225): `len` must equal the buffer's length. */
 DWIM_B200_API int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len);
 /* As write, from bf16 bits (gpu/float.rs:5-8): the buffer holds the same
