@@ -46,6 +46,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -209,13 +211,40 @@ __device__ __forceinline__ uint32_t f16x2_rn(float lo, float hi) {
 }
 __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-// One finished element: the operator's epilogue, then the store (to every rank's copy of a shared result).
-__device__ __forceinline__ void gemm_emit(const GemmArgs &a, size_t t, size_t row, float x) {
-    const size_t i = t * a.out.pitch + a.out.row0 + row;
-    if (a.epi == EPI_ADD) x += a.out.dst[0][i];
-    else if (a.epi == EPI_SWIGLU) x = silu_mul_f(x, a.aux[t * a.rows + row]);
-    a.out.dst[0][i] = x;
-    for (int p = 1; p < a.out.world; p++) a.out.dst[p][i] = x;
+// Where a thread's results go: its row of one destination, or of every rank's copy of a shared
+// result.  The pointers are read from the kernel's parameters by constant index, once, ahead of
+// the stores' loop (indexing the parameter array by a variable, or reading a parameter after
+// every store, cost the 256-column kernel half its speed).
+struct EmitTo {
+    float *row[DWIM_MAX_WORLD];   // [p]: destination p's element (token 0, this thread's row)
+    size_t pitch;
+    const float *aux_row;
+    int world, epi;
+};
+__device__ __forceinline__ EmitTo emit_to(const GemmArgs &a, size_t row) {
+    EmitTo e;
+#pragma unroll
+    for (int p = 0; p < DWIM_MAX_WORLD; p++) e.row[p] = p < a.out.world ? a.out.dst[p] + a.out.row0 + row : nullptr;
+    e.pitch = a.out.pitch;
+    e.aux_row = a.aux ? a.aux + row : nullptr;
+    e.world = a.out.world;
+    e.epi = a.epi;
+    return e;
+}
+// One finished element: the operator's epilogue, then the store.
+template <bool SHARED>
+__device__ __forceinline__ void gemm_emit(const EmitTo &e, size_t rows, size_t t, float x) {
+    float *o = e.row[0] + t * e.pitch;
+    if (!SHARED) {
+        if (e.epi == EPI_ADD) x += *o;
+        else if (e.epi == EPI_SWIGLU) x = silu_mul_f(x, e.aux_row[t * rows]);
+    }
+    *o = x;
+    if (SHARED) {
+#pragma unroll
+        for (int p = 1; p < DWIM_MAX_WORLD; p++)
+            if (p < e.world) e.row[p][t * e.pitch] = x;
+    }
 }
 
 constexpr uint32_t H2_1024 = 0x64006400u, H2_M1024 = 0xE400E400u, H2_64 = 0x54005400u, H2_M64 = 0xD400D400u;
@@ -308,7 +337,7 @@ __device__ __forceinline__ void mins_q4k_terms(const uint4 &hdr, int part, float
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const __grid_constant__ CUtensorMap tmap_m, const GemmArgs a) {
+                const __grid_constant__ CUtensorMap tmap_m, const __grid_constant__ GemmArgs a) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzled tiles want 1024-byte alignment
@@ -544,19 +573,27 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             const size_t row = (size_t)row0 + rl;
             if (row < a.rows) {
                 const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
-                if (a.split) {
+                const EmitTo to = emit_to(a, row);
+                const size_t n = a.n, rows = a.rows;
+                const uint32_t tk = tok0 + g * C::DRAIN_COLS * 4;
+                auto all = [&](auto shared) {
+                    constexpr bool SHARED = decltype(shared)::value;
+                    if (a.split) {
 #pragma unroll
-                    for (int j = 0; j < C::DRAIN_COLS; j += 2) {
-                        const size_t t = (cbase + j) >> 1;
-                        if (t < a.n) gemm_emit(a, t, row, (acc[j] + acc[j + 1]) * lds32f(tok0 + (g * C::DRAIN_COLS + j) * 4));
-                    }
-                } else {
+                        for (int j = 0; j < C::DRAIN_COLS; j += 2) {
+                            const size_t t = (cbase + j) >> 1;
+                            if (t < n) gemm_emit<SHARED>(to, rows, t, (acc[j] + acc[j + 1]) * lds32f(tk + j * 4));
+                        }
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < C::DRAIN_COLS; j++) {
-                        const size_t t = cbase + j;
-                        if (t < a.n) gemm_emit(a, t, row, acc[j] * lds32f(tok0 + (g * C::DRAIN_COLS + j) * 4));
+                        for (int j = 0; j < C::DRAIN_COLS; j++) {
+                            const size_t t = cbase + j;
+                            if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j] * lds32f(tk + j * 4));
+                        }
                     }
-                }
+                };
+                if (to.world == 1) all(std::false_type{});
+                else all(std::true_type{});      // a shared result: a plain product only (the host checks)
             }
         }
     }

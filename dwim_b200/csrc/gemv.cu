@@ -571,12 +571,18 @@ __device__ __forceinline__ void emit(const GemvArgs &a, size_t t, size_t r, floa
     if (a.epi == EPI_ADD) v += a.out.dst[0][i];
     else if (a.epi == EPI_SWIGLU) v = silu_mul(v, a.aux[(a.t0 + t) * a.w.rows + r]);
     a.out.dst[0][i] = v;
-    // a shared result: the same element of every peer's copy (plain stores over NVLink)
-    for (int p = 1; p < a.out.world; p++) a.out.dst[p][i] = v;
+    // a shared result: the same element of every peer's copy (plain stores over NVLink).  The
+    // parameter array is indexed by constants only: a variable index would make the compiler keep
+    // a copy of the kernel's parameters in local memory.
+    if (a.out.world > 1) {
+#pragma unroll
+        for (int p = 1; p < DWIM_MAX_WORLD; p++)
+            if (p < a.out.world) a.out.dst[p][i] = v;
+    }
 }
 
 template <int FMT, int NT, int RT, int KS>
-__global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(const __grid_constant__ GemvArgs a) {
     constexpr int NW = RT * KS;
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;

@@ -59,7 +59,7 @@ struct Bf16Args {
 
 __device__ __forceinline__ float silu_mul_n(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-__global__ void __launch_bounds__(256) matmul_bf16_kernel(const Bf16Args a) {
+__global__ void __launch_bounds__(256) matmul_bf16_kernel(const __grid_constant__ Bf16Args a) {
     griddep_launch();
     griddep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -96,7 +96,11 @@ __global__ void __launch_bounds__(256) matmul_bf16_kernel(const Bf16Args a) {
             if (a.epi == EPI_ADD) y += a.out.dst[0][i];
             else if (a.epi == EPI_SWIGLU) y = silu_mul_n(y, a.aux[(t0 + t) * a.rows + r]);
             a.out.dst[0][i] = y;
-            for (int p = 1; p < a.out.world; p++) a.out.dst[p][i] = y;
+            if (a.out.world > 1) {
+#pragma unroll
+                for (int p = 1; p < DWIM_MAX_WORLD; p++)
+                    if (p < a.out.world) a.out.dst[p][i] = y;
+            }
         }
     }
 }
