@@ -306,6 +306,25 @@ __device__ __forceinline__ void unit_q4k_i8(const Lane &L, const I8Cols X, int u
     const uint32_t ma[2] = {ha.z & 0x3f3f3f3fu, ((ha.w >> 4) & 0x0f0f0f0fu) | ((ha.z >> 2) & 0x30303030u)};
     const uint32_t mb[2] = {hb.z & 0x3f3f3f3fu, ((hb.w >> 4) & 0x0f0f0f0fu) | ((hb.z >> 2) & 0x30303030u)};
     const float da = h2f_lo(ha.x), dma = h2f_hi(ha.x), db = h2f_lo(hb.x), dmb = h2f_hi(hb.x);
+    if constexpr (NTILE == 1) {
+        // one tile of 4n columns: the lane's two columns exist together, their sums and worths sit side by side
+        uint4 t0 = make_uint4(0, 0, 0, 0), t1 = t0;
+        float2 worth = make_float2(0.0f, 0.0f);
+        if (2 * L.c < X.tile_cols) {
+            t0 = lds128(blob + 256 * X.nc + (2 * L.c) * 16);
+            t1 = lds128(blob + 256 * X.nc + (2 * L.c + 1) * 16);
+            worth = lds64f2(blob + 272 * X.nc + 8 * L.c);
+        }
+        const int m0 = (dp4a_us(ma[1], t0.y, dp4a_us(ma[0], t0.x, 0)) << 7) + dp4a_us(ma[1], t0.w, dp4a_us(ma[0], t0.z, 0));
+        const int m1 = (dp4a_us(ma[1], t1.y, dp4a_us(ma[0], t1.x, 0)) << 7) + dp4a_us(ma[1], t1.w, dp4a_us(ma[0], t1.z, 0));
+        const int m2 = (dp4a_us(mb[1], t0.y, dp4a_us(mb[0], t0.x, 0)) << 7) + dp4a_us(mb[1], t0.w, dp4a_us(mb[0], t0.z, 0));
+        const int m3 = (dp4a_us(mb[1], t1.y, dp4a_us(mb[0], t1.x, 0)) << 7) + dp4a_us(mb[1], t1.w, dp4a_us(mb[0], t1.z, 0));
+        acc[0] += worth.x * (da * (float)(ilo[0][0] + (ihi[0][0] >> 4)) - dma * (float)m0);
+        acc[1] += worth.y * (da * (float)(ilo[0][1] + (ihi[0][1] >> 4)) - dma * (float)m1);
+        acc[2] += worth.x * (db * (float)(ilo[0][2] + (ihi[0][2] >> 4)) - dmb * (float)m2);
+        acc[3] += worth.y * (db * (float)(ilo[0][3] + (ihi[0][3] >> 4)) - dmb * (float)m3);
+        return;
+    }
 #pragma unroll
     for (int p = 0; p < NTILE; p++)
 #pragma unroll
