@@ -23,6 +23,7 @@ namespace dwim {
 bool gemm_supports(const WeightView &w);
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue);
+void gemm_release(dwim_b200_ctx *ctx);
 }  // namespace dwim
 
 extern "C" {
@@ -98,6 +99,7 @@ int dwim_b200_close(dwim_b200_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->stream || !ctx->stream_owned) cudaStreamSynchronize(ctx->stream);
     peer_release(ctx);
+    gemm_release(ctx);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
     if (ctx->argmax_dev) cudaFree(ctx->argmax_dev);
@@ -418,9 +420,7 @@ int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, co
 static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size_t cols, int split) {
     if (x->shadow_kind == kind && x->shadow_cols == cols && x->shadow_split == split) return 0;
     size_t n = x->len / cols;
-    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n, split)
-                  : kind == SHADOW_PANEL_I8 ? panel_i8_bytes(cols, n)
-                                            : panel_bytes(cols, (int)n * (split ? 2 : 1));
+    size_t need = kind == SHADOW_GEMM ? gemm_operand_bytes(cols, n, split) : panel_i8_bytes(cols, n);
     if (need > x->shadow_cap) {
         if (x->shadow) {
             DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -432,9 +432,8 @@ static int ensure_shadow(dwim_b200_ctx *ctx, dwim_b200_buffer *x, int kind, size
         x->shadow_cap = need;
     }
     x->shadow_kind = SHADOW_NONE;
-    int rc = kind == SHADOW_GEMM       ? build_gemm_operand(ctx, x->data, n, cols, split, (__half *)x->shadow)
-             : kind == SHADOW_PANEL_I8 ? build_panels_i8(ctx, x->data, n, cols, (uint8_t *)x->shadow)
-                                       : build_panels(ctx, x->data, n, cols, kind, split, (__half *)x->shadow);
+    int rc = kind == SHADOW_GEMM ? build_gemm_operand(ctx, x->data, n, cols, split, (__half *)x->shadow)
+                                 : build_panels_i8(ctx, x->data, n, cols, (uint8_t *)x->shadow);
     if (rc) return rc;
     x->shadow_kind = kind;
     x->shadow_cols = cols;
@@ -455,29 +454,43 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
     if (v.fmt == BF16) return matmul_bf16(ctx, v, x->data, n, out, aux, epilogue);
     // bf16 activations are exact in one f16 column; f32 ones travel as two
     // (value and rounding remainder), summed again in the epilogue.
-    // Q4_K: the tensor-core kernel from nine tokens on (measured on B200 at [17408, 5120]: 29 us at 32
-    // tokens against 57 us for sixteen through the small-M kernel's f16 routine)
-    if (n > I8_MAX_TOKENS && gemm_supports(v)) {
+    // Up to eight tokens: the small-M kernel's int8 routines.  Above: the tensor-core kernels -- Q4_K
+    // from nine tokens on (measured on B200 at [17408, 5120]: 26 us at nine to sixteen tokens, against
+    // 57 us for sixteen through two small-M launches); Q6_K and Q8_0, whose dense path first decodes
+    // the matrix, from 33 on, and in groups of eight through the small-M kernel below that.
+    const bool dense = gemm_supports(v) && n > (v.fmt == Q4_K ? (size_t)I8_MAX_TOKENS : (size_t)32);
+    if (dense) {
+        // bf16 activations are exact in one f16 column; f32 ones travel as two
+        // (value and rounding remainder), summed again in the epilogue.
         int split = x->bf16_exact ? 0 : 1;
         int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
         if (rc) return rc;
         return gemm_large(ctx, v, (const __half *)x->shadow, n, split, out, aux, epilogue);
     }
-    // one or two tokens of Q4_K: integer nibbles against the activations' int8 digit planes
-    if (gemv_takes_i8(v, n)) {
+    if (!gemv_takes_i8(v, n < (size_t)I8_MAX_TOKENS ? n : (size_t)I8_MAX_TOKENS))
+        return fail(ctx, DWIM_B200_EFORMAT, "%s: no kernel takes format %d with %zu columns", what, v.fmt, v.cols);
+    if (n <= (size_t)I8_MAX_TOKENS) {
         int rc = ensure_shadow(ctx, x, SHADOW_PANEL_I8, v.cols, 0);
         if (rc) return rc;
-        return gemv_small_i8(ctx, v, (const uint8_t *)x->shadow, (int)n, out, aux, epilogue);
+        return gemv_small_i8(ctx, v, (const uint8_t *)x->shadow, (int)n, 0, out, aux, epilogue);
     }
-    // bf16 activations are exact in one f16 column; f32 ones travel as two.
-    int split = x->bf16_exact ? 0 : 1;
-    int rc = ensure_shadow(ctx, x, v.fmt == Q4_K ? SHADOW_PANEL_Q4K : SHADOW_PANEL_NATURAL, v.cols, split);
-    if (rc) return rc;
-    int per = gemv_max_tokens(split), ncols_total = (int)n * (split ? 2 : 1);
-    for (size_t t0 = 0; t0 < n; t0 += per) {
-        int nt = (int)(n - t0 < (size_t)per ? n - t0 : per);
-        rc = gemv_small(ctx, v, (const __half *)x->shadow, ncols_total, (int)t0 * (split ? 2 : 1), nt, t0, split, out, aux,
-                        epilogue);
+    // groups of eight tokens, each with its own digit planes (the buffer's shadow holds one group at a time)
+    const size_t need = panel_i8_bytes(v.cols, I8_MAX_TOKENS);
+    if (need > x->shadow_cap) {
+        if (x->shadow) {
+            DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(x->shadow);
+            x->shadow = nullptr;
+            x->shadow_cap = 0;
+        }
+        DWIM_CUDA(ctx, cudaMalloc(&x->shadow, need));
+        x->shadow_cap = need;
+    }
+    x->shadow_kind = SHADOW_NONE;
+    for (size_t t0 = 0; t0 < n; t0 += I8_MAX_TOKENS) {
+        const size_t nt = n - t0 < (size_t)I8_MAX_TOKENS ? n - t0 : (size_t)I8_MAX_TOKENS;
+        int rc = build_panels_i8(ctx, x->data + t0 * v.cols, nt, v.cols, (uint8_t *)x->shadow);
+        if (rc == 0) rc = gemv_small_i8(ctx, v, (const uint8_t *)x->shadow, (int)nt, t0, out, aux, epilogue);
         if (rc) return rc;
     }
     return 0;
@@ -535,7 +548,7 @@ int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_
         // one and two tokens: both matrices in one launch, the activation applied where the two sums meet
         rc = ensure_shadow(ctx, x, SHADOW_PANEL_I8, gate->v.cols, 0);
         if (rc == 0)
-            rc = gemv_small_i8(ctx, gate->v, (const uint8_t *)x->shadow, (int)n, out_local(out->data, gate->v.rows), nullptr, EPI_STORE, &up->v);
+            rc = gemv_small_i8(ctx, gate->v, (const uint8_t *)x->shadow, (int)n, 0, out_local(out->data, gate->v.rows), nullptr, EPI_STORE, &up->v);
     } else {
         // up . x into scratch, then gate . x with the activation fused into the
         // epilogue, as the reference's CUDA device does (gpu/cuda/mod.rs:1148-1175).

@@ -15,10 +15,8 @@
 // so that consecutive matmuls on one input convert it once).
 enum ShadowKind : int {
     SHADOW_NONE = 0,
-    SHADOW_PANEL_NATURAL,   // small-M panels, k in order            (Q8_0, Q6_K)
-    SHADOW_PANEL_Q4K,       // small-M panels, k permuted + swizzled (Q4_K)
-    SHADOW_GEMM,            // f16 rows + sub-block means, for the tensor-core GEMM
-    SHADOW_PANEL_I8         // int8 digit planes per 256-wide unit, for the one- and two-token Q4_K kernel
+    SHADOW_GEMM,            // f16 rows, sub-block means and token scales, for the tensor-core kernels
+    SHADOW_PANEL_I8         // int8 digit planes per 256-wide unit, for the small-M kernel
 };
 
 constexpr int DWIM_MAX_WORLD = 8;
@@ -67,6 +65,10 @@ struct dwim_b200_ctx {
     // (an upload's repack): that launch must be an ordinary one, because a
     // programmatic dependent streams weights before it waits for the kernels ahead.
     bool weights_written = false;
+    // the dense pair kernel's weight panel: f16 value and remainder of the dequantized rows, the rows' scales (gemm.cu)
+    __half *pair_hi = nullptr, *pair_lo = nullptr;
+    float *pair_scale = nullptr;
+    size_t pair_cap = 0;             // f16 elements in each of the two
     // argmax's result slots: device keys, their pinned host copy (neighbours.cu), created on request
     unsigned long long *argmax_dev = nullptr, *argmax_host = nullptr;
     size_t argmax_cap = 0;
@@ -152,11 +154,6 @@ int dequantize_device(dwim_b200_ctx *ctx, const WeightView &w, float *out_dev);
 int quantize_device(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const float *w_dev, uint8_t *file_dev);
 
 // prologue.cu
-// Elements (f16) of one column's panel per 256 weights of K: 256 activations
-// and 16 entries of per-sub-block means (hi then lo halves).
-constexpr int PANEL_STRIDE = 272;
-size_t panel_bytes(size_t cols, int ncols);
-int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels);
 // int8 panels: per unit of 256 activations one blob of i8_unit_bytes(nc), nc = planes * tokens columns
 // (column = 4*token + plane for one and two tokens, plane*tokens + token for three to eight):
 //   [sub-block j (8)][column][32 digits]        256*nc B
@@ -180,16 +177,14 @@ enum Epilogue : int { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
 // One launch: tokens [t0, t0 + n_tokens) of a panel array holding ncols_total
 // columns, the launch's first at col0.  aux is the `up` product for EPI_SWIGLU.
 bool gemv_takes_i8(const WeightView &w, size_t n);
-int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, const OutSpec &out, const float *aux,
-                  int epilogue, const WeightView *up = nullptr);
+// n_tokens tokens (at most eight) whose results are tokens [t0, t0 + n_tokens) of out and aux.
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, size_t t0, const OutSpec &out,
+                  const float *aux, int epilogue, const WeightView *up = nullptr);
 void peer_release(dwim_b200_ctx *ctx);
 void shared_release(dwim_b200_buffer *buf);
 // neighbours.cu
 int matmul_bf16(dwim_b200_ctx *ctx, const WeightView &w, const float *x, size_t n, const OutSpec &out, const float *aux, int epi);
 // static_scratch.cu
 int static_scratch_prepare(dwim_b200_ctx *ctx);
-int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
-               size_t t0, int split, const OutSpec &out, const float *aux, int epilogue);
-int gemv_max_tokens(int split);
 
 }  // namespace dwim

@@ -602,6 +602,199 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ---- the dense pair kernel: Q8_0 and Q6_K above the small-M kernel's range --------------------
+// Those formats scale every 32 (Q8_0) or 16 (Q6_K) weights by a factor of their own,
+// so their integer quants cannot share an accumulator the way Q4_K's sc*q do, and a
+// weight times its scales does not fit f16's 11 bits.  Their large-M product therefore
+// runs on dequantized weights carried exactly as two f16 terms: a row panel of W is
+// decoded (bit-exact decoders of formats.cuh), scaled by a power of two per row so
+// that its largest weight lands in [8, 16), and written as hi = f16(w) and
+// lo = f16(w - hi) (22 bits between them); the kernel below multiplies
+// (hi + lo) . x with two MMAs per 16 of K into one TMEM accumulator over the whole of
+// K, and the epilogue multiplies by the row's and the token's powers of two again.
+// Plain tcgen05 pipeline: warp 0 feeds hi, lo and activation tiles by TMA, warp 1
+// issues the MMAs, warps 2-5 (one per TMEM lane quadrant) drain and store.
+struct PairArgs {
+    size_t rows;            // weight rows of the whole matrix (the pitch of aux)
+    size_t panel_row0;      // first row of this panel
+    size_t panel_rows;      // rows in this panel
+    size_t n, ncols, kblocks;
+    int split;
+    OutSpec out;
+    const float *row_scale;   // [panel_rows]
+    const float *tok_scale;   // [n]
+    const float *aux;
+    int epi;
+    uint32_t *status;
+};
+template <int BN> struct PairCfg {
+    static constexpr int STAGE = 2 * A_BYTES + BN * BK * 2;
+    static constexpr int STAGES = (MAX_SMEM - 4096 - BN * 4) / STAGE > 6 ? 6 : (MAX_SMEM - 4096 - BN * 4) / STAGE;
+    static constexpr int SMEM = 2048 + STAGES * STAGE + BN * 4 + 1024;
+    static_assert(STAGES >= 3 && SMEM <= MAX_SMEM, "the pair kernel's stages do not fit");
+};
+constexpr int PAIR_THREADS = 6 * 32;
+
+template <int BN>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
+                 const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PairArgs a) {
+    using C = PairCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full0 = base, empty0 = base + 64, accfull = base + 128, tmem_slot = base + 136;
+    const uint32_t stage0 = base + 1024, tok0 = stage0 + C::STAGES * C::STAGE;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
+    const int kblocks = (int)a.kblocks;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accfull, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    griddep_launch();
+    if (warp == 0) {
+        griddep_wait();   // the weight panel and the activations' operand come from the kernels just ahead
+        if (lane == 0) {
+            for (int kb = 0; kb < kblocks; kb++) {
+                const int s = kb % C::STAGES;
+                mbar_wait_parked(empty0 + 8 * s, ((kb / C::STAGES) & 1) ^ 1, a.status, 0x100000u);
+                mbar_expect_tx(full0 + 8 * s, C::STAGE);
+                const uint32_t st = stage0 + s * C::STAGE;
+                tma_load_2d(st, &tmap_hi, kb * BK, row0, full0 + 8 * s);
+                tma_load_2d(st + A_BYTES, &tmap_lo, kb * BK, row0, full0 + 8 * s);
+                tma_load_2d(st + 2 * A_BYTES, &tmap_x, kb * BK, col0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
+        constexpr uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);   // stride offset 1024 B, version 1, 128-byte swizzle
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
+        for (int kb = 0; kb < kblocks; kb++) {
+            const int s = kb % C::STAGES;
+            mbar_wait_parked(full0 + 8 * s, (kb / C::STAGES) & 1, a.status, 0x200000u);
+            tc_fence_after();
+            const uint32_t st = stage0 + s * C::STAGE;
+            const uint32_t hi_lo = ((st & 0x3ffffu) >> 4) | (1u << 16), lo_lo = (((st + A_BYTES) & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t b_lo = (((st + 2 * A_BYTES) & 0x3ffffu) >> 4) | (1u << 16);
+            if (lane == 0) {
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) {
+                    if (kb == 0 && k == 0) umma_f16_lo<0>(tm, hi_lo, b_lo, desc_hi, idesc);
+                    else umma_f16_lo<1>(tm, hi_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                    umma_f16_lo<1>(tm, lo_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                }
+                umma_commit(empty0 + 8 * s);
+                if (kb == kblocks - 1) umma_commit(accfull);
+            }
+            __syncwarp();
+        }
+    } else {
+        const int quad = warp & 3;
+        const int rl = quad * 32 + lane;
+        griddep_wait();   // the kernel ahead may still read or write `out` and `aux`
+        for (int j = lane; j < BN; j += 32) {
+            const size_t t = ((size_t)col0 + j) >> (a.split ? 1 : 0);
+            sts32f(tok0 + j * 4, t < a.n ? a.tok_scale[t] : 0.0f);
+        }
+        __syncwarp();
+        const size_t prow = (size_t)row0 + rl;                 // row within the panel
+        const bool live = prow < a.panel_rows;
+        const float rs = live ? a.row_scale[prow] : 0.0f;
+        mbar_wait_parked(accfull, 0, a.status, 0x400000u);
+        tc_fence_after();
+        // destinations of this thread's row, by constant index (see EmitTo)
+        EmitTo to;
+#pragma unroll
+        for (int p = 0; p < DWIM_MAX_WORLD; p++)
+            to.row[p] = p < a.out.world ? a.out.dst[p] + a.out.row0 + a.panel_row0 + prow : nullptr;
+        to.pitch = a.out.pitch;
+        to.aux_row = a.aux ? a.aux + a.panel_row0 + prow : nullptr;
+        to.world = a.out.world;
+        to.epi = a.epi;
+        const size_t n = a.n, rows = a.rows;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+        for (int c = 0; c < BN / 16; c++) {
+            uint32_t v[16];
+            tmem_ld16(taddr + c * 16, v);
+            tmem_ld_wait();
+            if (!live) continue;
+            const size_t cbase = (size_t)col0 + c * 16;
+            auto all = [&](auto shared) {
+                constexpr bool SHARED = decltype(shared)::value;
+                if (a.split) {
+#pragma unroll
+                    for (int j = 0; j < 16; j += 2) {
+                        const size_t t = (cbase + j) >> 1;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const size_t t = cbase + j;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    }
+                }
+            };
+            if (to.world == 1) all(std::false_type{});
+            else all(std::true_type{});
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+}
+
+// A row of W decoded, scaled by its own power of two and written as two f16 terms, each run of
+// four k in the order (0, 2, 1, 3) the activations' operand is stored in.  One block per row.
+__global__ void __launch_bounds__(256) dequant_pair_kernel(const WeightView w, size_t row0, size_t cols, __half *__restrict__ hi,
+                                                           __half *__restrict__ lo, float *__restrict__ row_scale) {
+    griddep_launch();
+    griddep_wait();   // the kernel ahead may still read the panel
+    __shared__ float part[8];
+    const size_t r = row0 + blockIdx.x;
+    const uint8_t *row = w.quants + r * w.qpitch;
+    auto weight = [&](size_t k) -> float {
+        if (w.fmt == Q6_K) return q6k_weight(row + (k >> 8) * Q6_K_DEV, __half2float(w.scales[r * w.srow + (k >> 8)]), (int)(k & 255));
+        if (w.fmt == Q4_K) return q4k_weight(row + (k >> 8) * Q4_K_FILE, (int)(k & 255));
+        if (w.fmt == BF16) return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(row)[k] << 16);
+        return __fmul_rn((float)(int8_t)row[k], __half2float(w.scales[r * w.srow + (k >> 5)]));   // gpu/quant.rs:48-62
+    };
+    float amax = 0.0f;
+    for (size_t k = threadIdx.x; k < cols; k += 256) amax = fmaxf(amax, fabsf(weight(k)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = part[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) amax = fmaxf(amax, part[i]);
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 130;     // the largest weight to [8, 16)
+    e = amax > 0.0f ? max(-100, min(100, e)) : 0;
+    const float down = __uint_as_float((uint32_t)(127 - e) << 23);
+    if (threadIdx.x == 0) row_scale[blockIdx.x] = __uint_as_float((uint32_t)(127 + e) << 23);
+    __half *h = hi + (size_t)blockIdx.x * cols, *l = lo + (size_t)blockIdx.x * cols;
+    for (size_t k = threadIdx.x; k < cols; k += 256) {
+        const float v = weight(k) * down;
+        const __half a = to_f16_clamped(v);
+        const size_t at = (k & ~(size_t)3) | ((k & 1) << 1) | ((k >> 1) & 1);   // 0, 1, 2, 3 -> 0, 2, 1, 3
+        h[at] = a;
+        l[at] = to_f16_clamped(v - __half2float(a));
+    }
+}
+
 // ---- host side ---------------------------------------------------------------------
 typedef CUresult (*EncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                 const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -666,20 +859,93 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
     return 0;
 }
 
+constexpr size_t PAIR_PANEL_ROWS = 16384;   // rows decoded at a time: 335 MB of f16 pairs at 5120 columns
+
+template <int BN>
+int launch_pair(dwim_b200_ctx *ctx, const WeightView &w, size_t r0, size_t nr, const __half *operand, size_t n, int split,
+                const OutSpec &out, const float *aux, int epi) {
+    using C = PairCfg<BN>;
+    const size_t ncols = n * (split ? 2 : 1), units = w.cols / 256;
+    const __half *hi = ctx->pair_hi, *lo = ctx->pair_lo;
+    CUtensorMap th, tl, tx;
+    int rc;
+    if ((rc = encode_2d(ctx, &th, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, hi, w.cols, nr, w.cols * 2, BK, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B,
+                        "weight panel (hi)")))
+        return rc;
+    if ((rc = encode_2d(ctx, &tl, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, lo, w.cols, nr, w.cols * 2, BK, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B,
+                        "weight panel (lo)")))
+        return rc;
+    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B,
+                        "activation")))
+        return rc;
+    const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
+    PairArgs a{w.rows, r0, nr, n, ncols, w.cols / BK, split, out, ctx->pair_scale, tok_scale, aux, epi, ctx->status};
+    auto kern = gemm_pair_kernel<BN>;
+    static bool configured[64] = {false};
+    if (!configured[ctx->device & 63]) {
+        DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured[ctx->device & 63] = true;
+    }
+    dim3 grid((unsigned)((nr + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
+    DWIM_CUDA(ctx, launch_dependent(true, kern, grid, dim3(PAIR_THREADS), (size_t)C::SMEM, ctx->stream, th, tl, tx, a));
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}
+
 }  // namespace
 
-// Formats the tensor-core kernel takes; the rest goes through the small-M
-// kernel in groups of tokens.
-bool gemm_supports(const WeightView &w) { return w.fmt == Q4_K && w.cols % 256 == 0; }
+// Formats the tensor-core kernels take: Q4_K by the kernel that multiplies its integers
+// directly, the others as dequantized f16 pairs, a panel of rows at a time.
+bool gemm_supports(const WeightView &w) { return w.cols % 256 == 0 && (w.fmt == Q4_K || w.fmt == Q6_K || w.fmt == Q8_0); }
 
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue) {
     if (!gemm_supports(w)) return fail(ctx, DWIM_B200_EFORMAT, "the tensor-core GEMM does not take format %d", w.fmt);
     const size_t ncols = n * (split ? 2 : 1);
-    if (ncols <= 32) return launch_gemm<32>(ctx, w, operand, n, split, out, aux, epilogue);
-    if (ncols <= 64) return launch_gemm<64>(ctx, w, operand, n, split, out, aux, epilogue);
-    if (ncols <= 128) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
-    return launch_gemm<256>(ctx, w, operand, n, split, out, aux, epilogue);
+    if (w.fmt == Q4_K) {
+        if (ncols <= 32) return launch_gemm<32>(ctx, w, operand, n, split, out, aux, epilogue);
+        if (ncols <= 64) return launch_gemm<64>(ctx, w, operand, n, split, out, aux, epilogue);
+        if (ncols <= 128) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
+        return launch_gemm<256>(ctx, w, operand, n, split, out, aux, epilogue);
+    }
+    // the panel's buffers: created on first use, grown when a wider matrix comes
+    const size_t panel = w.rows < PAIR_PANEL_ROWS ? (w.rows + TILE_M - 1) / TILE_M * TILE_M : PAIR_PANEL_ROWS;
+    const size_t need = panel * w.cols;
+    if (need > ctx->pair_cap) {
+        if (ctx->pair_hi) {
+            DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ctx->pair_hi);
+            cudaFree(ctx->pair_lo);
+            ctx->pair_hi = ctx->pair_lo = nullptr;
+            ctx->pair_cap = 0;
+        }
+        DWIM_CUDA(ctx, cudaMalloc((void **)&ctx->pair_hi, need * sizeof(__half)));
+        DWIM_CUDA(ctx, cudaMalloc((void **)&ctx->pair_lo, need * sizeof(__half)));
+        if (!ctx->pair_scale) DWIM_CUDA(ctx, cudaMalloc((void **)&ctx->pair_scale, PAIR_PANEL_ROWS * sizeof(float)));
+        ctx->pair_cap = need;
+    }
+    for (size_t r0 = 0; r0 < w.rows; r0 += panel) {
+        const size_t nr = w.rows - r0 < panel ? w.rows - r0 : panel;
+        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, dequant_pair_kernel, dim3((unsigned)nr), dim3(256), 0, ctx->stream, w, r0,
+                                        w.cols, ctx->pair_hi, ctx->pair_lo, ctx->pair_scale));
+        ctx->weights_written = false;
+        DWIM_LAUNCHED(ctx);
+        int rc;
+        if (ncols <= 64) rc = launch_pair<64>(ctx, w, r0, nr, operand, n, split, out, aux, epilogue);
+        else if (ncols <= 128) rc = launch_pair<128>(ctx, w, r0, nr, operand, n, split, out, aux, epilogue);
+        else rc = launch_pair<256>(ctx, w, r0, nr, operand, n, split, out, aux, epilogue);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+void gemm_release(dwim_b200_ctx *ctx) {
+    if (ctx->pair_hi) cudaFree(ctx->pair_hi);
+    if (ctx->pair_lo) cudaFree(ctx->pair_lo);
+    if (ctx->pair_scale) cudaFree(ctx->pair_scale);
+    ctx->pair_hi = ctx->pair_lo = nullptr;
+    ctx->pair_scale = nullptr;
+    ctx->pair_cap = 0;
 }
 
 }  // namespace dwim

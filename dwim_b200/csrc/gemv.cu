@@ -1,5 +1,5 @@
 // The small-M product (decode and speculative verify): out[t][r] = w[r] . x[t]
-// for up to 16 tokens, bound by how fast the packed weights stream from HBM.
+// for up to eight tokens, bound by how fast the packed weights stream from HBM.
 //
 // Replaces the reference's matmul_tile16_* / matmul_rows* kernels for few
 // tokens (matmul_tile.cu:94-258, matmul_rows.cu:29-184; dispatch at
@@ -10,19 +10,22 @@
 //     rows; for each tile it streams the rows' packed blocks, K in chunks of
 //     `kc` units of 256 weights, through a ring of shared-memory stages.
 //   - One producer warp fills the ring with cp.async.bulk (the TMA engine's
-//     untiled copy): per stage one copy per weight row (the row's bytes for
-//     the chunk are contiguous in HBM), one per row of scales where the format
-//     keeps them apart, and one per unit for the activation panels.  Stages
-//     are handed over with mbarriers (full: transaction bytes; empty: one
-//     arrival per consumer warp).  Every wait is bounded.
+//     untiled copy): a stage of whole rows is one contiguous run of HBM and one
+//     copy (plus one for the rows' scales where the format keeps them apart);
+//     longer rows are cut in chunks, one copy per row and chunk.  Stages are
+//     handed over with mbarriers (full: transaction bytes; empty: one arrival
+//     per consumer warp).  Every wait is bounded.
 //   - RT*KS consumer warps.  Warp (rt, ks) owns row tile rt and every KS-th
-//     unit of a chunk.  It unpacks quants in registers to f16 *integers*
-//     (exact), multiplies them with the f16 activation columns on the tensor
-//     cores (mma.sync m16n8k16, fp32 accumulate: weight rows are the M side,
-//     activation columns the N side) and applies the f16/f32 block scales to
-//     the fp32 partial sums.  An f32 activation travels as two f16 columns
-//     (value and rounding remainder), so products are exact and the result
-//     differs from the CPU's only by fp32 summation order.
+//     unit of a chunk.  The quants stay integers: nibbles (Q4_K) are masked
+//     four at a time, Q6_K's six bits assembled into signed bytes, Q8_0's bytes
+//     used as they are, and multiplied on the tensor cores (mma.sync int8,
+//     weight rows on the M side) with the activations' signed base-256 digit
+//     planes as columns (prologue.cu).  The integer sums of a sub-block are
+//     weighted by its scale (integer multiply-add for the 6-bit and 8-bit
+//     sub-scales, fp32 for Q8_0's f16 ones), and the unit's d and the plane's
+//     worth scale once per unit in fp32: the result differs from the CPU's by
+//     fp32 summation order and the planes' rounding (2^-31 or 2^-23 of a unit's
+//     largest activation).
 //   - The K-split warps of a row tile are summed through shared memory in a
 //     fixed order (deterministic), then the epilogue stores, adds to, or
 //     SwiGLU-combines the output (modes after prelude.cu:29-35).
@@ -35,12 +38,10 @@
 namespace dwim {
 
 constexpr int MAX_STAGES = 8;
-constexpr int PANEL_BYTES = PANEL_STRIDE * 2;   // 544: 16 B multiple, 32 mod 128
 
 struct GemvArgs {
     WeightView w;
-    const uint8_t *panels;   // [units][ncols_total][PANEL_BYTES]
-    int ncols_total;         // columns in the panel array
+    const uint8_t *panels;   // [units][i8_unit_bytes(ncols)]: the activations' digit planes (prologue.cu)
     int xunit;               // bytes of one unit's panels for this launch
     int xsrc_stride;         // bytes between units in the panel array
     int ctas_per_sm;         // 0: one
@@ -49,9 +50,7 @@ struct GemvArgs {
     // writes silu(gate . x) * (up . x).  Null: an ordinary product.
     const uint8_t *up_quants;
     const __half *up_scales;
-    int col0;                // first column of this launch
-    int ncols;               // columns of this launch (<= 8*NT)
-    int split;               // 1: columns are (hi, lo) pairs of a token
+    int ncols;               // digit-plane columns: planes * tokens
     int n_tokens;            // tokens of this launch
     size_t t0;               // first token's index in out
     OutSpec out;
@@ -71,12 +70,6 @@ struct GemvArgs {
     uint32_t *status;
 };
 
-constexpr uint32_t H2_1024 = 0x64006400u;   // half2(1024, 1024)
-constexpr uint32_t H2_1056 = 0x64206420u;   // half2(1056, 1056)
-constexpr uint32_t H2_1152 = 0x64806480u;   // half2(1152, 1152)
-constexpr uint32_t H2_M1024 = 0xE400E400u;  // half2(-1024, -1024)
-constexpr uint32_t H2_M64 = 0xD400D400u;    // half2(-64, -64)
-constexpr uint32_t H2_SIXTEENTH = 0x2C002C00u;  // half2(1/16, 1/16)
 
 // Q4_K through the int8 tensor-core path (one or two tokens): the same blocks,
 // another activation operand and unit routine.
@@ -87,12 +80,9 @@ constexpr bool is_i8(int fmt) { return fmt == Q4K_I8 || fmt == Q8_I8 || fmt == Q
 constexpr int base_of(int fmt) { return fmt == Q4K_I8 ? (int)Q4_K : fmt == Q8_I8 ? (int)Q8_0 : fmt == Q6K_I8 ? (int)Q6_K : fmt; }
 
 template <int FMT> struct Traits;
-template <> struct Traits<Q4_K> { static constexpr int UNIT_Q = 144; };
 template <> struct Traits<Q4K_I8> { static constexpr int UNIT_Q = 144; };
 template <> struct Traits<Q8_I8> { static constexpr int UNIT_Q = 256; };
 template <> struct Traits<Q6K_I8> { static constexpr int UNIT_Q = 208; };
-template <> struct Traits<Q6_K> { static constexpr int UNIT_Q = 208; };
-template <> struct Traits<Q8_0> { static constexpr int UNIT_Q = 256; };
 
 // What a consumer lane needs to know about the stage it reads.
 struct Lane {
@@ -100,106 +90,7 @@ struct Lane {
     uint32_t row_a, row_b;   // shared addresses of rows g and g+8 (quant region)
     uint32_t srow_a, srow_b; // shared addresses of the rows' scales
     uint32_t xbase;          // shared address of the launch's panels (unit 0 of the stage, or of the row when resident)
-    uint32_t x[2];           // shared address of this lane's column panel, per column group
-    bool xv[2];              // whether that column exists
 };
-
-// ---------------------------------------------------------------------------
-// Q4_K: one unit = one 144-byte block per row
-// ---------------------------------------------------------------------------
-// Lane c owns the 64 weights [64c, 64c+64) of each of its two rows: 32 bytes
-// whose low nibbles are sub-block 2c and high nibbles sub-block 2c+1.  The
-// 6-bit sub-block scale is folded into the f16 integers before the MMA
-// (sc*q <= 945 is exact in f16), so a whole block shares the f32 factor d.
-// The minimums go through one more MMA per block: A = the eight m_j, B = the
-// per-sub-block activation means (hi, lo); acc -= 32*dmin * that.
-struct Q4kScales {
-    uint32_t mul_lo, add_lo;   // low nibbles:  (1024+q)   * sc      - 1024*sc
-    uint32_t mul_hi, add_hi;   // high nibbles: (1024+16q) * (sc/16) - 64*sc
-    uint32_t mins;             // half2(m_2c, m_2c+1)
-    float d, dmin32;
-};
-__device__ __forceinline__ Q4kScales q4k_scales(const uint4 &hdr, int c) {
-    int sh = (c & 1) * 16;
-    uint32_t y = (hdr.y >> sh) & 0xffffu, z = (hdr.z >> sh) & 0xffffu, w = (hdr.w >> sh) & 0xffffu;
-    uint32_t sc2 = c < 2 ? (y & 0x3f3fu) : ((w & 0x0f0fu) | ((y >> 2) & 0x3030u));
-    uint32_t m2 = c < 2 ? (z & 0x3f3fu) : (((w >> 4) & 0x0f0fu) | ((z >> 2) & 0x3030u));
-    // bytes (a, b) -> half2(a, b): put 0x64 above each byte (1024 + v), take 1024 off
-    uint32_t scp = hsub2(prmt(sc2, 0x00006464u, 0x5140u), H2_1024);
-    uint32_t mp = hsub2(prmt(m2, 0x00006464u, 0x5140u), H2_1024);
-    uint32_t sa = prmt(scp, scp, 0x1010u);   // half2(sc_a, sc_a)
-    uint32_t sb = prmt(scp, scp, 0x3232u);   // half2(sc_b, sc_b)
-    Q4kScales s;
-    s.mul_lo = sa;
-    s.add_lo = hmul2(sa, H2_M1024);
-    s.mul_hi = hmul2(sb, H2_SIXTEENTH);
-    s.add_hi = hmul2(sb, H2_M64);
-    s.mins = mp;
-    s.d = h2f_lo(hdr.x);
-    s.dmin32 = h2f_hi(hdr.x) * 32.0f;
-    return s;
-}
-
-template <int NT>
-__device__ __forceinline__ void unit_q4k(const Lane &L, int ul, int xu, int ncols, const uint32_t (&xo)[4],
-                                         float (&acc)[NT][4]) {
-    const uint32_t ba = L.row_a + ul * 144, bb = L.row_b + ul * 144;
-    const uint4 ha = lds128(ba), hb = lds128(bb);
-    uint32_t qa[8], qb[8];
-    {
-        uint4 t0 = lds128(ba + 16 + 32 * L.c), t1 = lds128(ba + 32 + 32 * L.c);
-        qa[0] = t0.x; qa[1] = t0.y; qa[2] = t0.z; qa[3] = t0.w;
-        qa[4] = t1.x; qa[5] = t1.y; qa[6] = t1.z; qa[7] = t1.w;
-        uint4 u0 = lds128(bb + 16 + 32 * L.c), u1 = lds128(bb + 32 + 32 * L.c);
-        qb[0] = u0.x; qb[1] = u0.y; qb[2] = u0.z; qb[3] = u0.w;
-        qb[4] = u1.x; qb[5] = u1.y; qb[6] = u1.z; qb[7] = u1.w;
-    }
-    const Q4kScales sa = q4k_scales(ha, L.c), sb = q4k_scales(hb, L.c);
-    // two independent accumulator chains (low / high nibbles) keep the tensor pipe busy
-    float c1[NT][4], c1h[NT][4], c2[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) c1[nt][i] = c1h[nt][i] = c2[nt][i] = 0.0f;
-    uint32_t xb[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 128 * L.c;
-
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t wa = qa[j], wb = qb[j], was = wa >> 8, wbs = wb >> 8;
-        // bytes (0,2) and (1,3) of the word, low then high nibbles
-        const uint32_t a_le = hfma2(lop3_and_or(wa, 0x000f000fu, H2_1024), sa.mul_lo, sa.add_lo);
-        const uint32_t a_lo = hfma2(lop3_and_or(was, 0x000f000fu, H2_1024), sa.mul_lo, sa.add_lo);
-        const uint32_t a_he = hfma2(lop3_and_or(wa, 0x00f000f0u, H2_1024), sa.mul_hi, sa.add_hi);
-        const uint32_t a_ho = hfma2(lop3_and_or(was, 0x00f000f0u, H2_1024), sa.mul_hi, sa.add_hi);
-        const uint32_t b_le = hfma2(lop3_and_or(wb, 0x000f000fu, H2_1024), sb.mul_lo, sb.add_lo);
-        const uint32_t b_lo = hfma2(lop3_and_or(wbs, 0x000f000fu, H2_1024), sb.mul_lo, sb.add_lo);
-        const uint32_t b_he = hfma2(lop3_and_or(wb, 0x00f000f0u, H2_1024), sb.mul_hi, sb.add_hi);
-        const uint32_t b_ho = hfma2(lop3_and_or(wbs, 0x00f000f0u, H2_1024), sb.mul_hi, sb.add_hi);
-        const uint32_t off = 8 * (j & 4) + xo[j & 3];
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            uint2 x0 = make_uint2(0, 0), x1 = make_uint2(0, 0);
-            if (L.xv[nt]) {
-                x0 = lds64(xb[nt] + off);        // sub-block 2c   (low nibbles)
-                x1 = lds64(xb[nt] + 64 + off);   // sub-block 2c+1 (high nibbles)
-            }
-            mma16816(c1[nt], a_le, b_le, a_lo, b_lo, x0.x, x0.y);
-            mma16816(c1h[nt], a_he, b_he, a_ho, b_ho, x1.x, x1.y);
-        }
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        uint2 xm = make_uint2(0, 0);
-        if (L.xv[nt]) xm = lds64(L.x[nt] + xu * ncols * PANEL_BYTES + 512 + 8 * L.c);
-        mma16816(c2[nt], sa.mins, sb.mins, sa.mins, sb.mins, xm.x, xm.y);
-        acc[nt][0] += sa.d * (c1[nt][0] + c1h[nt][0]) - sa.dmin32 * c2[nt][0];
-        acc[nt][1] += sa.d * (c1[nt][1] + c1h[nt][1]) - sa.dmin32 * c2[nt][1];
-        acc[nt][2] += sb.d * (c1[nt][2] + c1h[nt][2]) - sb.dmin32 * c2[nt][2];
-        acc[nt][3] += sb.d * (c1[nt][3] + c1h[nt][3]) - sb.dmin32 * c2[nt][3];
-    }
-}
 
 // ---------------------------------------------------------------------------
 // Q4_K, one or two tokens, int8 tensor-core path
@@ -323,24 +214,24 @@ __device__ __forceinline__ void unit_q4k_i8(const Lane &L, const I8Cols X, int u
         acc[1] += worth.y * (da * (float)(ilo[0][1] + (ihi[0][1] >> 4)) - dma * (float)m1);
         acc[2] += worth.x * (db * (float)(ilo[0][2] + (ihi[0][2] >> 4)) - dmb * (float)m2);
         acc[3] += worth.y * (db * (float)(ilo[0][3] + (ihi[0][3] >> 4)) - dmb * (float)m3);
-        return;
-    }
+    } else {
 #pragma unroll
-    for (int p = 0; p < NTILE; p++)
+        for (int p = 0; p < NTILE; p++)
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            uint4 t = make_uint4(0, 0, 0, 0);
-            float worth = 0.0f;
-            if (2 * L.c + i < X.tile_cols) {
-                const int col = p * X.tile_stride + 2 * L.c + i;
-                t = lds128(blob + 256 * X.nc + col * 16);
-                worth = lds32f(blob + 272 * X.nc + 4 * col);
+            for (int i = 0; i < 2; i++) {
+                uint4 t = make_uint4(0, 0, 0, 0);
+                float worth = 0.0f;
+                if (2 * L.c + i < X.tile_cols) {
+                    const int col = p * X.tile_stride + 2 * L.c + i;
+                    t = lds128(blob + 256 * X.nc + col * 16);
+                    worth = lds32f(blob + 272 * X.nc + 4 * col);
+                }
+                const int m_a = (dp4a_us(ma[1], t.y, dp4a_us(ma[0], t.x, 0)) << 7) + dp4a_us(ma[1], t.w, dp4a_us(ma[0], t.z, 0));
+                const int m_b = (dp4a_us(mb[1], t.y, dp4a_us(mb[0], t.x, 0)) << 7) + dp4a_us(mb[1], t.w, dp4a_us(mb[0], t.z, 0));
+                acc[i] += worth * (da * (float)(ilo[p][i] + (ihi[p][i] >> 4)) - dma * (float)m_a);
+                acc[2 + i] += worth * (db * (float)(ilo[p][2 + i] + (ihi[p][2 + i] >> 4)) - dmb * (float)m_b);
             }
-            const int m_a = (dp4a_us(ma[1], t.y, dp4a_us(ma[0], t.x, 0)) << 7) + dp4a_us(ma[1], t.w, dp4a_us(ma[0], t.z, 0));
-            const int m_b = (dp4a_us(mb[1], t.y, dp4a_us(mb[0], t.x, 0)) << 7) + dp4a_us(mb[1], t.w, dp4a_us(mb[0], t.z, 0));
-            acc[i] += worth * (da * (float)(ilo[p][i] + (ihi[p][i] >> 4)) - dma * (float)m_a);
-            acc[2 + i] += worth * (db * (float)(ilo[p][2 + i] + (ihi[p][2 + i] >> 4)) - dmb * (float)m_b);
-        }
+    }
 }
 
 // Q8_0.  A 32-weight block is one MMA (s8 x s8); its f16 scale weighs the block's
@@ -461,122 +352,6 @@ __device__ __forceinline__ void unit_q6k_i8(const Lane &L, const I8Cols X, int u
 }
 
 // ---------------------------------------------------------------------------
-// Q8_0: one unit = eight 32-weight blocks per row (256 quant bytes, 8 scales)
-// ---------------------------------------------------------------------------
-// Lane c owns bytes [8c, 8c+8) of each block: two words, one per MMA.
-__device__ __forceinline__ void s8x4_to_h2(uint32_t w, uint32_t &p01, uint32_t &p23) {
-    w ^= 0x80808080u;                                    // q + 128, unsigned
-    p01 = hsub2(prmt(w, 0x64646464u, 0x5140u), H2_1152); // 1024 + 128 + q - 1152
-    p23 = hsub2(prmt(w, 0x64646464u, 0x5342u), H2_1152);
-}
-
-template <int NT>
-__device__ __forceinline__ void unit_q8_0(const Lane &L, int ul, int xu, int ncols, float (&acc)[NT][4]) {
-    const uint32_t qa = L.row_a + ul * 256 + 8 * L.c, qb = L.row_b + ul * 256 + 8 * L.c;
-    const uint4 sa = lds128(L.srow_a + ul * 16), sb = lds128(L.srow_b + ul * 16);
-    const uint32_t sca[4] = {sa.x, sa.y, sa.z, sa.w}, scb[4] = {sb.x, sb.y, sb.z, sb.w};
-    uint32_t xb[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 16 * L.c;
-#pragma unroll
-    for (int blk = 0; blk < 8; blk++) {
-        const uint2 wa = lds64(qa + 32 * blk), wb = lds64(qb + 32 * blk);
-        uint32_t a0, a2, a1, a3, e0, e2, e1, e3;
-        s8x4_to_h2(wa.x, a0, a2);
-        s8x4_to_h2(wb.x, a1, a3);
-        s8x4_to_h2(wa.y, e0, e2);
-        s8x4_to_h2(wb.y, e1, e3);
-        const float da = (blk & 1) ? h2f_hi(sca[blk >> 1]) : h2f_lo(sca[blk >> 1]);
-        const float db = (blk & 1) ? h2f_hi(scb[blk >> 1]) : h2f_lo(scb[blk >> 1]);
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (L.xv[nt]) xv = lds128(xb[nt] + 64 * blk);
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            mma16816(c, a0, a1, a2, a3, xv.x, xv.y);
-            mma16816(c, e0, e1, e2, e3, xv.z, xv.w);
-            acc[nt][0] += da * c[0];
-            acc[nt][1] += da * c[1];
-            acc[nt][2] += db * c[2];
-            acc[nt][3] += db * c[3];
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------
-// Q6_K: one unit = one 208-byte device block per row (+ its f16 d)
-// ---------------------------------------------------------------------------
-// One MMA per 16-weight scale group: lane c holds weights 4c..4c+3 of the
-// group.  For (half, lh) the lane reads two ql words and one qh word and
-// makes the four groups k = 0..3 from them.
-__device__ __forceinline__ float s8_byte_to_f32(uint32_t word_xor80, int b) {
-    // 0x4B000000 | (s + 128) is 8388608 + s + 128 as a float
-    return __uint_as_float(prmt(word_xor80, 0x4B000000u, 0x7540u + b)) - 8388736.0f;
-}
-
-template <int NT>
-__device__ __forceinline__ void unit_q6k(const Lane &L, int ul, int xu, int ncols, int d_index, float (&acc)[NT][4]) {
-    const uint32_t ba = L.row_a + ul * 208, bb = L.row_b + ul * 208;
-    uint4 ta = lds128(ba + 192), tb = lds128(bb + 192);
-    const uint32_t sca[4] = {ta.x ^ 0x80808080u, ta.y ^ 0x80808080u, ta.z ^ 0x80808080u, ta.w ^ 0x80808080u};
-    const uint32_t scb[4] = {tb.x ^ 0x80808080u, tb.y ^ 0x80808080u, tb.z ^ 0x80808080u, tb.w ^ 0x80808080u};
-    const float da = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_a + 2 * d_index)));
-    const float db = __half2float(__ushort_as_half((uint16_t)lds16(L.srow_b + 2 * d_index)));
-    float part[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) part[nt][i] = 0.0f;
-    uint32_t xb[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) xb[nt] = L.x[nt] + xu * ncols * PANEL_BYTES + 8 * L.c;
-
-#pragma unroll
-    for (int hf = 0; hf < 2; hf++)
-#pragma unroll
-        for (int lh = 0; lh < 2; lh++) {
-            const uint32_t o = 64 * hf + 16 * lh + 4 * L.c, oh = 128 + 32 * hf + 16 * lh + 4 * L.c;
-            const uint32_t la0 = lds32(ba + o), la1 = lds32(ba + o + 32), hha = lds32(ba + oh);
-            const uint32_t lb0 = lds32(bb + o), lb1 = lds32(bb + o + 32), hhb = lds32(bb + oh);
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const uint32_t la = (k & 1) ? la1 : la0, lb = (k & 1) ? lb1 : lb0;
-                const uint32_t lowa = ((k >> 1) ? (la >> 4) : la) & 0x0f0f0f0fu;
-                const uint32_t lowb = ((k >> 1) ? (lb >> 4) : lb) & 0x0f0f0f0fu;
-                const uint32_t ha = (k == 0 ? hha << 4 : k == 1 ? hha << 2 : k == 2 ? hha : hha >> 2) & 0x30303030u;
-                const uint32_t hb = (k == 0 ? hhb << 4 : k == 1 ? hhb << 2 : k == 2 ? hhb : hhb >> 2) & 0x30303030u;
-                const uint32_t qa = lowa | ha, qb = lowb | hb;   // bytes: q + 32
-                const uint32_t a0 = hsub2(prmt(qa, 0x64646464u, 0x5140u), H2_1056);
-                const uint32_t a2 = hsub2(prmt(qa, 0x64646464u, 0x5342u), H2_1056);
-                const uint32_t a1 = hsub2(prmt(qb, 0x64646464u, 0x5140u), H2_1056);
-                const uint32_t a3 = hsub2(prmt(qb, 0x64646464u, 0x5342u), H2_1056);
-                const int sidx = 8 * hf + 2 * k + lh;
-                const float fa = s8_byte_to_f32(sca[sidx >> 2], sidx & 3);
-                const float fb = s8_byte_to_f32(scb[sidx >> 2], sidx & 3);
-                const uint32_t koff = 2 * (128 * hf + 32 * k + 16 * lh);
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    uint2 xv = make_uint2(0, 0);
-                    if (L.xv[nt]) xv = lds64(xb[nt] + koff);
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    mma16816(c, a0, a1, a2, a3, xv.x, xv.y);
-                    part[nt][0] += fa * c[0];
-                    part[nt][1] += fa * c[1];
-                    part[nt][2] += fb * c[2];
-                    part[nt][3] += fb * c[3];
-                }
-            }
-        }
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        acc[nt][0] += da * part[nt][0];
-        acc[nt][1] += da * part[nt][1];
-        acc[nt][2] += db * part[nt][2];
-        acc[nt][3] += db * part[nt][3];
-    }
-}
-
-// ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float silu_mul(float g, float u) {
@@ -606,11 +381,9 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
     constexpr int BASE = base_of(FMT);
-    constexpr bool I8 = is_i8(FMT);
     constexpr bool HAS_SCALES = BASE == Q6_K || BASE == Q8_0;   // scales kept apart from the quants
-    // accumulator groups per lane: the int8 routines sum a token's planes as they go
-    constexpr int NACC = I8 ? 1 : NT;
-    constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * NACC * 4 * 32 : 0;
+    // a lane's four accumulators (two rows by two columns); the unit routines sum a token's planes as they go
+    constexpr int RED_FLOATS = KS > 1 ? 2 * KS * RT * 4 * 32 : 0;
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);   // full[MAX_STAGES], empty[MAX_STAGES], panels
@@ -696,14 +469,13 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
                     griddep_wait();
                     waited = true;
                     if (a.x_resident && lane == 0) {
-                        // the launch's panels are one contiguous run: [units][ncols][PANEL_BYTES]; col0 = 0 for int8 panels
+                        // the launch's panels are one contiguous run
                         mbar_expect_tx(xbar, a.xres_bytes);
-                        bulk_g2s(smem_u32(xres), a.panels + (size_t)a.col0 * PANEL_BYTES, a.xres_bytes, xbar);
+                        bulk_g2s(smem_u32(xres), a.panels, a.xres_bytes, xbar);
                     }
                 }
                 for (int u = lane; u < kcc && !a.x_resident; u += 32)
-                    bulk_g2s(st + a.x_off + u * xbytes,
-                             a.panels + (size_t)(u0 + u) * a.xsrc_stride + (size_t)a.col0 * PANEL_BYTES, xbytes, bar);
+                    bulk_g2s(st + a.x_off + u * xbytes, a.panels + (size_t)(u0 + u) * a.xsrc_stride, xbytes, bar);
             }
         }
         // Drain: the copies this warp issued must have landed before the CTA's
@@ -730,13 +502,8 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     // apart to cover all banks, so lanes g = 0..3 take rows 0, 2, 4, 6 of the
     // eight and g = 4..7 rows 1, 3, 5, 7.
     const int grow = (FMT == Q4K_I8 || FMT == Q8_I8) ? ((L.g & 3) * 2 + (L.g >> 2)) : L.g;
-#pragma unroll
-    for (int nt = 0; nt < 2; nt++) L.xv[nt] = !I8 && nt < NT && (nt * 8 + L.g) < a.ncols;
     // the digit planes' columns: one tile of 4n columns (one and two tokens), or a tile of n columns per plane
     const I8Cols X = {a.ncols, NT == 1 ? 0 : a.n_tokens, NT == 1 ? a.ncols : a.n_tokens};
-    uint32_t xo[4];
-#pragma unroll
-    for (int v = 0; v < 4; v++) xo[v] = 8 * (v ^ L.c);
 
     uint32_t it = 0;
     int tile_parity = 0;
@@ -746,11 +513,7 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
     float gate[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // SwiGLU in one launch: the gate's sums of this lane, kept until up's arrive
     for (int tile = blockIdx.x; tile < a.n_tiles; tile += gridDim.x)
     for (int mat = 0; mat < n_mats; mat++, tile_parity ^= 1) {
-        float acc[NACC][4];
-#pragma unroll
-        for (int nt = 0; nt < NACC; nt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[nt][i] = 0.0f;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
         for (int ch = 0; ch < n_chunks; ch++, it++) {
             const int s = it % S;
@@ -763,18 +526,13 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
             L.srow_a = st + a.s_off + (rt * 16 + grow) * a.s_stride;
             L.srow_b = L.srow_a + 8 * a.s_stride;
             L.xbase = a.x_resident ? smem_u32(xres) : st + a.x_off;
-#pragma unroll
-            for (int nt = 0; nt < NACC; nt++) L.x[nt] = L.xbase + (nt * 8 + L.g) * PANEL_BYTES;
             const int xu0 = a.x_resident ? u0 : 0;
             // units are dealt to the K-split warps round-robin over the whole row,
             // so every warp gets the same number whatever the chunking
             for (int ul = (ks + KS - u0 % KS) % KS; ul < kcc; ul += KS) {
-                if constexpr (FMT == Q4K_I8) unit_q4k_i8<NT>(L, X, ul, xu0 + ul, acc[0]);
-                else if constexpr (FMT == Q8_I8) unit_q8_i8<NT>(L, X, ul, xu0 + ul, acc[0]);
-                else if constexpr (FMT == Q6K_I8) unit_q6k_i8<NT>(L, X, ul, xu0 + ul, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc[0]);
-                else if constexpr (FMT == Q4_K) unit_q4k<NT>(L, ul, xu0 + ul, a.ncols, xo, acc);
-                else if constexpr (FMT == Q8_0) unit_q8_0<NT>(L, ul, xu0 + ul, a.ncols, acc);
-                else unit_q6k<NT>(L, ul, xu0 + ul, a.ncols, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc);
+                if constexpr (FMT == Q4K_I8) unit_q4k_i8<NT>(L, X, ul, xu0 + ul, acc);
+                else if constexpr (FMT == Q8_I8) unit_q8_i8<NT>(L, X, ul, xu0 + ul, acc);
+                else unit_q6k_i8<NT>(L, X, ul, xu0 + ul, (a.whole_rows ? u0 : (u0 & 7)) + ul, acc);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
@@ -782,22 +540,18 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
 
         // ---- sum the K-split warps of this row tile, in warp order ----
         if (KS > 1) {
-            float *buf = red + tile_parity * (KS * RT * NACC * 128);
+            float *buf = red + tile_parity * (KS * RT * 128);
 #pragma unroll
-            for (int nt = 0; nt < NACC; nt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) buf[(((ks * RT + rt) * NACC + nt) * 4 + i) * 32 + lane] = acc[nt][i];
+            for (int i = 0; i < 4; i++) buf[((ks * RT + rt) * 4 + i) * 32 + lane] = acc[i];
             asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
             if (ks != 0) continue;
 #pragma unroll
-            for (int nt = 0; nt < NACC; nt++)
+            for (int i = 0; i < 4; i++) {
+                float v = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float v = 0.0f;
-#pragma unroll
-                    for (int k2 = 0; k2 < KS; k2++) v += buf[(((k2 * RT + rt) * NACC + nt) * 4 + i) * 32 + lane];
-                    acc[nt][i] = v;
-                }
+                for (int k2 = 0; k2 < KS; k2++) v += buf[((k2 * RT + rt) * 4 + i) * 32 + lane];
+                acc[i] = v;
+            }
         }
 
         if (!out_ready) {   // the kernel ahead may still be writing `out` or `aux`
@@ -806,9 +560,9 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
         }
         // ---- epilogue: lane (g, c) holds rows g, g+8 and columns 2c, 2c+1 of each group ----
         const size_t r0 = (size_t)tile * R + rt * 16 + grow, r1 = r0 + 8;
-        if constexpr (I8 && NT == 1) {
+        if constexpr (NT == 1) {
             // a token's four planes are columns 4t..4t+3: lanes c = 2t, 2t+1
-            float va = acc[0][0] + acc[0][1], vb = acc[0][2] + acc[0][3];
+            float va = acc[0] + acc[1], vb = acc[2] + acc[3];
             va += __shfl_xor_sync(0xffffffffu, va, 1);
             vb += __shfl_xor_sync(0xffffffffu, vb, 1);
             const int t = L.c >> 1;
@@ -819,36 +573,20 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
                 emit(a, t, r0, n_mats == 2 ? silu_mul(gate[0], va) : va);
                 emit(a, t, r1, n_mats == 2 ? silu_mul(gate[2], vb) : vb);
             }
-            continue;
-        } else if constexpr (I8) {
+        } else {
             // a tile per plane, summed by the unit routine: this lane holds tokens 2c and 2c+1 of its two rows
             if (n_mats == 2 && mat == 0) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) gate[i] = acc[0][i];
+                for (int i = 0; i < 4; i++) gate[i] = acc[i];
             } else {
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
                     const int t = 2 * L.c + i;
                     if (t < a.n_tokens) {
-                        emit(a, t, r0, n_mats == 2 ? silu_mul(gate[i], acc[0][i]) : acc[0][i]);
-                        emit(a, t, r1, n_mats == 2 ? silu_mul(gate[2 + i], acc[0][2 + i]) : acc[0][2 + i]);
+                        emit(a, t, r0, n_mats == 2 ? silu_mul(gate[i], acc[i]) : acc[i]);
+                        emit(a, t, r1, n_mats == 2 ? silu_mul(gate[2 + i], acc[2 + i]) : acc[2 + i]);
                     }
                 }
-            }
-            continue;
-        }
-#pragma unroll
-        for (int nt = 0; nt < NACC; nt++) {
-            if (a.split) {
-                const int t = nt * 4 + L.c;   // columns 2t (hi), 2t+1 (lo)
-                if (t < a.n_tokens) {
-                    emit(a, t, r0, acc[nt][0] + acc[nt][1]);
-                    emit(a, t, r1, acc[nt][2] + acc[nt][3]);
-                }
-            } else {
-                const int t = nt * 8 + 2 * L.c;
-                if (t < a.n_tokens) { emit(a, t, r0, acc[nt][0]); emit(a, t, r1, acc[nt][2]); }
-                if (t + 1 < a.n_tokens) { emit(a, t + 1, r0, acc[nt][1]); emit(a, t + 1, r1, acc[nt][3]); }
             }
         }
     }
@@ -857,28 +595,23 @@ __global__ void __launch_bounds__((RT * KS + 1) * 32, 1) dwim_smallm_kernel(cons
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-int gemv_max_tokens(int split) { return split ? 8 : 16; }
-
 template <int FMT, int NT, int RT, int KS>
 static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int R = RT * 16;
     constexpr int UNIT_Q = Traits<FMT>::UNIT_Q;
     constexpr int BASE = base_of(FMT);
-    constexpr int NACC = is_i8(FMT) ? 1 : NT;
-    constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * NACC * 4 * 32 * 4 + 127) & ~127) : 0;
+    constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * 4 * 32 * 4 + 127) & ~127) : 0;
     constexpr int SMEM_LIMIT = 227 * 1024;
     // CTAs per SM: two smaller CTAs overlap one's fill and drain with the other's steady state
     const int cps = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
     const int SMEM_MAX = cps > 1 ? (228 * 1024) / cps - 1024 : SMEM_LIMIT;
     const int fixed = 256 + RED_BYTES;
-    // Panels stay resident when the launch covers the whole panel array (one
-    // contiguous run) and it is small next to the ring.
+    // The digit planes stay resident in shared memory when they are small next to the ring, or
+    // when two stages of whole rows still fit beside them (the planes of five tokens of a
+    // 5120-wide row are 83 KB).
     const int xall = a.units * a.xunit;
-    const bool covers = a.col0 == 0 && a.ncols == a.ncols_total;
-    // ... and next to two stages of whole rows where those fit beside it (the int8 planes of five
-    // tokens of a 5120-wide row are 83 KB)
     const int two_whole = 2 * (int)((R * (a.w.qpitch + a.w.srow * 2) + 127) & ~127);
-    a.x_resident = covers && (xall <= 80 * 1024 || fixed + xall + two_whole <= SMEM_MAX);
+    a.x_resident = xall <= 80 * 1024 || fixed + xall + two_whole <= SMEM_MAX;
     a.xres_bytes = a.x_resident ? xall : 0;
     // K per stage.  Whole rows when two stages of them fit: the tile is then one
     // contiguous run of HBM and moves with a single bulk copy (issuing a bulk
@@ -937,59 +670,20 @@ template <int FMT, int NT>
 static int launch_shape(dwim_b200_ctx *ctx, GemvArgs &a) {
     // Row tiles per CTA (RT) x K-split warps per row tile (KS).  KS should
     // divide the row's units so that every warp gets the same share.
-    // Measured on B200 at the model's shapes: Q4_K runs best with 32-row tiles
-    // when there are rows enough for two tiles per SM, the wider formats with
-    // 16-row tiles (their stages are larger); eight K-split warps throughout.
-    // Three to eight tokens through the int8 planes (NT = 3) keep 16-row tiles:
-    // their planes then stay resident beside two stages of whole rows.
-    const size_t tiles32 = (a.w.rows + 31) / 32;
-    const bool q4 = base_of(FMT) == Q4_K;
-    if constexpr (is_i8(FMT) && NT == 3) {
-        return launch<FMT, NT, 1, 8>(ctx, a);
-    } else if constexpr (base_of(FMT) == Q4_K && NT == 2) {
-        // 17+ warps of the two-group f16 kernel would spill registers: four K-split warps there
-        if (q4 && tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 4>(ctx, a);
-        return launch<FMT, NT, 1, 8>(ctx, a);
-    } else if constexpr (base_of(FMT) == Q4_K) {
-        if (q4 && tiles32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 8>(ctx, a);
-        return launch<FMT, NT, 1, 8>(ctx, a);
-    } else {
-        return launch<FMT, NT, 1, 8>(ctx, a);
+    // Measured on B200 at the model's shapes: one and two tokens of Q4_K run
+    // best with 32-row tiles when there are rows enough for two tiles per SM,
+    // the wider formats with 16-row tiles (their stages are larger); eight
+    // K-split warps throughout.  Three to eight tokens (NT = 3) keep 16-row
+    // tiles: their planes then stay resident beside two stages of whole rows.
+    if constexpr (FMT == Q4K_I8 && NT == 1) {
+        if ((a.w.rows + 31) / 32 >= (size_t)2 * ctx->sm_count) return launch<FMT, NT, 2, 8>(ctx, a);
     }
+    return launch<FMT, NT, 1, 8>(ctx, a);
 }
 
-int gemv_small(dwim_b200_ctx *ctx, const WeightView &w, const __half *panels, int ncols_total, int col0, int n_tokens,
-               size_t t0, int split, const OutSpec &out, const float *aux, int epilogue) {
-    if (w.rows == 0 || n_tokens == 0) return 0;
-    GemvArgs a{};
-    a.w = w;
-    a.panels = reinterpret_cast<const uint8_t *>(panels);
-    a.ncols_total = ncols_total;
-    a.col0 = col0;
-    a.ncols = n_tokens * (split ? 2 : 1);
-    a.split = split;
-    a.n_tokens = n_tokens;
-    a.t0 = t0;
-    a.out = out;
-    a.aux = aux;
-    a.epi = epilogue;
-    a.units = (int)((w.cols + 255) / 256);
-    a.xunit = a.ncols * PANEL_BYTES;
-    a.xsrc_stride = ncols_total * PANEL_BYTES;
-    a.status = ctx->status;
-    if (a.ncols > 16) return fail(ctx, DWIM_B200_EINVAL, "small-M kernel: %d columns", a.ncols);
-    const bool two = a.ncols > 8;
-    switch (w.fmt) {
-    case Q4_K: return two ? launch_shape<Q4_K, 2>(ctx, a) : launch_shape<Q4_K, 1>(ctx, a);
-    case Q6_K: return two ? launch_shape<Q6_K, 2>(ctx, a) : launch_shape<Q6_K, 1>(ctx, a);
-    case Q8_0: return two ? launch_shape<Q8_0, 2>(ctx, a) : launch_shape<Q8_0, 1>(ctx, a);
-    default: return fail(ctx, DWIM_B200_EFORMAT, "unknown weight format %d", w.fmt);
-    }
-}
-
-// Whether a product of n tokens takes the int8 routines: up to eight tokens of
-// any format.  (The f16 routines remain for nine to sixteen tokens, and above
-// that for the formats the tensor-core kernel does not take.)
+// Whether the small-M kernel takes a product of n tokens: up to eight tokens of
+// any format (Q8_0 rows need not be whole 256-weight units: their scale rows are
+// padded with zeros).
 bool gemv_takes_i8(const WeightView &w, size_t n) {
     if (n < 1 || n > I8_MAX_TOKENS) return false;
     return w.fmt == Q8_0 || ((w.fmt == Q4_K || w.fmt == Q6_K) && w.cols % 256 == 0);
@@ -997,19 +691,17 @@ bool gemv_takes_i8(const WeightView &w, size_t n) {
 
 // Up to eight tokens through the int8 routines; `panels` from build_panels_i8.
 // `up`, when given, makes it the SwiGLU of the pair (w = gate) in one launch.
-int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, const OutSpec &out, const float *aux,
-                  int epilogue, const WeightView *up) {
+int gemv_small_i8(dwim_b200_ctx *ctx, const WeightView &w, const uint8_t *panels, int n_tokens, size_t t0, const OutSpec &out,
+                  const float *aux, int epilogue, const WeightView *up) {
     if (w.rows == 0 || n_tokens == 0) return 0;
     if (!gemv_takes_i8(w, (size_t)n_tokens))
         return fail(ctx, DWIM_B200_EINVAL, "int8 small-M kernel: format %d, %d tokens", w.fmt, n_tokens);
     GemvArgs a{};
     a.w = w;
     a.panels = panels;
-    a.ncols_total = a.ncols = i8_planes(n_tokens) * n_tokens;
-    a.col0 = 0;
-    a.split = 0;
+    a.ncols = i8_planes(n_tokens) * n_tokens;
     a.n_tokens = n_tokens;
-    a.t0 = 0;
+    a.t0 = t0;
     a.out = out;
     a.aux = aux;
     a.epi = epilogue;

@@ -1,43 +1,15 @@
-// Activation prologue: f32 activations -> the 16-bit operand forms the matmul
+// Activation prologue: f32 activations -> the operand forms the matmul
 // kernels read.  The reference does the same with its f16 shadow buffers
 // (`halves`, gpu/cuda/mod.rs:313-384; to_f16.cu:6-18): convert once, reuse for
-// every matmul that takes the same input.
-//
-// Panels (small-M kernel).  K is cut in units of 256 weights.  For unit u and
-// column c the panel is PANEL_STRIDE = 272 halves:
-//     [0, 256)   the column's activations for k in [256u, 256u+256)
-//     [256, 272) per-32-weight means of those activations (Q4_K only),
-//                each as a hi and a lo half: entry 4p+{0,1} = hi of sub-blocks
-//                2p, 2p+1; entry 4p+{2,3} = their lo parts
-// laid out [unit][column][272].  A "column" is one token (single mode) or one
-// half of a token: with split = 1 token t owns columns 2t (x rounded to f16)
-// and 2t+1 (the rounding's remainder, again as f16), so that hi + lo carries
-// 22 bits of the f32 activation and the tensor-core products stay exact.
-//
-// Order of k inside [0, 256):
-//   natural (Q8_0, Q6_K): position = k.
-//   Q4_K: the kernel's lane c (0..3) owns the 64 weights [64c, 64c+64) and
-//   unpacks bytes (0, 2) and (1, 3) of each 32-bit word together, so each run
-//   of four k is stored in the order (0, 2, 1, 3); and the 8-byte runs are
-//   XOR-swizzled by c so that the four lanes of a row hit different banks:
-//     run  = 16c + 8*nib + (j ^ c)      k = 64c + 32*nib + 4j + e
-//     position = 4*run + {0,2,1,3}[e]
+// every matmul that takes the same input.  Two forms: int8 digit planes per
+// 256-wide unit for the small-M kernel (up to eight tokens), and f16 rows with
+// sub-block means and a scale per token for the tensor-core kernels; either
+// can be written by the same launch that applies the RMS norm in front of the
+// product (rmsnorm.cu:11-58).
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace dwim {
-
-size_t panel_bytes(size_t cols, int ncols) {
-    size_t units = (cols + 255) / 256;
-    return units * (size_t)ncols * PANEL_STRIDE * sizeof(__half);
-}
-
-__device__ __forceinline__ int panel_pos_q4k(int k) {
-    int c = k >> 6, nib = (k >> 5) & 1, j = (k >> 2) & 7, e = k & 3;
-    int run = 16 * c + 8 * nib + (j ^ c);
-    int pe = ((e & 1) << 1) | (e >> 1);   // 0,1,2,3 -> 0,2,1,3
-    return 4 * run + pe;
-}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -45,69 +17,6 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// grid (units, tokens), 256 threads: thread k converts x[t][256u + k].
-template <bool Q4K>
-__global__ void __launch_bounds__(256) panel_kernel(const float *__restrict__ x, size_t cols, int ncols, int split,
-                                                    __half *__restrict__ panels) {
-    // as panel_i8_kernel: let the next small-M launch begin, wait for the kernel ahead
-    griddep_launch();
-    griddep_wait();
-    int u = blockIdx.x, t = blockIdx.y, k = threadIdx.x;
-    size_t kk = (size_t)u * 256 + k;
-    float v = kk < cols ? x[(size_t)t * cols + kk] : 0.0f;
-    __half hi = to_f16_clamped(v);
-    float rem = v - __half2float(hi);
-    __half lo = to_f16_clamped(rem);
-    int pos = Q4K ? panel_pos_q4k(k) : k;
-    int col = split ? 2 * t : t;
-    __half *p = panels + ((size_t)u * ncols + col) * PANEL_STRIDE;
-    p[pos] = hi;
-    if (split) p[PANEL_STRIDE + pos] = lo;
-    // means of the 32 activations of each sub-block (a warp = a sub-block)
-    float mh = 0.0f, ml = 0.0f;
-    if (Q4K) {
-        mh = warp_sum(__half2float(hi)) * (1.0f / 32.0f);
-        ml = warp_sum(__half2float(lo)) * (1.0f / 32.0f);
-    }
-    if ((k & 31) == 0) {
-        int j = k >> 5;
-        int e = 256 + 4 * (j >> 1) + (j & 1);
-        __half a = to_f16_clamped(mh);
-        p[e] = a;
-        p[e + 2] = to_f16_clamped(mh - __half2float(a));
-        if (split) {
-            __half b = to_f16_clamped(ml);
-            p[PANEL_STRIDE + e] = b;
-            p[PANEL_STRIDE + e + 2] = to_f16_clamped(ml - __half2float(b));
-        }
-    }
-}
-
-int build_panels(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols, int kind, int split, __half *panels) {
-    if (n == 0 || cols == 0) return 0;
-    size_t units = (cols + 255) / 256;
-    if (n > 65535) return fail(ctx, DWIM_B200_EINVAL, "too many tokens for one panel build: %zu", n);
-    dim3 grid((unsigned)units, (unsigned)n);
-    int ncols = (int)n * (split ? 2 : 1);
-    if (kind == SHADOW_PANEL_Q4K)
-        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, panel_kernel<true>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
-    else
-        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, panel_kernel<false>, grid, dim3(256), 0, ctx->stream, x, cols, ncols, split, panels));
-    DWIM_LAUNCHED(ctx);
-    return 0;
-}
-
-// Operands of the tensor-core GEMM (Q4_K).  Two arrays, one row per column
-// (a column is a token, or with split = 1 a token's hi or lo half, columns 2t
-// and 2t+1):
-//   x16   [ncols][K] f16      the activations; each run of four k is stored in
-//                             the order (0, 2, 1, 3), the order the dequantizer
-//                             produces weights in (it unpacks bytes 0,2 and 1,3
-//                             of a word together)
-//   means [ncols][K/256][16]  per 32-weight sub-block the mean of the column's
-//                             f16 values, as a hi half (entries 0-7) and the
-//                             remainder (entries 8-15): the operand the
-//                             sub-block minimums are multiplied with
 // ---- int8 digit planes (the small-M kernel's int8 routines) --------------------------------
 // A unit's 256 activations of a token share one exponent e (|x| < 2^e for all of
 // them) and become fixed point with P signed base-256 digits, Y = rint(x * 2^(8P-2-e))

@@ -47,29 +47,18 @@ extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwi
     if (!out || !x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: null pointer");
     if (out == x) return fail(ctx, DWIM_B200_EINVAL, "matmul_static: output aliases input");
     if (v.fmt == BF16) return fail(ctx, DWIM_B200_EFORMAT, "matmul_static: bf16 weights need no scratch: use matmul");
-    if (gemv_takes_i8(v, n)) {
-        // up to eight tokens: the int8 digit-plane operand, as dwim_b200_matmul
-        const size_t need = panel_i8_bytes(v.cols, n);
-        if (need > STATIC_SCRATCH_BYTES)
-            return fail(ctx, DWIM_B200_EINVAL,
-                        "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
-                        v.cols, need, STATIC_SCRATCH_BYTES);
-        void *scratch = ctx->static_scratch;
-        int rc = build_panels_i8(ctx, x, n, v.cols, (uint8_t *)scratch);
-        if (rc) return rc;
-        return gemv_small_i8(ctx, v, (const uint8_t *)scratch, (int)n, out_local(out, v.rows), nullptr, EPI_STORE);
-    }
-    const int split = 1;                                  // f32 activations: value + remainder columns
-    if (n > (size_t)gemv_max_tokens(split))
-        return fail(ctx, DWIM_B200_EINVAL, "matmul_static: %zu tokens, at most %d", n, gemv_max_tokens(split));
-    const int ncols = (int)n * 2;
-    const size_t need = panel_bytes(v.cols, ncols);
+    if (n > (size_t)I8_MAX_TOKENS)
+        return fail(ctx, DWIM_B200_EINVAL, "matmul_static: %zu tokens, at most %d", n, I8_MAX_TOKENS);
+    if (!gemv_takes_i8(v, n))
+        return fail(ctx, DWIM_B200_EFORMAT, "matmul_static: no small-M kernel takes format %d with %zu columns", v.fmt, v.cols);
+    // the int8 digit-plane operand, as dwim_b200_matmul builds it for up to eight tokens
+    const size_t need = panel_i8_bytes(v.cols, n);
     if (need > STATIC_SCRATCH_BYTES)
         return fail(ctx, DWIM_B200_EINVAL,
                     "matmul_static: %zu tokens of %zu columns need %zu bytes of scratch, the fixed array holds %zu", n,
                     v.cols, need, STATIC_SCRATCH_BYTES);
     void *scratch = ctx->static_scratch;
-    int rc = build_panels(ctx, x, n, v.cols, v.fmt == Q4_K ? SHADOW_PANEL_Q4K : SHADOW_PANEL_NATURAL, split, (__half *)scratch);
+    int rc = build_panels_i8(ctx, x, n, v.cols, (uint8_t *)scratch);
     if (rc) return rc;
-    return gemv_small(ctx, v, (const __half *)scratch, ncols, 0, (int)n, 0, split, out_local(out, v.rows), nullptr, EPI_STORE);
+    return gemv_small_i8(ctx, v, (const uint8_t *)scratch, (int)n, 0, out_local(out, v.rows), nullptr, EPI_STORE);
 }
