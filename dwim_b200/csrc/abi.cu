@@ -457,8 +457,9 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
     // Up to eight tokens: the small-M kernel's int8 routines.  Above: the tensor-core kernels -- Q4_K
     // from nine tokens on (measured on B200 at [17408, 5120]: 26 us at nine to sixteen tokens, against
     // 57 us for sixteen through two small-M launches); Q6_K and Q8_0, whose dense path first decodes
-    // the matrix, from 33 on, and in groups of eight through the small-M kernel below that.
-    const bool dense = gemm_supports(v) && n > (v.fmt == Q4_K ? (size_t)I8_MAX_TOKENS : (size_t)32);
+    // the matrix (3.7 ms for the [151936, 5120] head at 64 tokens, against eight small-M launches of
+    // 0.31 ms), from 65 on, and in groups of eight through the small-M kernel below that.
+    const bool dense = gemm_supports(v) && n > (v.fmt == Q4_K ? (size_t)I8_MAX_TOKENS : (size_t)64);
     if (dense) {
         // bf16 activations are exact in one f16 column; f32 ones travel as two
         // (value and rounding remainder), summed again in the epilogue.

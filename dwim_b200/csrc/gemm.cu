@@ -758,22 +758,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
 }
 
 // A row of W decoded, scaled by its own power of two and written as two f16 terms, each run of
-// four k in the order (0, 2, 1, 3) the activations' operand is stored in.  One block per row.
+// four k in the order (0, 2, 1, 3) the activations' operand is stored in.  One block per row; the
+// decoded row waits in shared memory (cols floats) while its largest magnitude is found.
 __global__ void __launch_bounds__(256) dequant_pair_kernel(const WeightView w, size_t row0, size_t cols, __half *__restrict__ hi,
                                                            __half *__restrict__ lo, float *__restrict__ row_scale) {
     griddep_launch();
     griddep_wait();   // the kernel ahead may still read the panel
+    extern __shared__ __align__(16) float wrow[];
     __shared__ float part[8];
     const size_t r = row0 + blockIdx.x;
     const uint8_t *row = w.quants + r * w.qpitch;
-    auto weight = [&](size_t k) -> float {
-        if (w.fmt == Q6_K) return q6k_weight(row + (k >> 8) * Q6_K_DEV, __half2float(w.scales[r * w.srow + (k >> 8)]), (int)(k & 255));
-        if (w.fmt == Q4_K) return q4k_weight(row + (k >> 8) * Q4_K_FILE, (int)(k & 255));
-        if (w.fmt == BF16) return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(row)[k] << 16);
-        return __fmul_rn((float)(int8_t)row[k], __half2float(w.scales[r * w.srow + (k >> 5)]));   // gpu/quant.rs:48-62
-    };
     float amax = 0.0f;
-    for (size_t k = threadIdx.x; k < cols; k += 256) amax = fmaxf(amax, fabsf(weight(k)));
+    for (size_t k = (size_t)threadIdx.x * 4; k < cols; k += 1024) {   // four consecutive weights: one sub-block, one scale
+        float v[4];
+        if (w.fmt == Q6_K) {
+            const uint8_t *blk = row + (k >> 8) * Q6_K_DEV;
+            const float d = __half2float(w.scales[r * w.srow + (k >> 8)]);
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = q6k_weight(blk, d, (int)(k & 255) + i);
+        } else {
+            // gpu/quant.rs:48-62: q as f32 * d
+            const float d = __half2float(w.scales[r * w.srow + (k >> 5)]);
+            const uint32_t q4 = *reinterpret_cast<const uint32_t *>(row + k);
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[i] = __fmul_rn((float)(int8_t)(q4 >> (8 * i)), d);
+        }
+        *reinterpret_cast<float4 *>(wrow + k) = make_float4(v[0], v[1], v[2], v[3]);
+        amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fmaxf(fabsf(v[2]), fabsf(v[3])), amax));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = amax;
@@ -786,12 +798,17 @@ __global__ void __launch_bounds__(256) dequant_pair_kernel(const WeightView w, s
     const float down = __uint_as_float((uint32_t)(127 - e) << 23);
     if (threadIdx.x == 0) row_scale[blockIdx.x] = __uint_as_float((uint32_t)(127 + e) << 23);
     __half *h = hi + (size_t)blockIdx.x * cols, *l = lo + (size_t)blockIdx.x * cols;
-    for (size_t k = threadIdx.x; k < cols; k += 256) {
-        const float v = weight(k) * down;
-        const __half a = to_f16_clamped(v);
-        const size_t at = (k & ~(size_t)3) | ((k & 1) << 1) | ((k >> 1) & 1);   // 0, 1, 2, 3 -> 0, 2, 1, 3
-        h[at] = a;
-        l[at] = to_f16_clamped(v - __half2float(a));
+    for (size_t k = (size_t)threadIdx.x * 4; k < cols; k += 1024) {
+        const float4 v4 = *reinterpret_cast<const float4 *>(wrow + k);
+        const float v[4] = {v4.x * down, v4.y * down, v4.z * down, v4.w * down};
+        uint32_t a[4], b[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            a[i] = to_f16_bits(v[i]);
+            b[i] = to_f16_bits(v[i] - from_f16_bits(a[i]));
+        }
+        *reinterpret_cast<uint2 *>(h + k) = make_uint2(a[0] | (a[2] << 16), a[1] | (a[3] << 16));
+        *reinterpret_cast<uint2 *>(l + k) = make_uint2(b[0] | (b[2] << 16), b[1] | (b[3] << 16));
     }
 }
 
@@ -896,7 +913,10 @@ int launch_pair(dwim_b200_ctx *ctx, const WeightView &w, size_t r0, size_t nr, c
 
 // Formats the tensor-core kernels take: Q4_K by the kernel that multiplies its integers
 // directly, the others as dequantized f16 pairs, a panel of rows at a time.
-bool gemm_supports(const WeightView &w) { return w.cols % 256 == 0 && (w.fmt == Q4_K || w.fmt == Q6_K || w.fmt == Q8_0); }
+bool gemm_supports(const WeightView &w) {
+    if (w.cols % 256) return false;
+    return w.fmt == Q4_K || ((w.fmt == Q6_K || w.fmt == Q8_0) && w.cols <= 12288);
+}
 
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue) {
@@ -908,6 +928,8 @@ int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, s
         if (ncols <= 128) return launch_gemm<128>(ctx, w, operand, n, split, out, aux, epilogue);
         return launch_gemm<256>(ctx, w, operand, n, split, out, aux, epilogue);
     }
+    if (w.cols * sizeof(float) > 48 * 1024)
+        return fail(ctx, DWIM_B200_EINVAL, "dense kernel: rows of %zu weights are too long for the decoder's shared memory", w.cols);
     // the panel's buffers: created on first use, grown when a wider matrix comes
     const size_t panel = w.rows < PAIR_PANEL_ROWS ? (w.rows + TILE_M - 1) / TILE_M * TILE_M : PAIR_PANEL_ROWS;
     const size_t need = panel * w.cols;
@@ -926,8 +948,8 @@ int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, s
     }
     for (size_t r0 = 0; r0 < w.rows; r0 += panel) {
         const size_t nr = w.rows - r0 < panel ? w.rows - r0 : panel;
-        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, dequant_pair_kernel, dim3((unsigned)nr), dim3(256), 0, ctx->stream, w, r0,
-                                        w.cols, ctx->pair_hi, ctx->pair_lo, ctx->pair_scale));
+        DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, dequant_pair_kernel, dim3((unsigned)nr), dim3(256), w.cols * sizeof(float),
+                                        ctx->stream, w, r0, w.cols, ctx->pair_hi, ctx->pair_lo, ctx->pair_scale));
         ctx->weights_written = false;
         DWIM_LAUNCHED(ctx);
         int rc;

