@@ -88,6 +88,10 @@ struct OutSpec {
     int world;        // destinations in use
     size_t pitch;     // floats between consecutive tokens in a destination
     size_t row0;      // destination row of the product's first row
+    // scatter (the K-sharded product's partial sums, each row to the rank that owns it): when
+    // scatter_per > 0, row r goes to dst[r / scatter_per] alone, at row (r % scatter_per) of that
+    // destination's slot for this rank (row0 is then the slot's offset in floats, pitch = scatter_per)
+    size_t scatter_per;
 };
 inline OutSpec out_local(float *out, size_t rows) {
     OutSpec o{};
@@ -95,6 +99,7 @@ inline OutSpec out_local(float *out, size_t rows) {
     o.world = 1;
     o.pitch = rows;
     o.row0 = 0;
+    o.scatter_per = 0;
     return o;
 }
 

@@ -46,7 +46,6 @@
 #include <cuda.h>
 #include <stdlib.h>
 
-#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -211,30 +210,45 @@ __device__ __forceinline__ uint32_t f16x2_rn(float lo, float hi) {
 }
 __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f / (1.0f + expf(-g))) * u; }
 
-// Where a thread's results go: its row of one destination, or of every rank's copy of a shared
-// result.  The pointers are read from the kernel's parameters by constant index, once, ahead of
-// the stores' loop (indexing the parameter array by a variable, or reading a parameter after
-// every store, cost the 256-column kernel half its speed).
+// Where a thread's results go: its row of one destination; or (SHARED kernels) of every rank's
+// copy of a shared result; or (a K-sharded product's partial sums) of its owner's slot alone.
+// The pointers are read from the kernel's parameters by constant index, once, ahead of the
+// stores' loop: indexing the parameter array by a variable, or reading a parameter after every
+// store, cost the 256-column kernel half its speed.  The many-destination stores live in kernel
+// instantiations of their own, so that the usual kernel's code stays small (an epilogue with
+// eight predicated stores per value stalled the main loop on instruction fetch).
 struct EmitTo {
-    float *row[DWIM_MAX_WORLD];   // [p]: destination p's element (token 0, this thread's row)
+    float *own;              // the first (or only) destination's element (token 0, this thread's row)
+    size_t offset;           // the same element's offset in every other destination
     size_t pitch;
     const float *aux_row;
+    const OutSpec *out;
     int world, epi;
 };
-__device__ __forceinline__ EmitTo emit_to(const GemmArgs &a, size_t row) {
+__device__ __forceinline__ EmitTo emit_to(const OutSpec &out, const float *aux, int epi, size_t row) {
     EmitTo e;
+    float *d = out.dst[0];
+    e.offset = out.row0 + row;
+    if (out.scatter_per) {
+        // the row's owner alone, its slot for this rank; the owner is picked by constant indices
+        const size_t owner = row / out.scatter_per;
+        e.offset = out.row0 + row - owner * out.scatter_per;
 #pragma unroll
-    for (int p = 0; p < DWIM_MAX_WORLD; p++) e.row[p] = p < a.out.world ? a.out.dst[p] + a.out.row0 + row : nullptr;
-    e.pitch = a.out.pitch;
-    e.aux_row = a.aux ? a.aux + row : nullptr;
-    e.world = a.out.world;
-    e.epi = a.epi;
+        for (int p = 1; p < DWIM_MAX_WORLD; p++)
+            if ((size_t)p == owner) d = out.dst[p];
+    }
+    e.own = d + e.offset;
+    e.pitch = out.pitch;
+    e.aux_row = aux ? aux + row : nullptr;
+    e.out = &out;
+    e.world = out.scatter_per ? 1 : out.world;
+    e.epi = epi;
     return e;
 }
 // One finished element: the operator's epilogue, then the store.
 template <bool SHARED>
 __device__ __forceinline__ void gemm_emit(const EmitTo &e, size_t rows, size_t t, float x) {
-    float *o = e.row[0] + t * e.pitch;
+    float *o = e.own + t * e.pitch;
     if (!SHARED) {
         if (e.epi == EPI_ADD) x += *o;
         else if (e.epi == EPI_SWIGLU) x = silu_mul_f(x, e.aux_row[t * rows]);
@@ -243,7 +257,7 @@ __device__ __forceinline__ void gemm_emit(const EmitTo &e, size_t rows, size_t t
     if (SHARED) {
 #pragma unroll
         for (int p = 1; p < DWIM_MAX_WORLD; p++)
-            if (p < e.world) e.row[p][t * e.pitch] = x;
+            if (p < e.world) e.out->dst[p][e.offset + t * e.pitch] = x;
     }
 }
 
@@ -334,7 +348,7 @@ __device__ __forceinline__ void mins_q4k_terms(const uint4 &hdr, int part, float
     }
 }
 
-template <int BN>
+template <int BN, bool SHARED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const __grid_constant__ CUtensorMap tmap_m, const __grid_constant__ GemmArgs a) {
@@ -563,9 +577,14 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             // would wait for the store before it
             for (int j = lane; j < C::DRAIN_COLS; j += 32) {
                 const size_t t = ((size_t)col0 + g * C::DRAIN_COLS + j) >> (a.split ? 1 : 0);
-                sts32f(tok0 + (g * C::DRAIN_COLS + j) * 4, t < a.n ? a.tok_scale[t] : 0.0f);
+                sts32f(tok0 + (g * C::DRAIN_COLS + j) * 4, t < a.n ? a.tok_scale[t] : 1.0f);
             }
             __syncwarp();
+            // nothing to multiply by for activations of the usual range: every scale is one
+            const uint32_t tk = tok0 + g * C::DRAIN_COLS * 4;
+            bool ones = true;
+            for (int j = lane; j < C::DRAIN_COLS; j += 32) ones = ones && lds32f(tk + j * 4) == 1.0f;
+            const bool scaled = !__all_sync(0xffffffffu, ones);
             drain(units - 1);
             float acc[C::DRAIN_COLS];
 #pragma unroll
@@ -573,27 +592,25 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             const size_t row = (size_t)row0 + rl;
             if (row < a.rows) {
                 const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
-                const EmitTo to = emit_to(a, row);
+                const EmitTo to = emit_to(a.out, a.aux, a.epi, row);
                 const size_t n = a.n, rows = a.rows;
-                const uint32_t tk = tok0 + g * C::DRAIN_COLS * 4;
-                auto all = [&](auto shared) {
-                    constexpr bool SHARED = decltype(shared)::value;
-                    if (a.split) {
+                if (scaled) {   // the tokens' powers of two
 #pragma unroll
-                        for (int j = 0; j < C::DRAIN_COLS; j += 2) {
-                            const size_t t = (cbase + j) >> 1;
-                            if (t < n) gemm_emit<SHARED>(to, rows, t, (acc[j] + acc[j + 1]) * lds32f(tk + j * 4));
-                        }
-                    } else {
+                    for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] *= lds32f(tk + j * 4);
+                }
+                if (a.split) {
 #pragma unroll
-                        for (int j = 0; j < C::DRAIN_COLS; j++) {
-                            const size_t t = cbase + j;
-                            if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j] * lds32f(tk + j * 4));
-                        }
+                    for (int j = 0; j < C::DRAIN_COLS; j += 2) {
+                        const size_t t = (cbase + j) >> 1;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j] + acc[j + 1]);
                     }
-                };
-                if (to.world == 1) all(std::false_type{});
-                else all(std::true_type{});      // a shared result: a plain product only (the host checks)
+                } else {
+#pragma unroll
+                    for (int j = 0; j < C::DRAIN_COLS; j++) {
+                        const size_t t = cbase + j;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j]);
+                    }
+                }
             }
         }
     }
@@ -635,7 +652,7 @@ template <int BN> struct PairCfg {
 };
 constexpr int PAIR_THREADS = 6 * 32;
 
-template <int BN>
+template <int BN, bool SHARED>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
                  const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PairArgs a) {
@@ -715,14 +732,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
         mbar_wait_parked(accfull, 0, a.status, 0x400000u);
         tc_fence_after();
         // destinations of this thread's row, by constant index (see EmitTo)
-        EmitTo to;
-#pragma unroll
-        for (int p = 0; p < DWIM_MAX_WORLD; p++)
-            to.row[p] = p < a.out.world ? a.out.dst[p] + a.out.row0 + a.panel_row0 + prow : nullptr;
-        to.pitch = a.out.pitch;
-        to.aux_row = a.aux ? a.aux + a.panel_row0 + prow : nullptr;
-        to.world = a.out.world;
-        to.epi = a.epi;
+        const EmitTo to = emit_to(a.out, a.aux, a.epi, a.panel_row0 + prow);
         const size_t n = a.n, rows = a.rows;
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -732,24 +742,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
             tmem_ld_wait();
             if (!live) continue;
             const size_t cbase = (size_t)col0 + c * 16;
-            auto all = [&](auto shared) {
-                constexpr bool SHARED = decltype(shared)::value;
-                if (a.split) {
+            if (a.split) {
 #pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const size_t t = (cbase + j) >> 1;
-                        if (t < n) gemm_emit<SHARED>(to, rows, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const size_t t = cbase + j;
-                        if (t < n) gemm_emit<SHARED>(to, rows, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
-                    }
+                for (int j = 0; j < 16; j += 2) {
+                    const size_t t = (cbase + j) >> 1;
+                    if (t < n) gemm_emit<SHARED>(to, rows, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
                 }
-            };
-            if (to.world == 1) all(std::false_type{});
-            else all(std::true_type{});
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const size_t t = cbase + j;
+                    if (t < n) gemm_emit<SHARED>(to, rows, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                }
+            }
         }
     }
     tc_fence_before();
@@ -862,11 +867,13 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
         return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
     GemmArgs a{w.rows, n, ncols, units, split, out, tok_scale, aux, epi, ctx->status};
-    auto kern = gemm_q4k_kernel<BN>;
-    static bool configured[64] = {false};
-    if (!configured[ctx->device & 63]) {
+    // a result shared by several ranks' copies takes the instantiation that stores to all of them
+    const bool shared = out.world > 1 && !out.scatter_per;
+    auto kern = shared ? gemm_q4k_kernel<BN, true> : gemm_q4k_kernel<BN, false>;
+    static bool configured[64][2] = {};
+    if (!configured[ctx->device & 63][shared]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured[ctx->device & 63] = true;
+        configured[ctx->device & 63][shared] = true;
     }
     dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
@@ -897,11 +904,12 @@ int launch_pair(dwim_b200_ctx *ctx, const WeightView &w, size_t r0, size_t nr, c
         return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
     PairArgs a{w.rows, r0, nr, n, ncols, w.cols / BK, split, out, ctx->pair_scale, tok_scale, aux, epi, ctx->status};
-    auto kern = gemm_pair_kernel<BN>;
-    static bool configured[64] = {false};
-    if (!configured[ctx->device & 63]) {
+    const bool shared = out.world > 1 && !out.scatter_per;
+    auto kern = shared ? gemm_pair_kernel<BN, true> : gemm_pair_kernel<BN, false>;
+    static bool configured[64][2] = {};
+    if (!configured[ctx->device & 63][shared]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured[ctx->device & 63] = true;
+        configured[ctx->device & 63][shared] = true;
     }
     dim3 grid((unsigned)((nr + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     DWIM_CUDA(ctx, launch_dependent(true, kern, grid, dim3(PAIR_THREADS), (size_t)C::SMEM, ctx->stream, th, tl, tx, a));

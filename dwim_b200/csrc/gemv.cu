@@ -361,6 +361,16 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 
 __device__ __forceinline__ void emit(const GemvArgs &a, size_t t, size_t r, float v) {
     if (r >= a.w.rows) return;
+    if (a.out.scatter_per) {
+        // a K-sharded product's partial sum: to the row's owner alone, into its slot for this rank
+        const size_t owner = r / a.out.scatter_per, local = r - owner * a.out.scatter_per;
+        float *d = a.out.dst[0];
+#pragma unroll
+        for (int p = 1; p < DWIM_MAX_WORLD; p++)
+            if ((size_t)p == owner) d = a.out.dst[p];
+        d[(a.t0 + t) * a.out.pitch + a.out.row0 + local] = v;
+        return;
+    }
     const size_t i = (a.t0 + t) * a.out.pitch + a.out.row0 + r;
     if (a.epi == EPI_ADD) v += a.out.dst[0][i];
     else if (a.epi == EPI_SWIGLU) v = silu_mul(v, a.aux[(a.t0 + t) * a.w.rows + r]);
