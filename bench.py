@@ -517,7 +517,7 @@ def ffn_config(inner, hidden, m, act, gpus):
     return {"workload": f"feed-forward block: Q4_K gate, up [{inner},{hidden}], down [{hidden},{inner}] x {act} X[{m},{hidden}]",
             "format": "q4_k", "rows": inner, "cols": hidden, "tokens": m, "activations": act,
             "sharding": (f"tensor parallel over {gpus}: gate/up by rows, down by the same K blocks (cuts at multiples of "
-                         "256), one NCCL all-reduce of the f32 [tokens, hidden] partial sums") if gpus > 1 else "none",
+                         "256), the f32 [tokens, hidden] partial sums added over the ranks (see reduction)") if gpus > 1 else "none",
             "l2": "blocks rotate over copies totalling more than the 126 MB L2"}
 
 
@@ -540,8 +540,11 @@ def run_ffn(args, fmt, inner, hidden, m, act):
     # every rank draws the same block (seed 5) and keeps its shard
     rng = np.random.default_rng(5)
     b, e = shard.ffn_cuts(inner, world)[rank]
+    full = []                                   # rank 0 keeps the whole block for the parity check
     def quantized(rows, cols, keep_rows=None, keep_cols=None):
         w = 0.02 * rng.standard_normal((rows, cols), dtype=np.float32)
+        if rank == 0:
+            full.append(w)
         if keep_rows is not None:
             w = w[keep_rows[0]:keep_rows[1]]
         if keep_cols is not None:
@@ -553,10 +556,14 @@ def run_ffn(args, fmt, inner, hidden, m, act):
         raise SystemExit(f"rank {rank} of {world} holds no part of the block")
     my_bytes = gate.data.size + up.data.size + down.data.size
     copies = int(min(24, max(2, -(-3 * L2_BYTES // my_bytes))))
-    blocks = [shard.ShardedFFN(dev, gate, up, down, 0, 1) for _ in range(copies)]   # already this rank's shard
-    # a few tokens: the partial sums through the library's all-reduce over peer memory (--nccl: through NCCL)
+    push = world > 1 and args.exchange == "push"
+    blocks = [shard.ShardedFFN(dev, gate, up, down, 0, 1, exchange="push" if push else "nccl") for _ in range(copies)]   # already this rank's shard
+    # --exchange nccl: the partial sums through NCCL, or for a few tokens through the library's small all-reduce
     peer, reduction = None, "NCCL all-reduce"
-    if world > 1 and m * hidden <= 16 * 1024 and not args.nccl:   # measured: at 8 tokens (160 KB) NCCL is level with it
+    if push:
+        reduction = ("fused: the down projection's epilogue stores partial sums into their rows' owners, the owners add "
+                     "and store the sums into every rank's copy (two barrier kernels, no collective call)")
+    elif world > 1 and m * hidden <= 16 * 1024 and not args.nccl:   # measured: at 8 tokens (160 KB) NCCL is level with it
         try:
             peer = shard.PeerReduce(dev, rank, world, 16 * 1024)
             reduction = "peer-store all-reduce (library kernel over IPC-mapped mailboxes)"
@@ -600,6 +607,31 @@ def run_ffn(args, fmt, inner, hidden, m, act):
         seconds, launches = timed(args.steps)
     per_step = seconds / args.steps
 
+    # parity of what was timed: a sample of tokens through the oracle's whole block on rank 0 (it
+    # quantizes the block itself: the device quantizer is byte-exact with it), against every rank's result
+    (dev.touch_bf16(xb) if bits is not None else dev.touch(xb))
+    got = dev.read(blocks[0].forward(xb)).reshape(m, hidden)
+    tok = np.arange(m) if m <= 24 else np.unique(np.concatenate([np.arange(8), np.arange(m - 8, m), np.random.default_rng(9).choice(m, 8, replace=False)]))
+    xs = ((bits.astype(np.uint32) << 16).view(np.float32) if bits is not None else x).reshape(m, hidden)[tok]
+    want_t = torch.zeros(tok.size * hidden, dtype=torch.float32, device="cuda")
+    if rank == 0:
+        import oracle
+        oracle.build()
+        qg, qu, qd = (oracle.quantize(fmt, w) for w in full)
+        hmid = oracle.swiglu(fmt, qg, qu, inner, hidden, xs)
+        want_t.copy_(torch.from_numpy(oracle.matmul(fmt, qd, hidden, inner, hmid).ravel()))
+        del qg, qu, qd
+    full.clear()
+    if dist:
+        dist.broadcast(want_t, 0)
+    worst = conftest_max_rel_err(got[tok], want_t.cpu().numpy())
+    if dist:
+        t = torch.tensor([worst], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = float(t.item())
+    parity = {"max_rel_err": worst, "tolerance": 1e-3, "ok": bool(worst <= 1e-3), "tokens_checked": int(tok.size),
+              "checked": "every rank's copy of the block's output, all rows, against the CPU oracle's whole block"}
+
     # end to end: pinned host x -> device -> block -> pinned host out
     hx = torch.empty(m * hidden, dtype=torch.uint16 if bits is not None else torch.float32, pin_memory=True).numpy()
     hx[:] = (bits if bits is not None else x).ravel()
@@ -637,7 +669,7 @@ def run_ffn(args, fmt, inner, hidden, m, act):
             "config": dict(ffn_config(inner, hidden, m, act, world), reduction=reduction if world > 1 else "none"),
             "e2e": {"value": m / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(hx.nbytes),
                     "d2h_bytes_per_step": int(hout.nbytes), "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roof, "device": dev.name(),
+            "gpu_launches": int(launches), "clocks": clocks.summary(), "roofline": roof, "parity": parity, "device": dev.name(),
         }
         if world == 1 and not args.no_cpu_baseline:
             cb = cpu_baseline(fmt, inner, hidden, m, act)

@@ -61,6 +61,8 @@ SIGNATURES = {
     "dwim_b200_shared_connect": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _sz]),
     "dwim_b200_matmul_gather": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _sz]),
     "dwim_b200_shared_barrier": (C.c_int, [_vp, _vp]),
+    "dwim_b200_matmul_scatter": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "dwim_b200_reduce_gather": (C.c_int, [_vp, _vp, _vp, _sz, _sz]),
     "dwim_b200_shard_rows": (C.c_int, [_sz, C.c_int, C.c_int, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "dwim_b200_gather_rows": (C.c_int, [_vp, _vp, _vp, _sz, _sz, C.c_int, _sz]),
     "dwim_b200_peer_handle_bytes": (_sz, []),

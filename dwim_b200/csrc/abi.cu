@@ -497,6 +497,18 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
     return 0;
 }
 
+}  // extern "C"
+
+namespace dwim {
+// For the sharded forms in peer.cu: a plain product into destinations described by `out`.
+int product_into(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const dwim_b200_weight *w, dwim_b200_buffer *x,
+                 const char *what) {
+    return product(ctx, out, out_len, w, x, nullptr, EPI_STORE, what);
+}
+}  // namespace dwim
+
+extern "C" {
+
 int dwim_b200_matmul(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w, dwim_b200_buffer *x) {
     if (!ctx || !out || !w || !x) return DWIM_B200_EINVAL;
     int rc = product(ctx, out_local(out->data, w->v.rows), out->len, w, x, nullptr, EPI_STORE, "matmul");

@@ -348,3 +348,94 @@ extern "C" int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
     DWIM_LAUNCHED(ctx);
     return 0;
 }
+
+// ---- the K-sharded product: partial sums scattered to the rows' owners, reduced, gathered --------
+// The closing product of a tensor-parallel block (the feed-forward block's down
+// projection, an attention block's output projection) is split along K: every
+// rank multiplies its K slice of W with its slice of the activations and holds
+// a partial sum of the whole [n, rows] result.  Rows are owned by ranks in
+// slices of `per` = ceil(rows / world).  dwim_b200_matmul_scatter's epilogue
+// stores each partial sum straight into its row's owner: slot `rank` of the
+// owner's copy of the shared `slots` buffer ([world][n][per] floats), by plain
+// stores over NVLink while other tiles multiply.  After a barrier,
+// dwim_b200_reduce_gather adds a rank's own rows over the slots in rank order
+// (the same bits on every rank) and stores the sums into every rank's copy of
+// the shared result; a second barrier closes the exchange.
+namespace {
+
+struct ReduceArgs {
+    const float *slots;                 // this rank's copy: [world][n][per]
+    float *out[DWIM_MAX_WORLD];         // every rank's copy of the result [n][rows]
+    size_t n, rows, per, begin, mine;   // mine = rows this rank owns, from `begin`
+    int world;
+};
+
+__global__ void __launch_bounds__(256) reduce_gather_kernel(const __grid_constant__ ReduceArgs a) {
+    dwim::griddep_launch();
+    dwim::griddep_wait();
+    const size_t total = a.n * a.mine;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / a.mine, r = i - t * a.mine;
+        float sum = 0.0f;
+        for (int q = 0; q < a.world; q++) sum += a.slots[((size_t)q * a.n + t) * a.per + r];
+        const size_t at = t * a.rows + a.begin + r;
+#pragma unroll
+        for (int p = 0; p < DWIM_MAX_WORLD; p++)
+            if (p < a.world) a.out[p][at] = sum;
+    }
+}
+
+}  // namespace
+
+namespace dwim {
+int product_into(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const dwim_b200_weight *w, dwim_b200_buffer *x,
+                 const char *what);
+}
+
+extern "C" int dwim_b200_matmul_scatter(dwim_b200_ctx *ctx, dwim_b200_buffer *slots, const dwim_b200_weight *w, dwim_b200_buffer *x) {
+    using namespace dwim;
+    if (!ctx || !slots || !w || !x) return DWIM_B200_EINVAL;
+    if (slots->sh_world < 1) return fail(ctx, DWIM_B200_EINVAL, "matmul_scatter: the slots are not a connected shared buffer");
+    const size_t rows = w->v.rows, cols = w->v.cols;
+    if (cols == 0 || x->len % cols) return fail(ctx, DWIM_B200_EINVAL, "matmul_scatter: input of %zu floats is not rows of %zu", x->len, cols);
+    const size_t n = x->len / cols, world = (size_t)slots->sh_world, per = (rows + world - 1) / world;
+    if (slots->len != world * n * per)
+        return fail(ctx, DWIM_B200_EINVAL, "matmul_scatter: slots of %zu floats, %zu ranks x %zu tokens x %zu rows need %zu", slots->len,
+                    world, n, per, world * n * per);
+    OutSpec o{};
+    o.world = slots->sh_world;
+    for (int r = 0; r < slots->sh_world; r++) o.dst[r] = slots->sh_peer[r];   // by owner rank
+    o.pitch = per;
+    o.row0 = (size_t)slots->sh_rank * n * per;                                // this rank's slot in every owner's copy
+    o.scatter_per = per;
+    // the product checks its output's length against tokens x pitch
+    return product_into(ctx, o, n * per, w, x, "matmul_scatter");
+}
+
+extern "C" int dwim_b200_reduce_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *slots, size_t n, size_t rows) {
+    using namespace dwim;
+    if (!ctx || !out || !slots) return DWIM_B200_EINVAL;
+    if (out->sh_world < 1 || slots->sh_world != out->sh_world || slots->sh_rank != out->sh_rank)
+        return fail(ctx, DWIM_B200_EINVAL, "reduce_gather: out and slots are not shared buffers of one group");
+    const size_t world = (size_t)out->sh_world, per = (rows + world - 1) / world;
+    if (out->len != n * rows || slots->len != world * n * per)
+        return fail(ctx, DWIM_B200_EINVAL, "reduce_gather: out of %zu and slots of %zu floats for [%zu, %zu] over %zu ranks", out->len,
+                    slots->len, n, rows, world);
+    ReduceArgs a{};
+    a.slots = slots->data;
+    for (int r = 0; r < out->sh_world; r++) a.out[r] = out->sh_peer[r];
+    a.n = n;
+    a.rows = rows;
+    a.per = per;
+    a.begin = (size_t)out->sh_rank * per;
+    a.mine = a.begin >= rows ? 0 : (rows - a.begin < per ? rows - a.begin : per);
+    a.world = out->sh_world;
+    out->shadow_kind = SHADOW_NONE;
+    out->bf16_exact = false;
+    if (n * a.mine == 0) return 0;
+    size_t blocks = (n * a.mine + 255) / 256, cap = (size_t)ctx->sm_count * 8;
+    DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, reduce_gather_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0,
+                                    ctx->stream, a));
+    DWIM_LAUNCHED(ctx);
+    return 0;
+}

@@ -225,6 +225,14 @@ class B200:
     def shared_barrier(self, buf: Buffer) -> None:
         self._check(self._L.dwim_b200_shared_barrier(self._ctx, buf._h))
 
+    def matmul_scatter(self, slots: Buffer, w: Weight, x: Buffer) -> None:
+        """The K-sharded product, every partial sum stored into its row's owner's slot."""
+        self._check(self._L.dwim_b200_matmul_scatter(self._ctx, slots._h, w._h, x._h))
+
+    def reduce_gather(self, out: Buffer, slots: Buffer, n: int, rows: int) -> None:
+        """This rank's rows summed over the slots, the sums stored into every rank's copy of ``out``."""
+        self._check(self._L.dwim_b200_reduce_gather(self._ctx, out._h, slots._h, n, rows))
+
     # -- the small all-reduce over peer memory (one process per GPU) ------------
     def peer_create(self, world: int, rank: int, cap: int) -> bytes:
         """Allocates this rank's mailbox for vectors of up to ``cap`` floats;

@@ -199,9 +199,16 @@ class ShardedFFN:
     per GPU).  ``forward`` leaves the block's full output on every rank."""
 
     def __init__(self, dev: B200, gate: Tensor, up: Tensor, down: Tensor, rank: int = 0, world: int = 1, group=None,
-                 peer: PeerReduce | None = None):
+                 peer: PeerReduce | None = None, exchange: str = "nccl"):
+        """``exchange``: how the ranks' partial sums of the down projection are added.
+        "push": the product's epilogue stores each partial sum into its row's owner
+        (``B200.matmul_scatter``), the owners add and store the sums into every rank's
+        copy of the result (``B200.reduce_gather``): no collective library call.
+        "nccl": one all-reduce after the product (or ``peer``, the library's small
+        all-reduce, for vectors it holds)."""
         import torch
         self.dev, self.rank, self.world, self.group = dev, rank, world, group
+        self.exchange = exchange
         self.peer = peer                   # sums of up to peer.cap floats go through it instead of NCCL
         self.hidden, self.inner = gate.cols, gate.rows
         g, u, d = ffn_shard(gate, up, down, rank, world)
@@ -229,11 +236,46 @@ class ShardedFFN:
         self._out_t = bufs[0]
         return bufs
 
+    _shared_push: dict = {}
+
+    def _push_buffers(self, n: int):
+        """The shared slots and result of the "push" exchange, one set per shape and
+        device, created by every rank at the same point (their handles are exchanged)."""
+        key = (id(self.dev), n, self.hidden, self.world)
+        bufs = ShardedFFN._shared_push.get(key)
+        if bufs is None:
+            import torch.distributed as dist
+            per = -(-self.hidden // self.world)
+            made = []
+            for length in (self.world * n * per, n * self.hidden):
+                buf, handle = self.dev.shared_alloc(length)
+                handles = [None] * self.world
+                if self.world > 1:
+                    dist.all_gather_object(handles, handle, group=self.group)
+                else:
+                    handles = [handle]
+                self.dev.shared_connect(buf, self.world, self.rank, handles)
+                made.append(buf)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            bufs = (made[0], made[1], self.dev.alloc(n * max(self.my_inner, 1)), self.dev.alloc(n * max(self.my_inner, 1)))
+            ShardedFFN._shared_push[key] = bufs
+        return bufs
+
     def forward(self, x):
         """The block applied to ``x`` (n * hidden floats): returns the device
         buffer of n * hidden floats, valid until the next ``forward`` of any
         block of this shape on the device."""
         n = len(x) // self.hidden
+        if self.exchange == "push":
+            slots, out, h, scratch = self._push_buffers(n)
+            if self.my_inner:
+                self.dev.swiglu(h, self.gate, self.up, x, scratch)
+                self.dev.matmul_scatter(slots, self.down, h)
+            self.dev.shared_barrier(slots)
+            self.dev.reduce_gather(out, slots, n, self.hidden)
+            self.dev.shared_barrier(out)
+            return out
         out_t, out, h, scratch = self._buffers(n)
         if self.my_inner:
             self.dev.swiglu(h, self.gate, self.up, x, scratch)

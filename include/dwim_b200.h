@@ -247,6 +247,22 @@ DWIM_B200_API int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *
  * captured in a CUDA graph and replayed. */
 DWIM_B200_API int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
 
+/* The K-sharded product with the reduction's first half fused into it: `w` holds
+ * this rank's K slice of a [rows, K] matrix (all rows), `x` this rank's slice of
+ * the activations; rows are owned by ranks in slices of per = ceil(rows / world).
+ * The kernel's epilogue stores every partial sum into its row's owner: slot
+ * `rank` of the owner's copy of the shared buffer `slots` (world * n * per f32,
+ * laid out [source rank][token][row of the slice]).  After every rank's call
+ * and dwim_b200_shared_barrier(slots), reduce_gather adds this rank's own rows
+ * over the slots in rank order and stores the sums into every rank's copy of
+ * the shared result `out` (n * rows f32, token-major); after
+ * dwim_b200_shared_barrier(out) every copy holds the full sum, the same bits on
+ * every rank.  Replaces an all-reduce of the n * rows partial sums. */
+DWIM_B200_API int dwim_b200_matmul_scatter(dwim_b200_ctx *ctx, dwim_b200_buffer *slots, const dwim_b200_weight *w,
+                                           dwim_b200_buffer *x);
+DWIM_B200_API int dwim_b200_reduce_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *slots,
+                                          size_t n, size_t rows);
+
 /* The rows rank `rank` of `world` holds when a matrix is split by output
  * rows at multiples of `align`: [*begin, *end). */
 DWIM_B200_API int dwim_b200_shard_rows(size_t rows, int rank, int world, size_t align,

@@ -754,6 +754,23 @@ def test_adopted_stream_and_touch(oracle):
         d.close()
 
 
+@pytest.mark.parametrize("n", [1, 6, 40])
+def test_feed_forward_block_push_exchange_in_a_world_of_one(dev, oracle, n):
+    """matmul_scatter, reduce_gather and the barriers with a single rank: the
+    whole result is this rank's slice, its one slot the whole sum."""
+    from dwim_b200 import Tensor, shard
+    rng = np.random.default_rng(161 + n)
+    hidden, inner = 512, 1024
+    mk = lambda r, c: Tensor("q4_k", (r, c), oracle.quantize("q4_k", (0.05 * rng.standard_normal((r, c))).astype(np.float32)))
+    gate, up, down = mk(inner, hidden), mk(inner, hidden), mk(hidden, inner)
+    x = rng.standard_normal((n, hidden)).astype(np.float32)
+    block = shard.ShardedFFN(dev, gate, up, down, exchange="push")
+    got = dev.read(block.forward(dev.buffer(x))).reshape(n, hidden)
+    h = oracle.swiglu("q4_k", gate.data, up.data, inner, hidden, x)
+    want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
+    assert max_rel_err(got, want) <= 5e-5
+
+
 def test_shared_buffer_in_a_world_of_one(dev, oracle):
     """matmul_gather and the barrier with a single rank: two row shards written
     into one shared result at their offsets, as two ranks would."""

@@ -55,6 +55,17 @@ def _rank(rank: int, world: int, port: int, queue):
             want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
             err = np.abs(got - want).max() / np.sqrt((want * want).mean())
             assert err < 5e-5, (n, rank, err)
+        # the same block with the reduction fused into the down projection: partial sums stored into
+        # their rows' owners, added there, the sums stored into every rank's copy (one to 300 tokens:
+        # the small-M kernel, the token groups, the tensor-core kernel)
+        pushed = shard.ShardedFFN(dev, gate, up, down, rank, world, exchange="push")
+        for n in (1, 5, 12, 300):
+            x = rng.standard_normal((n, hidden)).astype(np.float32)
+            got = dev.read(pushed.forward(dev.buffer(x))).reshape(n, hidden)
+            h = oracle.swiglu("q4_k", gate.data, up.data, inner, hidden, x)
+            want = oracle.matmul("q4_k", down.data, hidden, inner, h).reshape(n, hidden)
+            err = np.abs(got - want).max() / np.sqrt((want * want).mean())
+            assert err < 5e-5, ("push ffn", n, rank, err)
         # the row-sharded product with the all-gather fused into its epilogue: every rank's copy of
         # the shared result must hold every rank's rows (uneven shards: 1000 rows over two ranks)
         rows, cols = 1000, 1024
