@@ -46,6 +46,7 @@ struct dwim_b200_weight {
     dwim::WeightView v{};
     void *quants_alloc = nullptr;
     void *scales_alloc = nullptr;
+    void *mins_alloc = nullptr;      // see WeightView::mins
 };
 
 struct dwim_b200_ctx {
