@@ -92,13 +92,19 @@ struct GemmArgs {
 // stages, two raw stages, one stage of the minimums' operands, and a hand-over
 // per K block (a B stage is reloaded as soon as its own K block is done).
 template <int BN> struct Cfg {
-    static constexpr int B_STAGES = BN > 128 ? 3 : 4;
-    static constexpr int RAW_STAGES = BN > 128 ? 2 : 3;
-    static constexpr int MIN_STAGES = BN > 128 ? 1 : 2;            // stages of the minimums' A operand (the workers write it)
+    static constexpr int CG = BN > 128 ? 2 : 1;                     // CTAs per tile of 128*CG rows: a pair at 256 columns
+    static constexpr int BN_CTA = BN / CG;                         // B columns (and their means) a CTA keeps
+    // One B stage per K block of a unit, never more: a K block's barrier (full) takes the producer's
+    // arrival for the next unit only after the MMAs of this unit's K block are done, which is what
+    // frees the stage when the ring is no longer than a unit.  (With six stages the arrival could
+    // come while the workers' of the unit before were still outstanding.)
+    static constexpr int B_STAGES = KBLOCKS;
+    static constexpr int RAW_STAGES = 3;
+    static constexpr int MIN_STAGES = 2;                           // stages of the minimums' A operand
     static constexpr int HAND = BN > 128 ? 1 : 2;                  // K blocks per hand-over
     static constexpr int NHAND = KBLOCKS / HAND;
-    static constexpr int B_BYTES = BN * BK * 2;
-    static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [K group of 8][column][16 B]: the means' hi and lo parts
+    static constexpr int B_BYTES = BN_CTA * BK * 2;
+    static constexpr int BMIN_BYTES = BN_CTA * 16 * 2;             // [K group of 8][column][16 B]: the means' hi and lo parts
     static constexpr int MEAN_BYTES = ((BMIN_BYTES + 1023) / 1024) * 1024;   // a stage of the means; always two of them
     static constexpr int TOK_BYTES = BN * 4;                       // the columns' token scales, for the epilogue
     static constexpr int A_RING = KBLOCKS * A_BYTES;
@@ -111,46 +117,85 @@ template <int BN> struct Cfg {
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
+// CG: the CTAs that share a tile (cta_group): 1, or 2 for a pair of CTAs of a cluster, whose
+// MMAs one thread of the pair's first CTA issues for both (M = 256: each CTA's 128 rows of A
+// from its own shared memory into its own tensor memory; B's columns half from each).
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    if (CG == 2) asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    else asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CG == 2) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc]; f16 inputs, f32 accumulate.
+template <int CG>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
+    if (CG == 2)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+            : "memory");
 }
 // The same with the descriptors given as (low word, shared high word) and the
 // accumulate flag fixed at compile time: the issuing thread has about one
 // instruction slot per five cycles, so every instruction between two MMAs counts.
-template <int ACC>
+template <int ACC, int CG>
 __device__ __forceinline__ void umma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .b64 da, db;\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "mov.b64 da, {%1, %3};\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
-        : "memory");
+    if (CG == 2)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t"
+            "}\n" ::"r"(d_tmem),
+            "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
+            : "memory");
 }
-// Arrive on an mbarrier once every MMA this thread issued so far has finished.
+// Arrive on an mbarrier once every MMA this thread issued so far has finished; for a pair,
+// on the barrier at the same place in both CTAs.
+template <int CG>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    if (CG == 2)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                     "h"((uint16_t)3)
+                     : "memory");
+    else asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -248,9 +293,8 @@ __device__ __forceinline__ EmitTo emit_to(const OutSpec &out, size_t row) {
 // One finished element: the operator's epilogue, then the store.  Everything but the thread's
 // own pointer is read from the kernel's parameters (constant memory) where it is used.
 template <int MODE>
-__device__ __forceinline__ void gemm_emit(const EmitTo &e, const OutSpec &out, const float *aux, int epi, size_t rows, size_t row,
-                                          size_t t, float x) {
-    float *o = e.own + t * out.pitch;
+__device__ __forceinline__ void gemm_emit(const EmitTo &e, float *o, const OutSpec &out, const float *aux, int epi, size_t rows,
+                                          size_t row, size_t t, float x) {
     if (MODE == EMIT_ONE) {
         if (epi == EPI_ADD) x += *o;
         else if (epi == EPI_SWIGLU) x = silu_mul_f(x, aux[t * rows + row]);
@@ -392,16 +436,28 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
     const int units = (int)a.units;
+    // A pair (CG = 2): the CTAs of a cluster of two take neighbouring row tiles and the same
+    // columns.  The first one (the leader) issues the MMAs for both; the barriers that gate
+    // an MMA (full, minfull, accempty) are the leader's and count both CTAs' arrivals, those an
+    // MMA's completion releases (empty, accfull) exist in both and are signalled together.
+    constexpr int CG = C::CG;
+    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+    const bool lead = rank == 0;
+    const int colh = col0 + (int)rank * C::BN_CTA;                       // the first of the B columns this CTA keeps
+    const uint32_t full_lead = CG == 2 ? mapa_shared(full0, 0) : full0;  // the leader's barriers, as any CTA of the pair names them
+    const uint32_t minfull_lead = CG == 2 ? mapa_shared(minfull0, 0) : minfull0;
+    const uint32_t accempty_lead = CG == 2 ? mapa_shared(accempty0, 0) : accempty0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NHAND; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4 * C::HAND);   // the producer's expect_tx arrival + the hand-over's worker warps
-            mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
+            mbar_init(full0 + 8 * s, 1 + 4 * C::HAND * CG);   // the leader's expect_tx arrival + the hand-over's worker warps
+            mbar_init(empty0 + 8 * s, 1);                     // the MMA warp's commit
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(minfull0 + 8 * s, 2);              // the means' and the minimums' producers
+            // the means' and the minimums' producers; at the leader also the other CTA's word that its own have landed
+            mbar_init(minfull0 + 8 * s, lead ? 2 + (CG - 1) : 2);
             mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's minimums and means have been read
-            mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS);
+            mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS * CG);
         }
         for (int s = 0; s < C::RAW_STAGES; s++) {
             mbar_init(rawfull0 + 8 * s, 1);
@@ -410,11 +466,12 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, C::TMEM_COLS);
-        tmem_relinquish();
+        tmem_alloc<CG>(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish<CG>();
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync();   // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem_base = lds32(tmem_slot);
     // Launched as a programmatic dependent: the next launch on the stream may begin as SMs
@@ -428,7 +485,7 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         griddep_wait();   // the operand comes from the prologue kernel just ahead
         if (lane == 0) {
             // this tile's columns of the means: two runs of 16 bytes per column and unit (hi parts, lo parts)
-            const uint32_t mean_cols = (uint32_t)min((size_t)BN, a.ncols - (size_t)col0);
+            const uint32_t mean_cols = (size_t)colh < a.ncols ? (uint32_t)min((size_t)C::BN_CTA, a.ncols - (size_t)colh) : 0u;
             for (int u = 0; u < units; u++) {
                 // The unit's means first: they are read last, by the two MMAs that close the unit, and
                 // their stage (one of two) was last read by unit u - 2.  Loaded behind the B tiles, with
@@ -436,9 +493,11 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 if (u >= 2) mbar_wait_parked(accfull0 + 8 * (u & 1), ((u - 2) >> 1) & 1, a.status, 0x40u);
                 mbar_expect_tx(minfull0 + 8 * (u & 1), 2 * mean_cols * 16);
                 const uint32_t bm = mean0 + (u & 1) * C::MEAN_BYTES;
-                const __half *mu = a.means + ((size_t)(2 * u) * a.ncols + col0) * 8;
-                bulk_g2s(bm, mu, mean_cols * 16, minfull0 + 8 * (u & 1));                             // the hi parts
-                bulk_g2s(bm + BN * 16, mu + a.ncols * 8, mean_cols * 16, minfull0 + 8 * (u & 1));     // the lo parts
+                const __half *mu = a.means + ((size_t)(2 * u) * a.ncols + colh) * 8;
+                if (mean_cols) {
+                    bulk_g2s(bm, mu, mean_cols * 16, minfull0 + 8 * (u & 1));                                    // the hi parts
+                    bulk_g2s(bm + C::BN_CTA * 16, mu + a.ncols * 8, mean_cols * 16, minfull0 + 8 * (u & 1));     // the lo parts
+                }
                 for (int h = 0; h < C::NHAND; h++) {
                     // B stage kb % B_STAGES was last read by K block kb - B_STAGES
                     for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
@@ -446,10 +505,12 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                         if (prev >= 0)
                             mbar_wait_parked(empty0 + 8 * ((prev % KBLOCKS) / C::HAND), (prev / KBLOCKS) & 1, a.status, 0x20u);
                     }
-                    mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES);
+                    if (lead) mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES * CG);   // both CTAs' halves
                     for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
                         const int kb = KBLOCKS * u + g;
-                        tma_load_2d(bstage0 + (kb % C::B_STAGES) * C::B_BYTES, &tmap_x, kb * BK, col0, full0 + 8 * h);
+                        const uint32_t dst = bstage0 + (kb % C::B_STAGES) * C::B_BYTES;
+                        if (CG == 2) tma_load_2d_pair(dst, &tmap_x, kb * BK, colh, full_lead + 8 * h);
+                        else tma_load_2d(dst, &tmap_x, kb * BK, col0, full0 + 8 * h);
                     }
                 }
             }
@@ -487,12 +548,21 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 bulk_g2s(am + 3 * MINS_GROUP, src + MINS_GROUP, MINS_GROUP, bar);
             }
         }
+    } else if (warp == 1 && !lead) {
+        // ------------------------------ the pair's second CTA: no MMAs to issue ------------------------------
+        // Its means and minimums arrive on its own barrier (a bulk copy signals the CTA it writes
+        // to); this warp passes each completion on to the leader's.
+        for (int u = 0; u < units; u++) {
+            mbar_wait_parked(minfull0 + 8 * (u & 1), (u >> 1) & 1, a.status, 0x200u);
+            if (lane == 0) mbar_arrive_cluster(minfull_lead + 8 * (u & 1));
+            __syncwarp();
+        }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp runs the loop (uniform control flow keeps addresses
         // and descriptors on the uniform data path) and one lane issues.  Units
         // are taken two at a time so that the accumulator buffer is static.
-        constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
+        constexpr uint32_t idesc = idesc_f16(TILE_M * CG, BN);
         constexpr uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);   // stride offset 1024 B, version 1, 128-byte swizzle
         const uint32_t a_lo = ((astage0 & 0x3ffffu) >> 4) | (1u << 16), b_lo = ((bstage0 & 0x3ffffu) >> 4) | (1u << 16);
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
@@ -517,13 +587,13 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                         if (lane == 0) {
 #pragma unroll
                             for (int k = 0; k < BK / 16; k++) {   // 32 bytes further along the swizzled row per K=16
-                                if (g == 0 && k == 0) umma_f16_lo<0>(s1, ad, bd, desc_hi, idesc);
-                                else umma_f16_lo<1>(s1, ad + 2 * k, bd + 2 * k, desc_hi, idesc);
+                                if (g == 0 && k == 0) umma_f16_lo<0, CG>(s1, ad, bd, desc_hi, idesc);
+                                else umma_f16_lo<1, CG>(s1, ad + 2 * k, bd + 2 * k, desc_hi, idesc);
                             }
                         }
                         bs = bs + 1 == C::B_STAGES ? 0 : bs + 1;
                     }
-                    if (lane == 0) umma_commit(empty0 + 8 * h);   // the stages may be refilled once these finish
+                    if (lane == 0) umma_commit<CG>(empty0 + 8 * h);   // the stages may be refilled once these finish
                     __syncwarp();
                 }
                 const int ms = u % C::MIN_STAGES;
@@ -532,10 +602,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 if (lane == 0) {
                     // the minimums: terms (hi, hi | lo, lo) against the means' (hi, lo) twice
                     const uint32_t am = min0 + ms * AMIN_BYTES;
-                    const uint64_t bdm = smem_desc_plain(mean0 + ab * C::MEAN_BYTES, BN * 16);
-                    umma_f16(s1, smem_desc_plain(am, TILE_M * 16), bdm, idesc, 1);
-                    umma_f16(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), bdm, idesc, 1);
-                    umma_commit(accfull0 + 8 * ab);     // the unit's sum is complete
+                    const uint64_t bdm = smem_desc_plain(mean0 + ab * C::MEAN_BYTES, C::BN_CTA * 16);
+                    umma_f16<CG>(s1, smem_desc_plain(am, TILE_M * 16), bdm, idesc, 1);
+                    umma_f16<CG>(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), bdm, idesc, 1);
+                    umma_commit<CG>(accfull0 + 8 * ab);     // the unit's sum is complete
                 }
                 __syncwarp();
             }
@@ -576,7 +646,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
+            if (lane == 0) {
+                if (CG == 2) mbar_arrive_cluster(accempty_lead + 8 * ab);
+                else mbar_arrive(accempty0 + 8 * ab);
+            }
         };
 
         for (int u = 0; u < units; u++) {
@@ -591,7 +664,10 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             store_q4k_block(blk, a_row_sw);
             fence_async_smem();      // the tensor core reads shared memory through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8 * (g / C::HAND));
+            if (lane == 0) {
+                if (CG == 2) mbar_arrive_cluster(full_lead + 8 * (g / C::HAND));
+                else mbar_arrive(full0 + 8 * (g / C::HAND));
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(rawempty0 + 8 * rs);
             if (drains && u > 0) drain(u - 1);
@@ -616,33 +692,61 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             float acc[C::DRAIN_COLS];
 #pragma unroll
             for (int j = 0; j < C::DRAIN_COLS / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
-            const size_t row = (size_t)row0 + rl;
-            if (row < a.rows) {
-                const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
-                const EmitTo to = emit_to<MODE>(a.out, row);
-                if (scaled) {   // the tokens' powers of two
+            int nvals = C::DRAIN_COLS;   // values per row: one per token
+            if (a.split) {
 #pragma unroll
-                    for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] *= lds32f(tk + j * 4);
-                }
+                for (int j = 0; j < C::DRAIN_COLS / 2; j++) acc[j] = acc[2 * j] + acc[2 * j + 1];
+                nvals = C::DRAIN_COLS / 2;
+            }
+            const size_t row = (size_t)row0 + rl;
+            const bool ok = row < a.rows;
+            const size_t t0 = ((size_t)col0 + g * C::DRAIN_COLS) >> (a.split ? 1 : 0);
+            const EmitTo to = emit_to<MODE>(a.out, ok ? row : 0);
+            const size_t pitch = a.out.pitch;
+            float *o = to.own + t0 * pitch;
+            if (MODE == EMIT_ONE && a.epi == EPI_STORE && !scaled && t0 + nvals <= a.n) {
+                // The usual case, a whole tile stored as it is, at three instructions a value: the
+                // stores of a tile were 8 us of instructions (address, bounds and epilogue tests for
+                // each value) on top of the memory system's 2.5 us.
                 if (a.split) {
 #pragma unroll
-                    for (int j = 0; j < C::DRAIN_COLS; j += 2) {
-                        const size_t t = (cbase + j) >> 1;
-                        if (t < a.n) gemm_emit<MODE>(to, a.out, a.aux, a.epi, a.rows, row, t, acc[j] + acc[j + 1]);
+                    for (int j = 0; j < C::DRAIN_COLS / 2; j++) {
+                        if (ok) *o = acc[j];
+                        o += pitch;
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j++) {
-                        const size_t t = cbase + j;
-                        if (t < a.n) gemm_emit<MODE>(to, a.out, a.aux, a.epi, a.rows, row, t, acc[j]);
+                        if (ok) *o = acc[j];
+                        o += pitch;
                     }
+                }
+            } else {
+                // Everything else sixteen values at a time from the front of the array, which then
+                // moves down by sixteen: the loop stays a loop and its code small.
+#pragma unroll 1
+                for (int c = 0; c < nvals; c += 16) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        if (j < C::DRAIN_COLS) {
+                            float x = acc[j];
+                            if (scaled) x *= lds32f(tk + ((c + j) << (a.split ? 1 : 0)) * 4);
+                            const size_t t = t0 + c + j;
+                            if (ok && c + j < nvals && t < a.n) gemm_emit<MODE>(to, o, a.out, a.aux, a.epi, a.rows, row, t, x);
+                            o += pitch;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j + 16 < C::DRAIN_COLS; j++) acc[j] = acc[j + 16];
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    // neither CTA of a pair leaves while the other may still signal its barriers or read its operands
+    if (CG == 2) cluster_sync();
+    if (warp == 1) tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
 }
 
 // ---- the dense pair kernel: Q8_0 and Q6_K above the small-M kernel's range --------------------
@@ -699,8 +803,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
-        tmem_relinquish();
+        tmem_alloc<1>(tmem_slot, BN < 32 ? 32 : BN);
+        tmem_relinquish<1>();
     }
     tc_fence_before();
     __syncthreads();
@@ -734,12 +838,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
             if (lane == 0) {
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++) {
-                    if (kb == 0 && k == 0) umma_f16_lo<0>(tm, hi_lo, b_lo, desc_hi, idesc);
-                    else umma_f16_lo<1>(tm, hi_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
-                    umma_f16_lo<1>(tm, lo_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                    if (kb == 0 && k == 0) umma_f16_lo<0, 1>(tm, hi_lo, b_lo, desc_hi, idesc);
+                    else umma_f16_lo<1, 1>(tm, hi_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                    umma_f16_lo<1, 1>(tm, lo_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
                 }
-                umma_commit(empty0 + 8 * s);
-                if (kb == kblocks - 1) umma_commit(accfull);
+                umma_commit<1>(empty0 + 8 * s);
+                if (kb == kblocks - 1) umma_commit<1>(accfull);
             }
             __syncwarp();
         }
@@ -772,20 +876,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 16; j += 2) {
                     const size_t t = (cbase + j) >> 1;
-                    if (t < n) gemm_emit<MODE>(to, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    if (t < n) gemm_emit<MODE>(to, to.own + t * a.out.pitch, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const size_t t = cbase + j;
-                    if (t < n) gemm_emit<MODE>(to, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    if (t < n) gemm_emit<MODE>(to, to.own + t * a.out.pitch, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+    if (warp == 1) tmem_dealloc<1>(tmem_base, BN < 32 ? 32 : BN);
 }
 
 // A row of W decoded, scaled by its own power of two and written as two f16 terms, each run of
@@ -884,7 +988,7 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
                         CU_TENSOR_MAP_SWIZZLE_NONE, "weight")))
         return rc;
     // activations: [ncols][K] f16, box [BN][64], 128-byte swizzle; columns past the end read as zero
-    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, BN,
+    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, C::BN_CTA,
                         CU_TENSOR_MAP_SWIZZLE_128B, "activation")))
         return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
@@ -898,9 +1002,11 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured[ctx->device & 63][mode] = true;
     }
-    dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
+    // row tiles in whole pairs where two CTAs share a tile; a tile past the last row reads zeros and stores nothing
+    const size_t row_tiles = ((w.rows + TILE_M - 1) / TILE_M + C::CG - 1) / C::CG * C::CG;
+    dim3 grid((unsigned)row_tiles, (unsigned)((ncols + BN - 1) / BN));
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
-    DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, a));
+    DWIM_CUDA(ctx, launch_dependent_cluster(dependent, C::CG, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, a));
     ctx->weights_written = false;
     DWIM_LAUNCHED(ctx);
     return 0;
@@ -954,7 +1060,7 @@ bool gemm_supports(const WeightView &w) {
 // the matrix and kept with it: a quarter of the matrix's own bytes.
 int gemm_prepare_weight(dwim_b200_ctx *ctx, dwim_b200_weight *w) {
     if (w->v.fmt != Q4_K || w->mins_alloc || w->v.rows == 0 || w->v.cols == 0) return 0;
-    const size_t tiles = (w->v.rows + TILE_M - 1) / TILE_M, units = w->v.cols / 256;
+    const size_t tiles = ((w->v.rows + TILE_M - 1) / TILE_M + 1) / 2 * 2, units = w->v.cols / 256;   // whole pairs of tiles
     DWIM_CUDA(ctx, cudaMalloc(&w->mins_alloc, tiles * units * MINS_BLOB));
     q4k_mins_kernel<<<dim3((unsigned)tiles, (unsigned)units), TILE_M, 0, ctx->stream>>>(w->v.quants, w->v.qpitch, w->v.rows, units,
                                                                                       (uint8_t *)w->mins_alloc);
