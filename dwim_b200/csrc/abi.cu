@@ -23,7 +23,6 @@ namespace dwim {
 bool gemm_supports(const WeightView &w);
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,
                const float *aux, int epilogue);
-int gemm_prepare_weight(dwim_b200_ctx *ctx, dwim_b200_weight *w);
 void gemm_release(dwim_b200_ctx *ctx);
 }  // namespace dwim
 
@@ -354,7 +353,6 @@ int dwim_b200_weight_free(dwim_b200_ctx *ctx, dwim_b200_weight *w) {
     cudaStreamSynchronize(ctx->stream);
     if (w->quants_alloc) cudaFree(w->quants_alloc);
     if (w->scales_alloc) cudaFree(w->scales_alloc);
-    if (w->mins_alloc) cudaFree(w->mins_alloc);
     delete w;
     return 0;
 }
@@ -467,8 +465,6 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
         // (value and rounding remainder), summed again in the epilogue.
         int split = x->bf16_exact ? 0 : 1;
         int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
-        // what the kernel wants beside the matrix is made on its first visit and kept in the handle
-        if (rc == 0) rc = gemm_prepare_weight(ctx, const_cast<dwim_b200_weight *>(w));
         if (rc) return rc;
         return gemm_large(ctx, v, (const __half *)x->shadow, n, split, out, aux, epilogue);
     }

@@ -46,7 +46,6 @@ struct dwim_b200_weight {
     dwim::WeightView v{};
     void *quants_alloc = nullptr;
     void *scales_alloc = nullptr;
-    void *mins_alloc = nullptr;      // see WeightView::mins
 };
 
 struct dwim_b200_ctx {
@@ -126,35 +125,6 @@ inline int fail(dwim_b200_ctx *ctx, int code, const char *fmt, ...) {
 // stream still runs (programmatic dependent launch).  Only for kernels that
 // call griddep_wait() (ptx.cuh) before they touch anything an earlier kernel
 // may read or write.  DWIM_B200_NO_PDL in the environment turns it off.
-template <typename... KArgs, typename... Args>
-inline cudaError_t launch_dependent_cluster(bool allow, unsigned cluster_x, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                            cudaStream_t stream, Args... args) {
-    static const bool on = getenv("DWIM_B200_NO_PDL") == nullptr;
-    const bool pdl = on && allow;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    unsigned n = 0;
-    if (pdl) {
-        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n].val.programmaticStreamSerializationAllowed = 1;
-        n++;
-    }
-    if (cluster_x > 1) {   // thread block clusters of cluster_x CTAs along x
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = cluster_x;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
-        n++;
-    }
-    cfg.attrs = attr;
-    cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, kern, args...);
-}
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_dependent(bool allow, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args... args) {

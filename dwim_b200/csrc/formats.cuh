@@ -73,7 +73,6 @@ struct WeightView {
     size_t qrow;             // bytes of quants in a row
     size_t qpitch;           // bytes from one row to the next
     size_t srow;             // f16 per row of scales
-    const uint8_t *mins;     // Q4_K: the tensor-core kernel's minimums operand, once that kernel has taken the matrix (gemm.cu)
 };
 
 // ---- f16 ------------------------------------------------------------------

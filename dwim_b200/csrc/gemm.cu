@@ -57,18 +57,13 @@ namespace {
 constexpr int TILE_M = 128;   // weight rows per CTA
 constexpr int BK = 64;        // K per stage: one 128-byte swizzled row of f16
 constexpr int KBLOCKS = 4;    // K blocks per unit = stages of the A ring: A stage index == K block within the unit
+constexpr int SCALE_SLOTS = 4;
 constexpr int N_WORKERS = 16;                                      // warps 2..17: four per TMEM lane quadrant
 constexpr int RAW_WARP = 2 + N_WORKERS;                            // the packed weights' producer
-constexpr int MINS_WARP = 3 + N_WORKERS;                           // the minimums' producer
-constexpr int GEMM_THREADS = (4 + N_WORKERS) * 32;
+constexpr int GEMM_THREADS = (3 + N_WORKERS) * 32;
 constexpr int RAW_BYTES = ((TILE_M * 144 + 1023) / 1024) * 1024;   // 18 KB
 constexpr int A_BYTES = TILE_M * BK * 2;                           // 16 KB
 constexpr int AMIN_BYTES = TILE_M * 16 * 4;                        // 8 KB: [K group of 8][row][16 B], four groups
-// The minimums' operand of a tile of 128 rows and one unit, as gemm_prepare_weight lays it out
-// beside the matrix: the rows' eight f16 values [row][16 B], their rounding remainders, and the
-// rows' scales s (f32).
-constexpr int MINS_GROUP = TILE_M * 16;
-constexpr int MINS_BLOB = 2 * MINS_GROUP + TILE_M * 4;
 constexpr int MAX_SMEM = 227 * 1024;
 constexpr int BAR_BYTES = 1024;
 
@@ -76,8 +71,6 @@ struct GemmArgs {
     size_t rows, n, ncols, units;   // weight rows, tokens, operand columns, 256-weight units of K
     int split;                      // 1: columns 2t, 2t+1 are token t's hi and lo halves
     OutSpec out;
-    const uint8_t *mins;            // the weights' minimums operand: [row tile][unit][MINS_BLOB]
-    const __half *means;            // the sub-block means: [unit][hi parts, lo parts][column][8 halves]
     const float *tok_scale;         // per token: the power of two its activations were divided by (prologue.cu)
     const float *aux;               // EPI_SWIGLU: the `up` product, token-major [n][rows]
     int epi;
@@ -92,24 +85,18 @@ struct GemmArgs {
 // stages, two raw stages, one stage of the minimums' operands, and a hand-over
 // per K block (a B stage is reloaded as soon as its own K block is done).
 template <int BN> struct Cfg {
-    static constexpr int CG = BN > 128 ? 2 : 1;                     // CTAs per tile of 128*CG rows: a pair at 256 columns
-    static constexpr int BN_CTA = BN / CG;                         // B columns (and their means) a CTA keeps
-    // One B stage per K block of a unit, never more: a K block's barrier (full) takes the producer's
-    // arrival for the next unit only after the MMAs of this unit's K block are done, which is what
-    // frees the stage when the ring is no longer than a unit.  (With six stages the arrival could
-    // come while the workers' of the unit before were still outstanding.)
-    static constexpr int B_STAGES = KBLOCKS;
-    static constexpr int RAW_STAGES = 3;
-    static constexpr int MIN_STAGES = 2;                           // stages of the minimums' A operand
+    static constexpr int B_STAGES = BN > 128 ? 3 : 4;
+    static constexpr int RAW_STAGES = BN > 128 ? 2 : 3;
+    static constexpr int MIN_STAGES = BN > 128 ? 1 : 2;
     static constexpr int HAND = BN > 128 ? 1 : 2;                  // K blocks per hand-over
     static constexpr int NHAND = KBLOCKS / HAND;
-    static constexpr int B_BYTES = BN_CTA * BK * 2;
-    static constexpr int BMIN_BYTES = BN_CTA * 16 * 2;             // [K group of 8][column][16 B]: the means' hi and lo parts
-    static constexpr int MEAN_BYTES = ((BMIN_BYTES + 1023) / 1024) * 1024;   // a stage of the means; always two of them
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int BMIN_BYTES = BN * 16 * 2;                 // [K group of 8][column][16 B]: the means' hi and lo parts
+    static constexpr int MIN_BYTES = AMIN_BYTES + ((BMIN_BYTES + 1023) / 1024) * 1024;
+    static constexpr int SCALE_BYTES = SCALE_SLOTS * TILE_M * 4;   // the unit's scale per row
     static constexpr int TOK_BYTES = BN * 4;                       // the columns' token scales, for the epilogue
-    static constexpr int A_RING = KBLOCKS * A_BYTES;
-    static constexpr int SMEM = BAR_BYTES + A_RING + B_STAGES * B_BYTES + MIN_STAGES * AMIN_BYTES + 2 * MEAN_BYTES +
-                                RAW_STAGES * RAW_BYTES + TOK_BYTES + 1024;   // + alignment slack
+    static constexpr int SMEM = BAR_BYTES + KBLOCKS * A_BYTES + B_STAGES * B_BYTES + MIN_STAGES * MIN_BYTES +
+                                RAW_STAGES * RAW_BYTES + SCALE_BYTES + TOK_BYTES + 1024;   // + alignment slack
     static_assert(SMEM <= MAX_SMEM, "the tile does not fit shared memory");
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;    // two accumulator buffers
     static constexpr int DRAIN_COLS = BN / 4 < 16 ? 16 : BN / 4;   // accumulator columns per draining warp
@@ -117,85 +104,46 @@ template <int BN> struct Cfg {
 };
 
 // ---- tcgen05 wrappers -----------------------------------------------------------
-// CG: the CTAs that share a tile (cta_group): 1, or 2 for a pair of CTAs of a cluster, whose
-// MMAs one thread of the pair's first CTA issues for both (M = 256: each CTA's 128 rows of A
-// from its own shared memory into its own tensor memory; B's columns half from each).
-template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    if (CG == 2) asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-    else asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
 }
-template <int CG>
 __device__ __forceinline__ void tmem_relinquish() {
-    if (CG == 2) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
-template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc]; f16 inputs, f32 accumulate.
-template <int CG>
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if (CG == 2)
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t"
-            "}\n" ::"r"(d_tmem),
-            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "setp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
-            "}\n" ::"r"(d_tmem),
-            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-            : "memory");
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
 }
 // The same with the descriptors given as (low word, shared high word) and the
 // accumulate flag fixed at compile time: the issuing thread has about one
 // instruction slot per five cycles, so every instruction between two MMAs counts.
-template <int ACC, int CG>
+template <int ACC>
 __device__ __forceinline__ void umma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc) {
-    if (CG == 2)
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            ".reg .b64 da, db;\n\t"
-            "setp.ne.b32 p, %5, 0;\n\t"
-            "mov.b64 da, {%1, %3};\n\t"
-            "mov.b64 db, {%2, %3};\n\t"
-            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t"
-            "}\n" ::"r"(d_tmem),
-            "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
-            : "memory");
-    else
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            ".reg .b64 da, db;\n\t"
-            "setp.ne.b32 p, %5, 0;\n\t"
-            "mov.b64 da, {%1, %3};\n\t"
-            "mov.b64 db, {%2, %3};\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t"
-            "}\n" ::"r"(d_tmem),
-            "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
-            : "memory");
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, {%6, %6, %6, %6}, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(0u)
+        : "memory");
 }
-// Arrive on an mbarrier once every MMA this thread issued so far has finished; for a pair,
-// on the barrier at the same place in both CTAs.
-template <int CG>
+// Arrive on an mbarrier once every MMA this thread issued so far has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    if (CG == 2)
-        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-                     "h"((uint16_t)3)
-                     : "memory");
-    else asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -271,15 +219,17 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) { return g * (1.0f
 // eight predicated stores per value stalled the main loop on instruction fetch).
 struct EmitTo {
     float *own;              // the first (or only) destination's element (token 0, this thread's row)
-    size_t offset;           // the same element's offset in every other destination (EMIT_SHARED)
+    size_t offset;           // the same element's offset in every other destination
+    size_t pitch;
+    const float *aux_row;
+    const OutSpec *out;
+    int world, epi;
 };
-enum EmitMode : int { EMIT_ONE = 0, EMIT_SHARED = 1, EMIT_SCATTER = 2 };
-template <int MODE>
-__device__ __forceinline__ EmitTo emit_to(const OutSpec &out, size_t row) {
+__device__ __forceinline__ EmitTo emit_to(const OutSpec &out, const float *aux, int epi, size_t row) {
     EmitTo e;
     float *d = out.dst[0];
     e.offset = out.row0 + row;
-    if (MODE == EMIT_SCATTER) {
+    if (out.scatter_per) {
         // the row's owner alone, its slot for this rank; the owner is picked by constant indices
         const size_t owner = row / out.scatter_per;
         e.offset = out.row0 + row - owner * out.scatter_per;
@@ -288,22 +238,26 @@ __device__ __forceinline__ EmitTo emit_to(const OutSpec &out, size_t row) {
             if ((size_t)p == owner) d = out.dst[p];
     }
     e.own = d + e.offset;
+    e.pitch = out.pitch;
+    e.aux_row = aux ? aux + row : nullptr;
+    e.out = &out;
+    e.world = out.scatter_per ? 1 : out.world;
+    e.epi = epi;
     return e;
 }
-// One finished element: the operator's epilogue, then the store.  Everything but the thread's
-// own pointer is read from the kernel's parameters (constant memory) where it is used.
-template <int MODE>
-__device__ __forceinline__ void gemm_emit(const EmitTo &e, float *o, const OutSpec &out, const float *aux, int epi, size_t rows,
-                                          size_t row, size_t t, float x) {
-    if (MODE == EMIT_ONE) {
-        if (epi == EPI_ADD) x += *o;
-        else if (epi == EPI_SWIGLU) x = silu_mul_f(x, aux[t * rows + row]);
+// One finished element: the operator's epilogue, then the store.
+template <bool SHARED>
+__device__ __forceinline__ void gemm_emit(const EmitTo &e, size_t rows, size_t t, float x) {
+    float *o = e.own + t * e.pitch;
+    if (!SHARED) {
+        if (e.epi == EPI_ADD) x += *o;
+        else if (e.epi == EPI_SWIGLU) x = silu_mul_f(x, e.aux_row[t * rows]);
     }
     *o = x;
-    if (MODE == EMIT_SHARED) {
+    if (SHARED) {
 #pragma unroll
         for (int p = 1; p < DWIM_MAX_WORLD; p++)
-            if (p < out.world) out.dst[p][e.offset + t * out.pitch] = x;
+            if (p < e.world) e.out->dst[p][e.offset + t * e.pitch] = x;
     }
 }
 
@@ -394,31 +348,10 @@ __device__ __forceinline__ void mins_q4k_terms(const uint4 &hdr, int part, float
     }
 }
 
-// The minimums' operand of a Q4_K matrix, computed once per matrix: for every tile of 128 rows and
-// every unit the rows' -(32*dmin/s)*m_j as f16 values [row][m_0..m_7] and rounding remainders,
-// and the rows' scales s.  Rows past the end come out as zeros.
-__global__ void __launch_bounds__(TILE_M) q4k_mins_kernel(const uint8_t *__restrict__ quants, size_t qpitch, size_t rows, size_t units,
-                                                          uint8_t *__restrict__ mins) {
-    const size_t tile = blockIdx.x, u = blockIdx.y, row = tile * TILE_M + threadIdx.x;
-    uint4 hdr = make_uint4(0u, 0u, 0u, 0u);
-    if (row < rows) hdr = *reinterpret_cast<const uint4 *>(quants + row * qpitch + u * 144);
-    const Q4kFold f = q4k_fold(hdr.x);
-    const float dmin32 = 32.0f * h2f_hi(hdr.x);
-    const float sc = f.zero ? dmin32 : h2f_lo(hdr.x) * __uint_as_float((uint32_t)(127 + f.e) << 23);
-    const float factor = f.zero ? -1.0f : -(dmin32 / sc);
-    uint32_t lo4[2][2], hi4[2][2];   // m_0..m_3 and m_4..m_7: [term][two values per word]
-    mins_q4k_terms(hdr, 0, factor, lo4);
-    mins_q4k_terms(hdr, 1, factor, hi4);
-    uint8_t *blob = mins + (tile * units + u) * MINS_BLOB;
-    *reinterpret_cast<uint4 *>(blob + threadIdx.x * 16) = make_uint4(lo4[0][0], lo4[0][1], hi4[0][0], hi4[0][1]);
-    *reinterpret_cast<uint4 *>(blob + MINS_GROUP + threadIdx.x * 16) = make_uint4(lo4[1][0], lo4[1][1], hi4[1][0], hi4[1][1]);
-    reinterpret_cast<float *>(blob + 2 * MINS_GROUP)[threadIdx.x] = sc;
-}
-
-template <int BN, int MODE>
+template <int BN, bool SHARED>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const __grid_constant__ GemmArgs a) {
+                const __grid_constant__ CUtensorMap tmap_m, const __grid_constant__ GemmArgs a) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzled tiles want 1024-byte alignment
@@ -427,37 +360,25 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const uint32_t rawfull0 = base + 96, rawempty0 = base + 128, accfull0 = base + 160, accempty0 = base + 176;
     const uint32_t tmem_slot = base + 192;
     const uint32_t astage0 = base + BAR_BYTES;
-    const uint32_t bstage0 = astage0 + C::A_RING;
+    const uint32_t bstage0 = astage0 + KBLOCKS * A_BYTES;
     const uint32_t min0 = bstage0 + C::B_STAGES * C::B_BYTES;
-    const uint32_t mean0 = min0 + C::MIN_STAGES * AMIN_BYTES;
-    const uint32_t raw0 = mean0 + 2 * C::MEAN_BYTES;
-    const uint32_t tok0 = raw0 + C::RAW_STAGES * RAW_BYTES;
+    const uint32_t raw0 = min0 + C::MIN_STAGES * C::MIN_BYTES;
+    const uint32_t scale0 = raw0 + C::RAW_STAGES * RAW_BYTES;
+    const uint32_t tok0 = scale0 + C::SCALE_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.x * TILE_M, col0 = blockIdx.y * BN;
     const int units = (int)a.units;
-    // A pair (CG = 2): the CTAs of a cluster of two take neighbouring row tiles and the same
-    // columns.  The first one (the leader) issues the MMAs for both; the barriers that gate
-    // an MMA (full, minfull, accempty) are the leader's and count both CTAs' arrivals, those an
-    // MMA's completion releases (empty, accfull) exist in both and are signalled together.
-    constexpr int CG = C::CG;
-    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
-    const bool lead = rank == 0;
-    const int colh = col0 + (int)rank * C::BN_CTA;                       // the first of the B columns this CTA keeps
-    const uint32_t full_lead = CG == 2 ? mapa_shared(full0, 0) : full0;  // the leader's barriers, as any CTA of the pair names them
-    const uint32_t minfull_lead = CG == 2 ? mapa_shared(minfull0, 0) : minfull0;
-    const uint32_t accempty_lead = CG == 2 ? mapa_shared(accempty0, 0) : accempty0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NHAND; s++) {
-            mbar_init(full0 + 8 * s, 1 + 4 * C::HAND * CG);   // the leader's expect_tx arrival + the hand-over's worker warps
-            mbar_init(empty0 + 8 * s, 1);                     // the MMA warp's commit
+            mbar_init(full0 + 8 * s, 1 + 4 * C::HAND);   // the producer's expect_tx arrival + the hand-over's worker warps
+            mbar_init(empty0 + 8 * s, 1);                // the MMA warp's commit
         }
         for (int s = 0; s < 2; s++) {
-            // the means' and the minimums' producers; at the leader also the other CTA's word that its own have landed
-            mbar_init(minfull0 + 8 * s, lead ? 2 + (CG - 1) : 2);
+            mbar_init(minfull0 + 8 * s, 1 + 8);          // the producer + the eight warps that write the minimums
             mbar_init(accfull0 + 8 * s, 1);              // also says that the unit's minimums and means have been read
-            mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS * CG);
+            mbar_init(accempty0 + 8 * s, 4 * C::DRAINERS);
         }
         for (int s = 0; s < C::RAW_STAGES; s++) {
             mbar_init(rawfull0 + 8 * s, 1);
@@ -466,12 +387,11 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc<CG>(tmem_slot, C::TMEM_COLS);
-        tmem_relinquish<CG>();
+        tmem_alloc(tmem_slot, C::TMEM_COLS);
+        tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
-    if (CG == 2) cluster_sync();   // both CTAs' barriers exist before either signals the other's
     tc_fence_after();
     const uint32_t tmem_base = lds32(tmem_slot);
     // Launched as a programmatic dependent: the next launch on the stream may begin as SMs
@@ -484,20 +404,8 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         // ------------------------------ TMA producer ------------------------------
         griddep_wait();   // the operand comes from the prologue kernel just ahead
         if (lane == 0) {
-            // this tile's columns of the means: two runs of 16 bytes per column and unit (hi parts, lo parts)
-            const uint32_t mean_cols = (size_t)colh < a.ncols ? (uint32_t)min((size_t)C::BN_CTA, a.ncols - (size_t)colh) : 0u;
             for (int u = 0; u < units; u++) {
-                // The unit's means first: they are read last, by the two MMAs that close the unit, and
-                // their stage (one of two) was last read by unit u - 2.  Loaded behind the B tiles, with
-                // a single stage, they were what every unit waited for.
-                if (u >= 2) mbar_wait_parked(accfull0 + 8 * (u & 1), ((u - 2) >> 1) & 1, a.status, 0x40u);
-                mbar_expect_tx(minfull0 + 8 * (u & 1), 2 * mean_cols * 16);
-                const uint32_t bm = mean0 + (u & 1) * C::MEAN_BYTES;
-                const __half *mu = a.means + ((size_t)(2 * u) * a.ncols + colh) * 8;
-                if (mean_cols) {
-                    bulk_g2s(bm, mu, mean_cols * 16, minfull0 + 8 * (u & 1));                                    // the hi parts
-                    bulk_g2s(bm + C::BN_CTA * 16, mu + a.ncols * 8, mean_cols * 16, minfull0 + 8 * (u & 1));     // the lo parts
-                }
+                const int ms = u % C::MIN_STAGES;
                 for (int h = 0; h < C::NHAND; h++) {
                     // B stage kb % B_STAGES was last read by K block kb - B_STAGES
                     for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
@@ -505,14 +413,21 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                         if (prev >= 0)
                             mbar_wait_parked(empty0 + 8 * ((prev % KBLOCKS) / C::HAND), (prev / KBLOCKS) & 1, a.status, 0x20u);
                     }
-                    if (lead) mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES * CG);   // both CTAs' halves
+                    mbar_expect_tx(full0 + 8 * h, C::HAND * C::B_BYTES);
                     for (int g = h * C::HAND; g < (h + 1) * C::HAND; g++) {
                         const int kb = KBLOCKS * u + g;
-                        const uint32_t dst = bstage0 + (kb % C::B_STAGES) * C::B_BYTES;
-                        if (CG == 2) tma_load_2d_pair(dst, &tmap_x, kb * BK, colh, full_lead + 8 * h);
-                        else tma_load_2d(dst, &tmap_x, kb * BK, col0, full0 + 8 * h);
+                        tma_load_2d(bstage0 + (kb % C::B_STAGES) * C::B_BYTES, &tmap_x, kb * BK, col0, full0 + 8 * h);
                     }
                 }
+                // the minimums' stage was last read by unit u - MIN_STAGES
+                if (u >= C::MIN_STAGES) {
+                    const int uu = u - C::MIN_STAGES;
+                    mbar_wait_parked(accfull0 + 8 * (uu & 1), (uu >> 1) & 1, a.status, 0x40u);
+                }
+                mbar_expect_tx(minfull0 + 8 * ms, C::BMIN_BYTES);
+                const uint32_t bm = min0 + ms * C::MIN_BYTES + AMIN_BYTES;
+                tma_load_2d(bm, &tmap_m, u * 16, col0, minfull0 + 8 * ms);                 // the means' hi parts
+                tma_load_2d(bm + BN * 16, &tmap_m, u * 16 + 8, col0, minfull0 + 8 * ms);   // and lo parts
             }
         }
     } else if (warp == RAW_WARP) {
@@ -527,42 +442,12 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 tma_load_2d(raw0 + rs * RAW_BYTES, &tmap_w, u * 144, row0, rawfull0 + 8 * rs);
             }
         }
-    } else if (warp == MINS_WARP) {
-        // ------------------------------ minimums' producer ------------------------------
-        // The A operand of the two MMAs that close a unit, prepared beside the matrix: the values
-        // go to K groups 0 and 1, the remainders to 2 and 3.  The stage was last read by unit
-        // u - MIN_STAGES.
-        if (lane == 0) {
-            const uint8_t *tile = a.mins + (size_t)blockIdx.x * units * MINS_BLOB;
-            for (int u = 0; u < units; u++) {
-                if (u >= C::MIN_STAGES) {
-                    const int uu = u - C::MIN_STAGES;
-                    mbar_wait_parked(accfull0 + 8 * (uu & 1), (uu >> 1) & 1, a.status, 0x1000u);
-                }
-                const uint32_t bar = minfull0 + 8 * (u & 1), am = min0 + (u % C::MIN_STAGES) * AMIN_BYTES;
-                const uint8_t *src = tile + (size_t)u * MINS_BLOB;
-                mbar_expect_tx(bar, 4 * MINS_GROUP);
-                bulk_g2s(am, src, MINS_GROUP, bar);
-                bulk_g2s(am + MINS_GROUP, src, MINS_GROUP, bar);
-                bulk_g2s(am + 2 * MINS_GROUP, src + MINS_GROUP, MINS_GROUP, bar);
-                bulk_g2s(am + 3 * MINS_GROUP, src + MINS_GROUP, MINS_GROUP, bar);
-            }
-        }
-    } else if (warp == 1 && !lead) {
-        // ------------------------------ the pair's second CTA: no MMAs to issue ------------------------------
-        // Its means and minimums arrive on its own barrier (a bulk copy signals the CTA it writes
-        // to); this warp passes each completion on to the leader's.
-        for (int u = 0; u < units; u++) {
-            mbar_wait_parked(minfull0 + 8 * (u & 1), (u >> 1) & 1, a.status, 0x200u);
-            if (lane == 0) mbar_arrive_cluster(minfull_lead + 8 * (u & 1));
-            __syncwarp();
-        }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         // The whole warp runs the loop (uniform control flow keeps addresses
         // and descriptors on the uniform data path) and one lane issues.  Units
         // are taken two at a time so that the accumulator buffer is static.
-        constexpr uint32_t idesc = idesc_f16(TILE_M * CG, BN);
+        constexpr uint32_t idesc = idesc_f16(TILE_M, BN);
         constexpr uint32_t desc_hi = 64u | (1u << 14) | (2u << 29);   // stride offset 1024 B, version 1, 128-byte swizzle
         const uint32_t a_lo = ((astage0 & 0x3ffffu) >> 4) | (1u << 16), b_lo = ((bstage0 & 0x3ffffu) >> 4) | (1u << 16);
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
@@ -587,25 +472,25 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                         if (lane == 0) {
 #pragma unroll
                             for (int k = 0; k < BK / 16; k++) {   // 32 bytes further along the swizzled row per K=16
-                                if (g == 0 && k == 0) umma_f16_lo<0, CG>(s1, ad, bd, desc_hi, idesc);
-                                else umma_f16_lo<1, CG>(s1, ad + 2 * k, bd + 2 * k, desc_hi, idesc);
+                                if (g == 0 && k == 0) umma_f16_lo<0>(s1, ad, bd, desc_hi, idesc);
+                                else umma_f16_lo<1>(s1, ad + 2 * k, bd + 2 * k, desc_hi, idesc);
                             }
                         }
                         bs = bs + 1 == C::B_STAGES ? 0 : bs + 1;
                     }
-                    if (lane == 0) umma_commit<CG>(empty0 + 8 * h);   // the stages may be refilled once these finish
+                    if (lane == 0) umma_commit(empty0 + 8 * h);   // the stages may be refilled once these finish
                     __syncwarp();
                 }
                 const int ms = u % C::MIN_STAGES;
-                mbar_wait_parked(minfull0 + 8 * ab, upar, a.status, 0x200u);
+                mbar_wait_parked(minfull0 + 8 * ms, (u / C::MIN_STAGES) & 1, a.status, 0x200u);
                 tc_fence_after();
                 if (lane == 0) {
                     // the minimums: terms (hi, hi | lo, lo) against the means' (hi, lo) twice
-                    const uint32_t am = min0 + ms * AMIN_BYTES;
-                    const uint64_t bdm = smem_desc_plain(mean0 + ab * C::MEAN_BYTES, C::BN_CTA * 16);
-                    umma_f16<CG>(s1, smem_desc_plain(am, TILE_M * 16), bdm, idesc, 1);
-                    umma_f16<CG>(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), bdm, idesc, 1);
-                    umma_commit<CG>(accfull0 + 8 * ab);     // the unit's sum is complete
+                    const uint32_t am = min0 + ms * C::MIN_BYTES;
+                    const uint64_t bdm = smem_desc_plain(am + AMIN_BYTES, BN * 16);
+                    umma_f16(s1, smem_desc_plain(am, TILE_M * 16), bdm, idesc, 1);
+                    umma_f16(s1, smem_desc_plain(am + 2 * TILE_M * 16, TILE_M * 16), bdm, idesc, 1);
+                    umma_commit(accfull0 + 8 * ab);     // the unit's sum is complete
                 }
                 __syncwarp();
             }
@@ -622,19 +507,17 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         const bool drains = g < C::DRAINERS;
         const uint32_t drain_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * C::DRAIN_COLS;
         const uint32_t a_row_sw = (astage0 + g * A_BYTES + rl * 128) | ((rl & 7) << 4);
-        // the row's scale of each unit, read a unit ahead of its drain
-        const float *scales = reinterpret_cast<const float *>(a.mins + (size_t)blockIdx.x * units * MINS_BLOB + 2 * MINS_GROUP) + rl;
-        float scale_of = 0.0f;              // of the unit that is drained next
         uint64_t acc2[C::DRAIN_COLS / 2];   // the row's sums, two columns per packed pair
 #pragma unroll
         for (int j = 0; j < C::DRAIN_COLS / 2; j++) acc2[j] = 0ull;
 
         auto drain = [&](int u) {
             const int ab = u & 1;
-            // the unit's sum is complete
+            // the unit's sum is complete; its last MMAs waited for the minimums'
+            // stage, which the row scales were written before
             mbar_wait_parked(accfull0 + 8 * ab, (u >> 1) & 1, a.status, 0x4000u);
             tc_fence_after();
-            const uint32_t sc = __float_as_uint(scale_of);
+            const uint32_t sc = __float_as_uint(lds32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4));
             const uint64_t sc2 = pack2(sc, sc);
 #pragma unroll
             for (int c = 0; c < C::DRAIN_COLS / 16; c++) {
@@ -646,15 +529,11 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                if (CG == 2) mbar_arrive_cluster(accempty_lead + 8 * ab);
-                else mbar_arrive(accempty0 + 8 * ab);
-            }
+            if (lane == 0) mbar_arrive(accempty0 + 8 * ab);
         };
 
         for (int u = 0; u < units; u++) {
-            const int rs = u % C::RAW_STAGES;
-            const float scale_u = __ldg(scales + (size_t)u * (MINS_BLOB / 4));
+            const int rs = u % C::RAW_STAGES, ms = u % C::MIN_STAGES;
             mbar_wait_parked(rawfull0 + 8 * rs, (u / C::RAW_STAGES) & 1, a.status, 0x400u);
             const uint32_t raw_row = raw0 + rs * RAW_BYTES + rl * 144;
             const uint4 hdr = lds128(raw_row);
@@ -662,16 +541,34 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
             load_q4k_block(hdr, raw_row, g, blk);
             mbar_wait_parked(empty0 + 8 * (g / C::HAND), (u & 1) ^ 1, a.status, 0x800u);   // the MMAs that read this stage are done
             store_q4k_block(blk, a_row_sw);
-            fence_async_smem();      // the tensor core reads shared memory through the async proxy
+            fence_async_smem();          // the tensor core reads shared memory through the async proxy
             __syncwarp();
-            if (lane == 0) {
-                if (CG == 2) mbar_arrive_cluster(full_lead + 8 * (g / C::HAND));
-                else mbar_arrive(full0 + 8 * (g / C::HAND));
+            if (lane == 0) mbar_arrive(full0 + 8 * (g / C::HAND));
+            if (g >= 2) {
+                // the minimums' A operand [K group][row][16 B]: groups (hi, hi, lo, lo) of the
+                // two f16 terms of -(32*dmin/s)*m_j; K block 2's warp writes m_0..m_3, K block 3's m_4..m_7
+                if (u >= C::MIN_STAGES) {   // the unit that used this stage last has read its minimums
+                    const int uu = u - C::MIN_STAGES;
+                    mbar_wait_parked(accfull0 + 8 * (uu & 1), (uu >> 1) & 1, a.status, 0x1000u);
+                }
+                const Q4kFold f = q4k_fold(hdr.x);
+                const float dmin32 = 32.0f * h2f_hi(hdr.x);
+                const float sc = f.zero ? dmin32 : h2f_lo(hdr.x) * __uint_as_float((uint32_t)(127 + f.e) << 23);
+                uint32_t b[2][2];
+                mins_q4k_terms(hdr, g - 2, f.zero ? -1.0f : -(dmin32 / sc), b);
+                const uint32_t am = min0 + ms * C::MIN_BYTES + rl * 16 + (g - 2) * 8;
+                sts64(am, b[0][0], b[0][1]);
+                sts64(am + TILE_M * 16, b[0][0], b[0][1]);
+                sts64(am + 2 * TILE_M * 16, b[1][0], b[1][1]);
+                sts64(am + 3 * TILE_M * 16, b[1][0], b[1][1]);
+                if (g == 2) sts32f(scale0 + ((u % SCALE_SLOTS) * TILE_M + rl) * 4, sc);
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(minfull0 + 8 * ms);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(rawempty0 + 8 * rs);
             if (drains && u > 0) drain(u - 1);
-            scale_of = scale_u;
         }
         if (drains) {
             griddep_wait();   // the kernel ahead may still read or write `out` and `aux`
@@ -683,70 +580,43 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
                 sts32f(tok0 + (g * C::DRAIN_COLS + j) * 4, t < a.n ? a.tok_scale[t] : 1.0f);
             }
             __syncwarp();
-            drain(units - 1);
             // nothing to multiply by for activations of the usual range: every scale is one
             const uint32_t tk = tok0 + g * C::DRAIN_COLS * 4;
             bool ones = true;
             for (int j = lane; j < C::DRAIN_COLS; j += 32) ones = ones && lds32f(tk + j * 4) == 1.0f;
             const bool scaled = !__all_sync(0xffffffffu, ones);
+            drain(units - 1);
             float acc[C::DRAIN_COLS];
 #pragma unroll
             for (int j = 0; j < C::DRAIN_COLS / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
-            int nvals = C::DRAIN_COLS;   // values per row: one per token
-            if (a.split) {
-#pragma unroll
-                for (int j = 0; j < C::DRAIN_COLS / 2; j++) acc[j] = acc[2 * j] + acc[2 * j + 1];
-                nvals = C::DRAIN_COLS / 2;
-            }
             const size_t row = (size_t)row0 + rl;
-            const bool ok = row < a.rows;
-            const size_t t0 = ((size_t)col0 + g * C::DRAIN_COLS) >> (a.split ? 1 : 0);
-            const EmitTo to = emit_to<MODE>(a.out, ok ? row : 0);
-            const size_t pitch = a.out.pitch;
-            float *o = to.own + t0 * pitch;
-            if (MODE == EMIT_ONE && a.epi == EPI_STORE && !scaled && t0 + nvals <= a.n) {
-                // The usual case, a whole tile stored as it is, at three instructions a value: the
-                // stores of a tile were 8 us of instructions (address, bounds and epilogue tests for
-                // each value) on top of the memory system's 2.5 us.
+            if (row < a.rows) {
+                const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
+                const EmitTo to = emit_to(a.out, a.aux, a.epi, row);
+                const size_t n = a.n, rows = a.rows;
+                if (scaled) {   // the tokens' powers of two
+#pragma unroll
+                    for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] *= lds32f(tk + j * 4);
+                }
                 if (a.split) {
 #pragma unroll
-                    for (int j = 0; j < C::DRAIN_COLS / 2; j++) {
-                        if (ok) *o = acc[j];
-                        o += pitch;
+                    for (int j = 0; j < C::DRAIN_COLS; j += 2) {
+                        const size_t t = (cbase + j) >> 1;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j] + acc[j + 1]);
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < C::DRAIN_COLS; j++) {
-                        if (ok) *o = acc[j];
-                        o += pitch;
+                        const size_t t = cbase + j;
+                        if (t < n) gemm_emit<SHARED>(to, rows, t, acc[j]);
                     }
-                }
-            } else {
-                // Everything else sixteen values at a time from the front of the array, which then
-                // moves down by sixteen: the loop stays a loop and its code small.
-#pragma unroll 1
-                for (int c = 0; c < nvals; c += 16) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        if (j < C::DRAIN_COLS) {
-                            float x = acc[j];
-                            if (scaled) x *= lds32f(tk + ((c + j) << (a.split ? 1 : 0)) * 4);
-                            const size_t t = t0 + c + j;
-                            if (ok && c + j < nvals && t < a.n) gemm_emit<MODE>(to, o, a.out, a.aux, a.epi, a.rows, row, t, x);
-                            o += pitch;
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j + 16 < C::DRAIN_COLS; j++) acc[j] = acc[j + 16];
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    // neither CTA of a pair leaves while the other may still signal its barriers or read its operands
-    if (CG == 2) cluster_sync();
-    if (warp == 1) tmem_dealloc<CG>(tmem_base, C::TMEM_COLS);
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
 // ---- the dense pair kernel: Q8_0 and Q6_K above the small-M kernel's range --------------------
@@ -782,7 +652,7 @@ template <int BN> struct PairCfg {
 };
 constexpr int PAIR_THREADS = 6 * 32;
 
-template <int BN, int MODE>
+template <int BN, bool SHARED>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
                  const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ PairArgs a) {
@@ -803,8 +673,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        tmem_alloc<1>(tmem_slot, BN < 32 ? 32 : BN);
-        tmem_relinquish<1>();
+        tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+        tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
@@ -838,12 +708,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
             if (lane == 0) {
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++) {
-                    if (kb == 0 && k == 0) umma_f16_lo<0, 1>(tm, hi_lo, b_lo, desc_hi, idesc);
-                    else umma_f16_lo<1, 1>(tm, hi_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
-                    umma_f16_lo<1, 1>(tm, lo_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                    if (kb == 0 && k == 0) umma_f16_lo<0>(tm, hi_lo, b_lo, desc_hi, idesc);
+                    else umma_f16_lo<1>(tm, hi_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
+                    umma_f16_lo<1>(tm, lo_lo + 2 * k, b_lo + 2 * k, desc_hi, idesc);
                 }
-                umma_commit<1>(empty0 + 8 * s);
-                if (kb == kblocks - 1) umma_commit<1>(accfull);
+                umma_commit(empty0 + 8 * s);
+                if (kb == kblocks - 1) umma_commit(accfull);
             }
             __syncwarp();
         }
@@ -862,7 +732,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
         mbar_wait_parked(accfull, 0, a.status, 0x400000u);
         tc_fence_after();
         // destinations of this thread's row, by constant index (see EmitTo)
-        const EmitTo to = emit_to<MODE>(a.out, a.panel_row0 + prow);
+        const EmitTo to = emit_to(a.out, a.aux, a.epi, a.panel_row0 + prow);
         const size_t n = a.n, rows = a.rows;
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
@@ -876,20 +746,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 16; j += 2) {
                     const size_t t = (cbase + j) >> 1;
-                    if (t < n) gemm_emit<MODE>(to, to.own + t * a.out.pitch, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    if (t < n) gemm_emit<SHARED>(to, rows, t, (__uint_as_float(v[j]) + __uint_as_float(v[j + 1])) * rs * lds32f(tok0 + (c * 16 + j) * 4));
                 }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     const size_t t = cbase + j;
-                    if (t < n) gemm_emit<MODE>(to, to.own + t * a.out.pitch, a.out, a.aux, a.epi, rows, a.panel_row0 + prow, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
+                    if (t < n) gemm_emit<SHARED>(to, rows, t, __uint_as_float(v[j]) * rs * lds32f(tok0 + (c * 16 + j) * 4));
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc<1>(tmem_base, BN < 32 ? 32 : BN);
+    if (warp == 1) tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
 }
 
 // A row of W decoded, scaled by its own power of two and written as two f16 terms, each run of
@@ -981,32 +851,33 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
                 const float *aux, int epi) {
     using C = Cfg<BN>;
     const size_t ncols = n * (split ? 2 : 1), units = w.cols / 256;
-    CUtensorMap tw, tx;
+    CUtensorMap tw, tx, tm;
     int rc;
     // packed weights as bytes: [rows][qpitch], box [128 rows][144 bytes]; rows past the end read as zero blocks
     if ((rc = encode_2d(ctx, &tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, w.quants, w.qpitch, w.rows, w.qpitch, 144, TILE_M,
                         CU_TENSOR_MAP_SWIZZLE_NONE, "weight")))
         return rc;
     // activations: [ncols][K] f16, box [BN][64], 128-byte swizzle; columns past the end read as zero
-    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, C::BN_CTA,
+    if ((rc = encode_2d(ctx, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand, w.cols, ncols, w.cols * 2, BK, BN,
                         CU_TENSOR_MAP_SWIZZLE_128B, "activation")))
         return rc;
+    // sub-block means: [ncols][units*16] f16, box [BN][8]
+    if ((rc = encode_2d(ctx, &tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, operand + ncols * w.cols, units * 16, ncols, units * 32, 8,
+                        BN, CU_TENSOR_MAP_SWIZZLE_NONE, "means")))
+        return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
-    GemmArgs a{w.rows, n, ncols, units, split, out, w.mins, operand + ncols * w.cols, tok_scale, aux, epi, ctx->status};
-    // a result shared by several ranks' copies, or scattered to its rows' owners, takes an instantiation of its own
-    const int mode = out.scatter_per ? EMIT_SCATTER : out.world > 1 ? EMIT_SHARED : EMIT_ONE;
-    auto kern = mode == EMIT_SCATTER ? gemm_q4k_kernel<BN, EMIT_SCATTER> : mode == EMIT_SHARED ? gemm_q4k_kernel<BN, EMIT_SHARED>
-                                                                                              : gemm_q4k_kernel<BN, EMIT_ONE>;
-    static bool configured[64][3] = {};
-    if (!configured[ctx->device & 63][mode]) {
+    GemmArgs a{w.rows, n, ncols, units, split, out, tok_scale, aux, epi, ctx->status};
+    // a result shared by several ranks' copies takes the instantiation that stores to all of them
+    const bool shared = out.world > 1 && !out.scatter_per;
+    auto kern = shared ? gemm_q4k_kernel<BN, true> : gemm_q4k_kernel<BN, false>;
+    static bool configured[64][2] = {};
+    if (!configured[ctx->device & 63][shared]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured[ctx->device & 63][mode] = true;
+        configured[ctx->device & 63][shared] = true;
     }
-    // row tiles in whole pairs where two CTAs share a tile; a tile past the last row reads zeros and stores nothing
-    const size_t row_tiles = ((w.rows + TILE_M - 1) / TILE_M + C::CG - 1) / C::CG * C::CG;
-    dim3 grid((unsigned)row_tiles, (unsigned)((ncols + BN - 1) / BN));
+    dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
-    DWIM_CUDA(ctx, launch_dependent_cluster(dependent, C::CG, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, a));
+    DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, tm, a));
     ctx->weights_written = false;
     DWIM_LAUNCHED(ctx);
     return 0;
@@ -1033,13 +904,12 @@ int launch_pair(dwim_b200_ctx *ctx, const WeightView &w, size_t r0, size_t nr, c
         return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
     PairArgs a{w.rows, r0, nr, n, ncols, w.cols / BK, split, out, ctx->pair_scale, tok_scale, aux, epi, ctx->status};
-    const int mode = out.scatter_per ? EMIT_SCATTER : out.world > 1 ? EMIT_SHARED : EMIT_ONE;
-    auto kern = mode == EMIT_SCATTER ? gemm_pair_kernel<BN, EMIT_SCATTER> : mode == EMIT_SHARED ? gemm_pair_kernel<BN, EMIT_SHARED>
-                                                                                              : gemm_pair_kernel<BN, EMIT_ONE>;
-    static bool configured[64][3] = {};
-    if (!configured[ctx->device & 63][mode]) {
+    const bool shared = out.world > 1 && !out.scatter_per;
+    auto kern = shared ? gemm_pair_kernel<BN, true> : gemm_pair_kernel<BN, false>;
+    static bool configured[64][2] = {};
+    if (!configured[ctx->device & 63][shared]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured[ctx->device & 63][mode] = true;
+        configured[ctx->device & 63][shared] = true;
     }
     dim3 grid((unsigned)((nr + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     DWIM_CUDA(ctx, launch_dependent(true, kern, grid, dim3(PAIR_THREADS), (size_t)C::SMEM, ctx->stream, th, tl, tx, a));
@@ -1054,21 +924,6 @@ int launch_pair(dwim_b200_ctx *ctx, const WeightView &w, size_t r0, size_t nr, c
 bool gemm_supports(const WeightView &w) {
     if (w.cols % 256) return false;
     return w.fmt == Q4_K || ((w.fmt == Q6_K || w.fmt == Q8_0) && w.cols <= 12288);
-}
-
-// A Q4_K matrix's minimums operand (q4k_mins_kernel), made when the tensor-core kernel first takes
-// the matrix and kept with it: a quarter of the matrix's own bytes.
-int gemm_prepare_weight(dwim_b200_ctx *ctx, dwim_b200_weight *w) {
-    if (w->v.fmt != Q4_K || w->mins_alloc || w->v.rows == 0 || w->v.cols == 0) return 0;
-    const size_t tiles = ((w->v.rows + TILE_M - 1) / TILE_M + 1) / 2 * 2, units = w->v.cols / 256;   // whole pairs of tiles
-    DWIM_CUDA(ctx, cudaMalloc(&w->mins_alloc, tiles * units * MINS_BLOB));
-    q4k_mins_kernel<<<dim3((unsigned)tiles, (unsigned)units), TILE_M, 0, ctx->stream>>>(w->v.quants, w->v.qpitch, w->v.rows, units,
-                                                                                      (uint8_t *)w->mins_alloc);
-    DWIM_CUDA(ctx, cudaGetLastError());
-    DWIM_LAUNCHED(ctx);
-    w->v.mins = (const uint8_t *)w->mins_alloc;
-    ctx->weights_written = true;   // the next launch reads what this one writes before it waits for the kernels ahead
-    return 0;
 }
 
 int gemm_large(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, size_t n, int split, const OutSpec &out,

@@ -201,7 +201,7 @@ __device__ __forceinline__ float block_sum_256(float v, float *scratch8) {
 // 64 a unit, the block four units.
 template <bool NORM, bool ALIGNED>   // ALIGNED: x (and xout, weight) are 16-byte aligned (a wrapped caller's pointer need not be)
 __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *x, const float *__restrict__ weight, float eps,
-                                                           float *xout, size_t cols, int split,
+                                                           float *xout, size_t cols, size_t units, int split,
                                                            __half *__restrict__ x16, __half *__restrict__ means,
                                                            float *__restrict__ tok_scale) {
     // as the small-M prologues: let the product's kernel begin (it streams weights first),
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *x, const
     e = amax > 0.0f ? max(-100, min(100, e)) : 0;
     const float down = __uint_as_float((uint32_t)(127 - e) << 23);
     if (k == 0) tok_scale[t] = __uint_as_float((uint32_t)(127 + e) << 23);
-    const size_t col = split ? 2 * (size_t)t : (size_t)t, ncols = (size_t)gridDim.x * (split ? 2 : 1);
+    const size_t col = split ? 2 * (size_t)t : (size_t)t;
     for (size_t at = (size_t)k * 4; at < cols; at += 1024) {
         const float4 v = *reinterpret_cast<float4 *>(row + at);
         const float f[4] = {v.x * down, v.y * down, v.z * down, v.w * down};
@@ -278,15 +278,15 @@ __global__ void __launch_bounds__(256) gemm_operand_kernel(const float *x, const
             const size_t u = at >> 8;
             const int j = (int)(at & 255) >> 5;
             const float mh = sh * (1.0f / 32.0f), ml = sl * (1.0f / 32.0f);
-            // [unit][hi parts, lo parts][column][8 sub-blocks]: a tile's columns of a unit are two runs of bytes
-            __half *m = means + ((2 * u) * ncols + col) * 8;
+            __half *m = means + (col * units + u) * 16;
             const __half a = to_f16_clamped(mh);
             m[j] = a;
-            m[ncols * 8 + j] = to_f16_clamped(mh - __half2float(a));
+            m[8 + j] = to_f16_clamped(mh - __half2float(a));
             if (split) {
+                __half *m2 = m + units * 16;
                 const __half b = to_f16_clamped(ml);
-                m[8 + j] = b;
-                m[ncols * 8 + 8 + j] = to_f16_clamped(ml - __half2float(b));
+                m2[j] = b;
+                m2[8 + j] = to_f16_clamped(ml - __half2float(b));
             }
         }
     }
@@ -310,7 +310,7 @@ int build_gemm_operand(dwim_b200_ctx *ctx, const float *x, size_t n, size_t cols
                      : (aligned ? gemm_operand_kernel<false, true> : gemm_operand_kernel<false, false>);
     if (smem > 48 * 1024) DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     DWIM_CUDA(ctx, launch_dependent(!ctx->weights_written, kern, dim3((unsigned)n), dim3(256), smem, ctx->stream, x, weight, eps,
-                                    xout, cols, split, out, means, tok_scale));
+                                    xout, cols, units, split, out, means, tok_scale));
     DWIM_LAUNCHED(ctx);
     return 0;
 }

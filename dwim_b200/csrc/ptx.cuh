@@ -169,37 +169,4 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
         : "memory");
 }
 
-// ---- a pair of CTAs on one tile (clusters of two, tcgen05 cta_group::2) ------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// The address, in the cluster's shared window, of CTA `rank`'s copy of a shared variable.
-__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
-    return r;
-}
-// Arrive on a barrier of any CTA of the cluster (an address from mapa_shared).  Release at CTA
-// scope, the default: what the arrival publishes here is this CTA's own shared or tensor memory,
-// which the pair's tensor cores read in place.  (A cluster-scope release cost each arrival
-// about a microsecond.)
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// All threads of all CTAs of the cluster.
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// The tiled copy into this CTA's shared memory whose bytes count on a barrier of the pair's
-// other CTA (`bar_cluster` from mapa_shared): each CTA of a pair brings its half of an operand,
-// the leader's barrier sees both.  No multicast: every CTA fetches what it keeps.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap, int c0, int c1, uint32_t bar_cluster) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(tmap), "r"(c0), "r"(c1), "r"(bar_cluster)
-        : "memory");
-}
-
 }  // namespace dwim
