@@ -95,6 +95,7 @@ int dwim_b200_open_on_stream(int device, void *cuda_stream, dwim_b200_ctx **out)
 }
 
 int dwim_b200_close(dwim_b200_ctx *ctx) {
+    DWIM_DEVICE(ctx);
     if (!ctx) return DWIM_B200_EINVAL;
     cudaSetDevice(ctx->device);
     if (ctx->stream || !ctx->stream_owned) cudaStreamSynchronize(ctx->stream);
@@ -114,12 +115,14 @@ int dwim_b200_close(dwim_b200_ctx *ctx) {
 const char *dwim_b200_last_error(const dwim_b200_ctx *ctx) { return ctx ? ctx->err : g_open_error; }
 
 int dwim_b200_name(const dwim_b200_ctx *ctx, char *buf, size_t cap) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf || cap == 0) return DWIM_B200_EINVAL;
     snprintf(buf, cap, "%s", ctx->name);
     return 0;
 }
 
 int dwim_b200_memory(const dwim_b200_ctx *ctx, uint64_t *free_bytes) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !free_bytes) return DWIM_B200_EINVAL;
     size_t f = 0, t = 0;
     cudaSetDevice(ctx->device);
@@ -142,6 +145,7 @@ static int check_status(dwim_b200_ctx *ctx) {
 }
 
 int dwim_b200_sync(dwim_b200_ctx *ctx) {
+    DWIM_DEVICE(ctx);
     if (!ctx) return DWIM_B200_EINVAL;
     return check_status(ctx);
 }
@@ -149,6 +153,7 @@ int dwim_b200_sync(dwim_b200_ctx *ctx) {
 void *dwim_b200_stream(const dwim_b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
 
 int dwim_b200_status(dwim_b200_ctx *ctx, uint32_t *status) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !status) return DWIM_B200_EINVAL;
     DWIM_CUDA(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     DWIM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -159,12 +164,14 @@ int dwim_b200_status(dwim_b200_ctx *ctx, uint32_t *status) {
 uint64_t dwim_b200_launches(const dwim_b200_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
 int dwim_b200_timer_begin(dwim_b200_ctx *ctx) {
+    DWIM_DEVICE(ctx);
     if (!ctx) return DWIM_B200_EINVAL;
     DWIM_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     return 0;
 }
 
 int dwim_b200_timer_end(dwim_b200_ctx *ctx, float *ms) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !ms) return DWIM_B200_EINVAL;
     DWIM_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
     DWIM_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
@@ -175,6 +182,7 @@ int dwim_b200_timer_end(dwim_b200_ctx *ctx, float *ms) {
 // ---- buffers ----------------------------------------------------------------
 
 int dwim_b200_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out) return DWIM_B200_EINVAL;
     *out = nullptr;
     dwim_b200_buffer *b = new (std::nothrow) dwim_b200_buffer();
@@ -196,6 +204,7 @@ int dwim_b200_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out) {
 }
 
 int dwim_b200_wrap(dwim_b200_ctx *ctx, float *device_ptr, size_t len, dwim_b200_buffer **out) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out) return DWIM_B200_EINVAL;
     *out = nullptr;
     REQUIRE(ctx, device_ptr || len == 0, DWIM_B200_EINVAL, "wrap: null device pointer");
@@ -210,6 +219,7 @@ int dwim_b200_wrap(dwim_b200_ctx *ctx, float *device_ptr, size_t len, dwim_b200_
 }
 
 int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t len) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len <= buf->cap, DWIM_B200_EINVAL, "resize to %zu beyond the %zu allocated", len, buf->cap);
     buf->len = len;
@@ -218,6 +228,7 @@ int dwim_b200_resize(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t len) {
 }
 
 int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     buf->shadow_kind = SHADOW_NONE;
     buf->bf16_exact = false;
@@ -225,6 +236,7 @@ int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
 }
 
 int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     buf->shadow_kind = SHADOW_NONE;
     buf->bf16_exact = true;
@@ -232,6 +244,7 @@ int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
 }
 
 int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf || (!data && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == buf->len, DWIM_B200_EINVAL, "write of %zu floats to a buffer of %zu", len, buf->len);
     if (len) DWIM_CUDA(ctx, cudaMemcpyAsync(buf->data, data, len * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
@@ -246,6 +259,7 @@ __global__ void bf16_to_f32_kernel(const uint16_t *__restrict__ in, size_t n, fl
 }
 
 int dwim_b200_write_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const uint16_t *data, size_t len) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf || (!data && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == buf->len, DWIM_B200_EINVAL, "write of %zu values to a buffer of %zu", len, buf->len);
     buf->shadow_kind = SHADOW_NONE;
@@ -266,6 +280,7 @@ int dwim_b200_write_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const uint16
 }
 
 int dwim_b200_read(dwim_b200_ctx *ctx, const dwim_b200_buffer *buf, float *out, size_t len) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf || (!out && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == buf->len, DWIM_B200_EINVAL, "read of %zu floats from a buffer of %zu", len, buf->len);
     if (len) DWIM_CUDA(ctx, cudaMemcpyAsync(out, buf->data, len * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
@@ -273,6 +288,7 @@ int dwim_b200_read(dwim_b200_ctx *ctx, const dwim_b200_buffer *buf, float *out, 
 }
 
 int dwim_b200_buffer_free(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     cudaStreamSynchronize(ctx->stream);
     if (buf->sh_world) shared_release(buf);
@@ -291,6 +307,7 @@ size_t dwim_b200_row_bytes(int fmt, size_t cols) { return file_row_bytes(fmt, co
 
 int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const void *blocks, size_t bytes,
                      dwim_b200_weight **out) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out) return DWIM_B200_EINVAL;
     *out = nullptr;
     REQUIRE(ctx, fmt == Q8_0 || fmt == Q4_K || fmt == Q6_K || fmt == BF16, DWIM_B200_EFORMAT, "unknown weight format %d", fmt);
@@ -349,6 +366,7 @@ int dwim_b200_upload(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, cons
 }
 
 int dwim_b200_weight_free(dwim_b200_ctx *ctx, dwim_b200_weight *w) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !w) return DWIM_B200_EINVAL;
     cudaStreamSynchronize(ctx->stream);
     if (w->quants_alloc) cudaFree(w->quants_alloc);
@@ -366,6 +384,7 @@ int dwim_b200_weight_shape(const dwim_b200_weight *w, int *fmt, size_t *rows, si
 }
 
 int dwim_b200_dequantize(dwim_b200_ctx *ctx, const dwim_b200_weight *w, float *out, size_t len) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !w || (!out && len)) return DWIM_B200_EINVAL;
     REQUIRE(ctx, len == w->v.rows * w->v.cols, DWIM_B200_EINVAL, "dequantize: %zu floats for a [%zu, %zu] matrix", len,
             w->v.rows, w->v.cols);
@@ -384,6 +403,7 @@ int dwim_b200_dequantize(dwim_b200_ctx *ctx, const dwim_b200_weight *w, float *o
 
 int dwim_b200_quantize(dwim_b200_ctx *ctx, int fmt, size_t rows, size_t cols, const float *weights, void *blocks,
                        size_t bytes) {
+    DWIM_DEVICE(ctx);
     if (!ctx) return DWIM_B200_EINVAL;
     REQUIRE(ctx, fmt == Q8_0 || fmt == Q4_K || fmt == Q6_K, DWIM_B200_EFORMAT, "unknown weight format %d", fmt);
     size_t rb = file_row_bytes(fmt, cols);
@@ -510,6 +530,7 @@ int product_into(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const d
 extern "C" {
 
 int dwim_b200_matmul(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w, dwim_b200_buffer *x) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out || !w || !x) return DWIM_B200_EINVAL;
     int rc = product(ctx, out_local(out->data, w->v.rows), out->len, w, x, nullptr, EPI_STORE, "matmul");
     out->shadow_kind = SHADOW_NONE;
@@ -519,6 +540,7 @@ int dwim_b200_matmul(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_
 
 int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *w, dwim_b200_buffer *x,
                             size_t row_begin, size_t total_rows) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out || !w || !x) return DWIM_B200_EINVAL;
     REQUIRE(ctx, out->sh_world >= 1, DWIM_B200_EINVAL, "matmul_gather: the output is not a connected shared buffer");
     REQUIRE(ctx, row_begin + w->v.rows <= total_rows, DWIM_B200_EINVAL, "matmul_gather: rows [%zu, %zu) of %zu", row_begin,
@@ -539,6 +561,7 @@ int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwi
 
 int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, const dwim_b200_weight *w, dwim_b200_buffer *input,
                          dwim_b200_buffer *scratch) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !x || !w || !input) return DWIM_B200_EINVAL;
     if (scratch) REQUIRE(ctx, scratch->len == x->len, DWIM_B200_EINVAL, "matmul_add: scratch of %zu for x of %zu", scratch->len, x->len);
     int rc = product(ctx, out_local(x->data, w->v.rows), x->len, w, input, nullptr, EPI_ADD, "matmul_add");
@@ -549,6 +572,7 @@ int dwim_b200_matmul_add(dwim_b200_ctx *ctx, dwim_b200_buffer *x, const dwim_b20
 
 int dwim_b200_swiglu(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_weight *gate, const dwim_b200_weight *up,
                      dwim_b200_buffer *x, dwim_b200_buffer *scratch) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out || !gate || !up || !x || !scratch) return DWIM_B200_EINVAL;
     REQUIRE(ctx, gate->v.rows == up->v.rows && gate->v.cols == up->v.cols, DWIM_B200_EINVAL,
             "swiglu: gate is [%zu, %zu] but up is [%zu, %zu]", gate->v.rows, gate->v.cols, up->v.rows, up->v.cols);
@@ -604,6 +628,7 @@ __global__ void gather_rows_kernel(float *__restrict__ out, const float *__restr
 
 int dwim_b200_gather_rows(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *parts, size_t n, size_t rows,
                           int world, size_t align) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out || !parts || world <= 0 || align == 0) return DWIM_B200_EINVAL;
     size_t b0, e0;
     dwim_b200_shard_rows(rows, 0, world, align, &b0, &e0);

@@ -143,6 +143,13 @@ inline cudaError_t launch_dependent(bool allow, void (*kern)(KArgs...), dim3 gri
     return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
+// Every entry point works on its context's device, whatever device the calling thread had
+// current: an engine drives several GPUs from one thread, or one context from several threads.
+#define DWIM_DEVICE(ctx)                            \
+    do {                                            \
+        if (ctx) cudaSetDevice((ctx)->device);      \
+    } while (0)
+
 #define DWIM_LAUNCHED(ctx)                                                                     \
     do {                                                                                       \
         (ctx)->launches++;                                                                     \

@@ -175,6 +175,7 @@ int matmul_bf16(dwim_b200_ctx *ctx, const WeightView &w, const float *x, size_t 
 
 extern "C" int dwim_b200_normalize(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *x,
                                    const dwim_b200_buffer *weight, size_t len, float eps) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !out || !x || !weight) return DWIM_B200_EINVAL;
     const size_t dim = weight->len;
     // gpu/cuda/mod.rs:1184-1185
@@ -215,6 +216,7 @@ extern "C" int dwim_b200_normalize(dwim_b200_ctx *ctx, dwim_b200_buffer *out, co
 }
 
 extern "C" int dwim_b200_argmax(dwim_b200_ctx *ctx, const dwim_b200_buffer *logits, size_t len, uint32_t *out, size_t n) {
+    DWIM_DEVICE(ctx);
     if (!ctx || !logits || (!out && n)) return DWIM_B200_EINVAL;
     if (len == 0 || n * len != logits->len || len > 0xffffffffull || n > 65535)
         return fail(ctx, DWIM_B200_EINVAL, "argmax: %zu rows of %zu logits in a buffer of %zu", n, len, logits->len);

@@ -125,6 +125,7 @@ void peer_release(dwim_b200_ctx *ctx) {
 }  // namespace dwim
 
 extern "C" int dwim_b200_peer_create(dwim_b200_ctx *ctx, int world, int rank, size_t cap, void *handle, size_t handle_bytes) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !handle) return DWIM_B200_EINVAL;
     if (world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || cap == 0)
@@ -157,6 +158,7 @@ extern "C" int dwim_b200_peer_create(dwim_b200_ctx *ctx, int world, int rank, si
 extern "C" size_t dwim_b200_peer_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
 
 extern "C" int dwim_b200_peer_connect(dwim_b200_ctx *ctx, const void *handles, size_t handle_bytes) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !handles) return DWIM_B200_EINVAL;
     PeerState *p = state(ctx);
@@ -175,6 +177,7 @@ extern "C" int dwim_b200_peer_connect(dwim_b200_ctx *ctx, const void *handles, s
 }
 
 extern "C" int dwim_b200_peer_allreduce(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, size_t n) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     PeerState *p = state(ctx);
@@ -274,6 +277,7 @@ void shared_release(dwim_b200_buffer *b) {
 }  // namespace dwim
 
 extern "C" int dwim_b200_shared_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_buffer **out, void *handle, size_t handle_bytes) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !out || !handle) return DWIM_B200_EINVAL;
     *out = nullptr;
@@ -302,6 +306,7 @@ extern "C" int dwim_b200_shared_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b200_
 
 extern "C" int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank, const void *handles,
                                         size_t handle_bytes) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     if (world < 1 || world > DWIM_MAX_WORLD || rank < 0 || rank >= world)
@@ -335,6 +340,7 @@ extern "C" int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
 }
 
 extern "C" int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !buf) return DWIM_B200_EINVAL;
     if (buf->sh_world < 1) return fail(ctx, DWIM_B200_EINVAL, "shared_barrier: not a connected shared buffer");
@@ -393,6 +399,7 @@ int product_into(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const d
 }
 
 extern "C" int dwim_b200_matmul_scatter(dwim_b200_ctx *ctx, dwim_b200_buffer *slots, const dwim_b200_weight *w, dwim_b200_buffer *x) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !slots || !w || !x) return DWIM_B200_EINVAL;
     if (slots->sh_world < 1) return fail(ctx, DWIM_B200_EINVAL, "matmul_scatter: the slots are not a connected shared buffer");
@@ -413,6 +420,7 @@ extern "C" int dwim_b200_matmul_scatter(dwim_b200_ctx *ctx, dwim_b200_buffer *sl
 }
 
 extern "C" int dwim_b200_reduce_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwim_b200_buffer *slots, size_t n, size_t rows) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !out || !slots) return DWIM_B200_EINVAL;
     if (out->sh_world < 1 || slots->sh_world != out->sh_world || slots->sh_rank != out->sh_rank)

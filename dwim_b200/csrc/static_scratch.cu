@@ -40,6 +40,7 @@ int static_scratch_prepare(dwim_b200_ctx *ctx) {
 }  // namespace dwim
 
 extern "C" int dwim_b200_matmul_static(dwim_b200_ctx *ctx, float *out, const dwim_b200_weight *w, const float *x, size_t n) {
+    DWIM_DEVICE(ctx);
     using namespace dwim;
     if (!ctx || !w) return DWIM_B200_EINVAL;
     const WeightView &v = w->v;

@@ -92,6 +92,23 @@ def _rank(rank: int, world: int, port: int, queue):
                 assert e.code == -6, e
             dev.sync()                                   # the status was cleared: usable again
             assert np.array_equal(dev.read(dev.buffer(np.arange(4, dtype=np.float32))), np.arange(4, dtype=np.float32))
+        # a context used from a thread that never chose a device (its current device is GPU 0): every
+        # entry point works on the context's own device
+        import threading
+        seen = {}
+
+        def from_thread():
+            try:
+                d2 = B200(rank)
+                v = np.arange(4096, dtype=np.float32) + rank
+                seen["ok"] = bool(np.array_equal(d2.read(d2.buffer(v)), v) and np.array_equal(dev.read(dev.buffer(v)), v))
+                d2.close()
+            except Exception as e:   # noqa: BLE001
+                seen["ok"] = repr(e)
+        th = threading.Thread(target=from_thread)
+        th.start()
+        th.join()
+        assert seen.get("ok") is True, seen
         dist.barrier()
         queue.put((rank, "ok"))
     except Exception as e:   # noqa: BLE001 - reported to the parent
