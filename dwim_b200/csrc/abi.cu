@@ -551,8 +551,8 @@ int dwim_b200_matmul_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out, const dwi
     o.row0 = row_begin;
     // this rank's copy first: the fused add / SwiGLU forms read it; the peers' follow
     o.dst[0] = out->data;
-    for (int r = 0, k = 1; r < out->sh_world; r++)
-        if (r != out->sh_rank) o.dst[k++] = out->sh_peer[r];
+    // the peers in ring order from this rank on: at any moment the ranks' stores head for different GPUs
+    for (int k = 1; k < out->sh_world; k++) o.dst[k] = out->sh_peer[(out->sh_rank + k) % out->sh_world];
     int rc = product(ctx, o, out->len, w, x, nullptr, EPI_STORE, "matmul_gather");
     out->shadow_kind = SHADOW_NONE;
     out->bf16_exact = false;

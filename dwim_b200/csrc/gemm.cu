@@ -348,10 +348,21 @@ __device__ __forceinline__ void mins_q4k_terms(const uint4 &hdr, int part, float
     }
 }
 
-template <int BN, bool SHARED>
+// One map per destination of a shared result, for the form of the kernel that writes it with TMA:
+// this rank's rows of destination p as [tokens][rows], box [a draining warp group's tokens][128 rows].
+struct OutMaps {
+    CUtensorMap m[DWIM_MAX_WORLD];
+};
+
+// OUT: 0 = one destination (or a scattered one); 1 = a result shared by several ranks, every value
+// stored to each copy from registers; 2 = the same through shared memory and one TMA store per
+// destination and group of columns (whole 512-byte runs over NVLink instead of 4-byte stores).
+template <int BN, int OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const __grid_constant__ CUtensorMap tmap_m, const __grid_constant__ GemmArgs a) {
+                const __grid_constant__ CUtensorMap tmap_m, const __grid_constant__ GemmArgs a,
+                const __grid_constant__ OutMaps maps) {
+    constexpr bool SHARED = OUT == 1;
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // the swizzled tiles want 1024-byte alignment
@@ -590,7 +601,34 @@ gemm_q4k_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
             for (int j = 0; j < C::DRAIN_COLS / 2; j++) unpack2(acc2[j], acc[2 * j], acc[2 * j + 1]);
             const size_t row = (size_t)row0 + rl;
-            if (row < a.rows) {
+            if (OUT == 2) {
+                // The group's tile [token][row] into the rings' shared memory, which nothing reads any
+                // more (the last unit's MMAs are done, its accumulator drained), then one store per
+                // destination.  Rows and tokens past the end are cut off by the maps' bounds.
+                const uint32_t stage = astage0 + g * (C::DRAIN_COLS * TILE_M * 4);
+                if (scaled) {
+#pragma unroll
+                    for (int j = 0; j < C::DRAIN_COLS; j++) acc[j] *= lds32f(tk + j * 4);
+                }
+                int nvals = C::DRAIN_COLS;
+                if (a.split) {
+#pragma unroll
+                    for (int j = 0; j < C::DRAIN_COLS / 2; j++) acc[j] = acc[2 * j] + acc[2 * j + 1];
+                    nvals = C::DRAIN_COLS / 2;
+                }
+#pragma unroll
+                for (int j = 0; j < C::DRAIN_COLS; j++)
+                    if (j < nvals) sts32f(stage + (j * TILE_M + rl) * 4, acc[j]);
+                fence_async_smem();
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");   // the group's four warps: all 128 rows are in
+                const size_t t0 = ((size_t)col0 + g * C::DRAIN_COLS) >> (a.split ? 1 : 0);
+                if (quad == 0 && lane == 0 && t0 < a.n) {
+#pragma unroll
+                    for (int p = 0; p < DWIM_MAX_WORLD; p++)
+                        if (p < a.out.world) tma_store_2d(&maps.m[p], row0, (int)t0, stage);
+                    tma_store_commit_wait();
+                }
+            } else if (row < a.rows) {
                 const size_t cbase = (size_t)col0 + g * C::DRAIN_COLS;
                 const EmitTo to = emit_to(a.out, a.aux, a.epi, row);
                 const size_t n = a.n, rows = a.rows;
@@ -867,17 +905,29 @@ int launch_gemm(dwim_b200_ctx *ctx, const WeightView &w, const __half *operand, 
         return rc;
     const float *tok_scale = reinterpret_cast<const float *>(operand + ncols * w.cols + ncols * units * 16);
     GemmArgs a{w.rows, n, ncols, units, split, out, tok_scale, aux, epi, ctx->status};
-    // a result shared by several ranks' copies takes the instantiation that stores to all of them
-    const bool shared = out.world > 1 && !out.scatter_per;
-    auto kern = shared ? gemm_q4k_kernel<BN, true> : gemm_q4k_kernel<BN, false>;
-    static bool configured[64][2] = {};
+    // A result shared by several ranks' copies takes an instantiation that stores to all of them: with
+    // TMA from shared memory when every copy's slice starts on a 16-byte boundary, else from registers.
+    int shared = out.world > 1 && !out.scatter_per ? 1 : 0;
+    OutMaps maps;          // only the TMA form reads it
+    if (shared && epi == EPI_STORE && out.pitch % 4 == 0) {
+        shared = 2;
+        for (int p = 0; p < out.world; p++)
+            if (reinterpret_cast<uintptr_t>(out.dst[p] + out.row0) % 16) shared = 1;
+        for (int p = 0; p < out.world && shared == 2; p++)
+            if ((rc = encode_2d(ctx, &maps.m[p], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, out.dst[p] + out.row0, w.rows, n,
+                                out.pitch * sizeof(float), TILE_M, (uint32_t)(C::DRAIN_COLS >> (split ? 1 : 0)),
+                                CU_TENSOR_MAP_SWIZZLE_NONE, "output")))
+                return rc;
+    }
+    auto kern = shared == 2 ? gemm_q4k_kernel<BN, 2> : shared == 1 ? gemm_q4k_kernel<BN, 1> : gemm_q4k_kernel<BN, 0>;
+    static bool configured[64][3] = {};
     if (!configured[ctx->device & 63][shared]) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured[ctx->device & 63][shared] = true;
     }
     dim3 grid((unsigned)((w.rows + TILE_M - 1) / TILE_M), (unsigned)((ncols + BN - 1) / BN));
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
-    DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, tm, a));
+    DWIM_CUDA(ctx, launch_dependent(dependent, kern, grid, dim3(GEMM_THREADS), (size_t)C::SMEM, ctx->stream, tw, tx, tm, a, maps));
     ctx->weights_written = false;
     DWIM_LAUNCHED(ctx);
     return 0;

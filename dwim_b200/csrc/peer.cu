@@ -431,7 +431,8 @@ extern "C" int dwim_b200_reduce_gather(dwim_b200_ctx *ctx, dwim_b200_buffer *out
                     slots->len, n, rows, world);
     ReduceArgs a{};
     a.slots = slots->data;
-    for (int r = 0; r < out->sh_world; r++) a.out[r] = out->sh_peer[r];
+    // every rank's copy, in ring order from this rank on (the ranks' stores then head for different GPUs)
+    for (int k = 0; k < out->sh_world; k++) a.out[k] = out->sh_peer[(out->sh_rank + k) % out->sh_world];
     a.n = n;
     a.rows = rows;
     a.per = per;
