@@ -499,11 +499,11 @@ def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
         traffic, traffic_note = None, None
         if world == 1 and (fmt, rows, cols) == ("q4_k", 17408, 5120):
             if m == 1:
-                traffic, traffic_note = 50.47e6, "profiles/gemv_kernel_q4k_c1.md"
+                traffic, traffic_note = 50.48e6, "profiles/dwim_smallm_kernel_q4k_c1.md"
             elif gemm:
                 # captured at M=512; weights fixed, operand reads in proportion to M, output in full
-                traffic = 50.1e6 + (7.7e6 + 35.65e6) * m / 512
-                traffic_note = ("profiles/gemm_q4k_kernel_c2.md: reads captured at M=512 (weights once + 7.7 MB of "
+                traffic = 50.1e6 + (10.6e6 + 35.65e6) * m / 512
+                traffic_note = ("profiles/gemm_q4k_kernel_c2.md: reads captured at M=512 (weights once + 10.6 MB of "
                                 "operands per 512 tokens) scaled by M, plus the output in full")
         if gemm:
             flops = 2.0 * m * my_rows * cols
