@@ -217,7 +217,7 @@ def workload_config(fmt, rows, cols, m, act, gpus, exchange="none"):
     if gpus > 1:
         sharding = {
             "push": (f"rows/{gpus}; every rank's product stores its rows of the f32 result into all {gpus} copies of a shared "
-                     "output from its epilogue (plain stores over NVLink, while other tiles multiply), then one barrier "
+                     "output from its epilogue (TMA stores from shared memory over NVLink, while other tiles multiply), then one barrier "
                      "kernel: the all-gather is inside the timed step"),
             "nccl": f"rows/{gpus} + NCCL all-gather of the f32 result + re-assembly kernel, inside the timed step",
             "none": (f"rows/{gpus}; a rank's rows of the result stay on it (they are the K slice its part of the "
@@ -1040,6 +1040,13 @@ def main():
                 mine[f"m{tokens}"] = {"us": lt["roofline"]["kernel_us"], "step_us": lt["ms_per_step"] * 1e3,
                                       "tflops": 2.0 * tokens * rows * cols / lt["roofline"]["kernel_us"] / 1e6,
                                       "max_rel_err": lt["parity"]["max_rel_err"]}
+            # the same product with f32 activations (two f16 columns per token), and the dense kernel's formats
+            for key, (f2, r2, c2, a2) in {"c2_f32_activations": (fmt, rows, cols, "f32"), "q8_0_5120x5120": ("q8_0", 5120, 5120, "bf16"),
+                                          "q6_k_12288x5120": ("q6_k", 12288, 5120, "bf16")}.items():
+                lt = run_gpu(args, "c2", f2, r2, c2, m, a2, quiet=True)
+                also[key] = {"tokens": m, "us": lt["roofline"]["kernel_us"], "step_us": lt["ms_per_step"] * 1e3,
+                             "tflops_per_step": lt["value"], "max_rel_err": lt["parity"]["max_rel_err"],
+                             "config": lt["config"]["workload"]}
             mine["m1"] = {"us": also["c1"]["kernel_us"], "step_us": also["c1"]["us_per_step"]}
             mine["m2048"] = {"us": line["roofline"]["kernel_us"], "step_us": line["ms_per_step"] * 1e3,
                              "tflops": line["roofline"]["achieved"]}

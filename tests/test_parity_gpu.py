@@ -474,7 +474,7 @@ def test_gemm_activation_range(dev, oracle, scale, bf16):
         assert max_rel_err(got[t], want[t]) <= 2e-5, (t, max_rel_err(got[t], want[t]))
 
 
-# ---- the operators either side of the product (SURVEY's "next" rows) -----------------------------
+# ---- the operators either side of the product (the norm before it, the arg-max after it, bf16 matrices) ----
 def test_normalize_matches_cpu(dev, oracle):
     """normalize_matches_cpu (gpu/tests.rs:788-812): the reference's shapes and
     generator; then the model's width, where the same launch also writes the next
