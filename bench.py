@@ -251,7 +251,7 @@ def parity_of(fmt, cols, x, got_rows, w_rows):
 
 
 # ---------------------------------------------------------------------------------------
-def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
+def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False, act_f16=False):
     import torch
     from dwim_b200 import B200, Tensor, shard_rows
 
@@ -265,6 +265,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False):
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = B200(local)
+    if act_f16:
+        dev.activation_precision("f16")
     ext = torch.cuda.ExternalStream(dev.stream, device=local)
 
     w, x, bits = make_inputs(fmt, rows, cols, m, act)
@@ -1044,6 +1046,11 @@ def main():
             for key, (f2, r2, c2, a2) in {"c2_f32_activations": (fmt, rows, cols, "f32"), "q8_0_5120x5120": ("q8_0", 5120, 5120, "bf16"),
                                           "q6_k_12288x5120": ("q6_k", 12288, 5120, "bf16")}.items():
                 lt = run_gpu(args, "c2", f2, r2, c2, m, a2, quiet=True)
+                if key == "c2_f32_activations":
+                    # and as one f16 column (dwim_b200_activation_precision: the reference device's precision)
+                    l16 = run_gpu(args, "c2", f2, r2, c2, m, a2, quiet=True, act_f16=True)
+                    also["c2_f32_activations_as_f16"] = {"tokens": m, "us": l16["roofline"]["kernel_us"], "step_us": l16["ms_per_step"] * 1e3,
+                                                         "tflops_per_step": l16["value"], "max_rel_err": l16["parity"]["max_rel_err"]}
                 also[key] = {"tokens": m, "us": lt["roofline"]["kernel_us"], "step_us": lt["ms_per_step"] * 1e3,
                              "tflops_per_step": lt["value"], "max_rel_err": lt["parity"]["max_rel_err"],
                              "config": lt["config"]["workload"]}

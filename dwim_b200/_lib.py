@@ -39,6 +39,7 @@ SIGNATURES = {
     "dwim_b200_resize": (C.c_int, [_vp, _vp, _sz]),
     "dwim_b200_touch": (C.c_int, [_vp, _vp]),
     "dwim_b200_touch_bf16": (C.c_int, [_vp, _vp]),
+    "dwim_b200_activation_precision": (C.c_int, [_vp, C.c_int]),
     "dwim_b200_write": (C.c_int, [_vp, _vp, _vp, _sz]),
     "dwim_b200_write_bf16": (C.c_int, [_vp, _vp, _vp, _sz]),
     "dwim_b200_read": (C.c_int, [_vp, _vp, _vp, _sz]),

@@ -235,6 +235,14 @@ int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
     return 0;
 }
 
+int dwim_b200_activation_precision(dwim_b200_ctx *ctx, int mode) {
+    DWIM_DEVICE(ctx);
+    if (!ctx) return DWIM_B200_EINVAL;
+    REQUIRE(ctx, mode == DWIM_B200_ACT_EXACT || mode == DWIM_B200_ACT_F16, DWIM_B200_EINVAL, "activation precision %d", mode);
+    ctx->act_f16 = mode == DWIM_B200_ACT_F16;
+    return 0;
+}
+
 int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
     DWIM_DEVICE(ctx);
     if (!ctx || !buf) return DWIM_B200_EINVAL;
@@ -483,7 +491,7 @@ static int product(dwim_b200_ctx *ctx, const OutSpec &out, size_t out_len, const
     if (dense) {
         // bf16 activations are exact in one f16 column; f32 ones travel as two
         // (value and rounding remainder), summed again in the epilogue.
-        int split = x->bf16_exact ? 0 : 1;
+        int split = x->bf16_exact || ctx->act_f16 ? 0 : 1;
         int rc = ensure_shadow(ctx, x, SHADOW_GEMM, v.cols, split);
         if (rc) return rc;
         return gemm_large(ctx, v, (const __half *)x->shadow, n, split, out, aux, epilogue);

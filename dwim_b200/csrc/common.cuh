@@ -65,6 +65,8 @@ struct dwim_b200_ctx {
     // (an upload's repack): that launch must be an ordinary one, because a
     // programmatic dependent streams weights before it waits for the kernels ahead.
     bool weights_written = false;
+    // 1: f32 activations go to the tensor-core kernels as one f16 column (dwim_b200_activation_precision)
+    int act_f16 = 0;
     // the dense pair kernel's weight panel: f16 value and remainder of the dequantized rows, the rows' scales (gemm.cu)
     __half *pair_hi = nullptr, *pair_lo = nullptr;
     float *pair_scale = nullptr;

@@ -188,7 +188,7 @@ extern "C" int dwim_b200_normalize(dwim_b200_ctx *ctx, dwim_b200_buffer *out, co
     if (dim % 256 == 0 && n > DWIM_SMALL_M_MAX && n <= 65535) {
         // more tokens than the small-M kernel takes: the next product is the tensor-core GEMM, whose
         // operand (f16 value and remainder columns, sub-block means, the token's scale) this launch writes
-        const int split = 1;
+        const int split = ctx->act_f16 ? 0 : 1;
         int rc = reserve_shadow(ctx, out, gemm_operand_bytes(dim, n, split));
         if (rc) return rc;
         rc = build_gemm_operand(ctx, x->data, n, dim, split, (__half *)out->shadow, weight->data, eps, out->data);

@@ -123,6 +123,11 @@ class B200:
         """``touch`` by a writer that vouches every value it wrote is exactly a bf16."""
         self._check(self._L.dwim_b200_touch_bf16(self._ctx, buf._h))
 
+    def activation_precision(self, mode: str) -> None:
+        """``"exact"`` (the default: f32 activations as two f16 columns) or ``"f16"`` (one column, the
+        precision of the reference's CUDA device, twice the rate) for products of more than eight tokens."""
+        self._check(self._L.dwim_b200_activation_precision(self._ctx, {"exact": 0, "f16": 1}[mode]))
+
     def resize(self, buf: Buffer, length: int) -> None:
         self._check(self._L.dwim_b200_resize(self._ctx, buf._h, length))
 

@@ -128,6 +128,17 @@ DWIM_B200_API int dwim_b200_touch(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
  * carries a token as one 16-bit column instead of two, as after write_bf16.
  * A value that is not a bf16 would be rounded to f16's 11 bits, silently. */
 DWIM_B200_API int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf);
+/* How f32 activations reach the tensor-core kernels (products of more than
+ * eight tokens; the small-M kernel's digit planes are exact either way).
+ * EXACT, the default: a token travels as two f16 columns, value and rounding
+ * remainder, and the product's error stays near 2e-6 of its rms; twice the
+ * tensor-core work of a bf16-exact buffer.  F16: one column, the activation
+ * rounded to f16 after the token's power-of-two scaling, which is the
+ * precision of the reference's own CUDA device (`halves`,
+ * gpu/cuda/mod.rs:313-384): error about 2e-4, twice the rate. */
+#define DWIM_B200_ACT_EXACT 0
+#define DWIM_B200_ACT_F16 1
+DWIM_B200_API int dwim_b200_activation_precision(dwim_b200_ctx *ctx, int mode);
 /* Device::write (gpu/mod.rs:224-225): `len` must equal the buffer's length. */
 DWIM_B200_API int dwim_b200_write(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, const float *data, size_t len);
 /* As write, from bf16 bits (gpu/float.rs:5-8): the buffer holds the same

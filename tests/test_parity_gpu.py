@@ -787,3 +787,32 @@ def test_shared_buffer_in_a_world_of_one(dev, oracle):
             dev.matmul_gather(out, dev.upload(t.slice_rows(b, e)), xb, b, rows)
         dev.shared_barrier(out)
         assert max_rel_err(dev.read(out), oracle.matmul("q4_k", t.data, rows, cols, x)) <= 2e-5
+
+
+def test_activation_precision_f16(dev, oracle):
+    """f32 activations as one f16 column on request (the reference device's own precision, `halves`,
+    gpu/cuda/mod.rs:313-384): inside the 1e-3 of the product's tolerance, and really another path than
+    the exact one."""
+    from dwim_b200 import DeviceError
+    g = np.random.default_rng(91)
+    rows, cols, n = 384, 5120, 40
+    blocks = oracle.quantize("q4_k", (0.02 * g.standard_normal((rows, cols))).astype(np.float32))
+    weight = upload(dev, "q4_k", rows, cols, blocks)
+    x = g.standard_normal((n, cols)).astype(np.float32)
+    x[3] *= 1e4                                    # a token of another magnitude keeps its own scale
+    want = oracle.matmul("q4_k", blocks, rows, cols, x)
+    xb, out = dev.buffer(x), dev.alloc(n * rows)
+    dev.matmul(out, weight, xb)
+    exact = max_rel_err(dev.read(out), want)
+    dev.activation_precision("f16")
+    try:
+        dev.matmul(out, weight, xb)
+        half = max_rel_err(dev.read(out), want)
+    finally:
+        dev.activation_precision("exact")
+    dev.matmul(out, weight, xb)
+    again = max_rel_err(dev.read(out), want)
+    assert exact <= 1e-5 and again <= 1e-5, (exact, again)
+    assert 1e-5 < half <= 1e-3, half
+    with pytest.raises(DeviceError):
+        dev._check(dev._L.dwim_b200_activation_precision(dev._ctx, 7))
