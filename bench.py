@@ -1050,7 +1050,8 @@ def main():
                     # and as one f16 column (dwim_b200_activation_precision: the reference device's precision)
                     l16 = run_gpu(args, "c2", f2, r2, c2, m, a2, quiet=True, act_f16=True)
                     also["c2_f32_activations_as_f16"] = {"tokens": m, "us": l16["roofline"]["kernel_us"], "step_us": l16["ms_per_step"] * 1e3,
-                                                         "tflops_per_step": l16["value"], "max_rel_err": l16["parity"]["max_rel_err"]}
+                                                         "tflops_per_step": l16["value"], "max_rel_err": l16["parity"]["max_rel_err"],
+                                                         "note": "opt-in, the reference device's precision: outside the 1e-3 bar on the worst element by design"}
                 also[key] = {"tokens": m, "us": lt["roofline"]["kernel_us"], "step_us": lt["ms_per_step"] * 1e3,
                              "tflops_per_step": lt["value"], "max_rel_err": lt["parity"]["max_rel_err"],
                              "config": lt["config"]["workload"]}

@@ -135,7 +135,10 @@ DWIM_B200_API int dwim_b200_touch_bf16(dwim_b200_ctx *ctx, dwim_b200_buffer *buf
  * tensor-core work of a bf16-exact buffer.  F16: one column, the activation
  * rounded to f16 after the token's power-of-two scaling, which is the
  * precision of the reference's own CUDA device (`halves`,
- * gpu/cuda/mod.rs:313-384): error about 2e-4, twice the rate. */
+ * gpu/cuda/mod.rs:313-384): rms error about 3e-4 of the result's magnitude,
+ * the worst element about 3e-3 -- inside that device's gate (1e-3 and 1e-2,
+ * gpu/tests.rs:198-211), outside this library's 1e-3 on the worst element --
+ * at twice the rate. */
 #define DWIM_B200_ACT_EXACT 0
 #define DWIM_B200_ACT_F16 1
 DWIM_B200_API int dwim_b200_activation_precision(dwim_b200_ctx *ctx, int mode);
