@@ -448,6 +448,8 @@ def run_gpu(args, name, fmt, rows, cols, m, act, quiet=False, act_f16=False):
         chunk, n_lanes = 256, 3
         for k in range(n_lanes):
             d = dev if k == 0 else B200(local)
+            if act_f16 and k:
+                d.activation_precision("f16")
             lanes.append((d, d.alloc(chunk * cols), d.alloc(chunk * my_rows)))
         pool = ThreadPoolExecutor(n_lanes)
 
