@@ -59,6 +59,7 @@ SIGNATURES = {
     "dwim_b200_argmax": (C.c_int, [_vp, _vp, _sz, C.POINTER(C.c_uint32), _sz]),
     "dwim_b200_matmul_static": (C.c_int, [_vp, _vp, _vp, _vp, _sz]),
     "dwim_b200_shared_alloc": (C.c_int, [_vp, _sz, C.POINTER(_vp), _vp, _sz]),
+    "dwim_b200_shared_connect_local": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp]),
     "dwim_b200_shared_connect": (C.c_int, [_vp, _vp, C.c_int, C.c_int, _vp, _sz]),
     "dwim_b200_matmul_gather": (C.c_int, [_vp, _vp, _vp, _vp, _sz, _sz]),
     "dwim_b200_shared_barrier": (C.c_int, [_vp, _vp]),

@@ -339,6 +339,26 @@ extern "C" int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *bu
     return 0;
 }
 
+extern "C" int dwim_b200_shared_connect_local(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank,
+                                              dwim_b200_buffer *const *copies) {
+    DWIM_DEVICE(ctx);
+    using namespace dwim;
+    if (!ctx || !buf || !copies) return DWIM_B200_EINVAL;
+    if (world < 1 || world > DWIM_MAX_WORLD || rank < 0 || rank >= world)
+        return fail(ctx, DWIM_B200_EINVAL, "shared_connect_local: world %d rank %d", world, rank);
+    if (buf->sh_flag_offset == 0) return fail(ctx, DWIM_B200_EINVAL, "shared_connect_local: not a buffer of shared_alloc");
+    if (buf->sh_world) return fail(ctx, DWIM_B200_EINVAL, "shared_connect_local: connected already");
+    for (int r = 0; r < world; r++) {
+        const dwim_b200_buffer *c = r == rank ? buf : copies[r];
+        if (!c || c->sh_flag_offset != buf->sh_flag_offset || c->cap != buf->cap)
+            return fail(ctx, DWIM_B200_EINVAL, "shared_connect_local: rank %d's copy is not a shared buffer of the same size", r);
+    }
+    for (int r = 0; r < world; r++) buf->sh_peer[r] = r == rank ? buf->data : copies[r]->data;   // nothing to unmap later
+    buf->sh_world = world;
+    buf->sh_rank = rank;
+    return 0;
+}
+
 extern "C" int dwim_b200_shared_barrier(dwim_b200_ctx *ctx, dwim_b200_buffer *buf) {
     DWIM_DEVICE(ctx);
     using namespace dwim;

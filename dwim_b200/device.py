@@ -224,6 +224,11 @@ class B200:
         blob = b"".join(bytes(h)[:nb].ljust(nb, b"\0") for h in handles)
         self._check(self._L.dwim_b200_shared_connect(self._ctx, buf._h, world, rank, blob, nb))
 
+    def shared_connect_local(self, buf: Buffer, world: int, rank: int, copies) -> None:
+        """``shared_connect`` for ranks of one process: ``copies`` are the ranks' buffers in rank order."""
+        arr = (C.c_void_p * world)(*[None if c is None else c._h for c in copies])
+        self._check(self._L.dwim_b200_shared_connect_local(self._ctx, buf._h, world, rank, arr))
+
     def matmul_gather(self, out: Buffer, w: Weight, x: Buffer, row_begin: int, total_rows: int) -> None:
         """The row-sharded product, its rows stored into every rank's copy of ``out``."""
         self._check(self._L.dwim_b200_matmul_gather(self._ctx, out._h, w._h, x._h, row_begin, total_rows))

@@ -241,6 +241,15 @@ DWIM_B200_API int dwim_b200_shared_alloc(dwim_b200_ctx *ctx, size_t len, dwim_b2
                                          size_t handle_bytes);
 DWIM_B200_API int dwim_b200_shared_connect(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank,
                                            const void *handles, size_t handle_bytes);
+/* The same for ranks that live in one process (one host thread driving several
+ * GPUs, as the reference's server would): `copies[r]` is rank r's buffer of
+ * dwim_b200_shared_alloc, of the same length (copies[rank] is ignored); the
+ * pointers are used as they are, so peer access between the devices must be
+ * enabled by the caller.  Ranks on one GPU may share results this way, but
+ * must not call dwim_b200_shared_barrier: kernels that wait for one another
+ * cannot be relied on to run together on one device. */
+DWIM_B200_API int dwim_b200_shared_connect_local(dwim_b200_ctx *ctx, dwim_b200_buffer *buf, int world, int rank,
+                                                 dwim_b200_buffer *const *copies);
 /* The row-sharded product with the all-gather fused into it: `w` holds rows
  * [row_begin, row_begin + rows(w)) of a matrix of `total_rows`; the kernel's
  * epilogue stores out[t * total_rows + row_begin + r] = w[r] . x[t] into EVERY

@@ -789,6 +789,30 @@ def test_shared_buffer_in_a_world_of_one(dev, oracle):
         assert max_rel_err(dev.read(out), oracle.matmul("q4_k", t.data, rows, cols, x)) <= 2e-5
 
 
+def test_shared_result_of_two_ranks_on_one_gpu(dev, oracle):
+    """Two ranks of one process (dwim_b200_shared_connect_local): each rank's matmul_gather must put
+    its rows into BOTH copies of the shared result -- the small-M kernel's peer stores, the
+    tensor-core kernel's TMA stores (slices on 16-byte boundaries) and its register stores (a slice
+    that is not).  No barrier kernel: both ranks share the GPU, and the stream orders them."""
+    from dwim_b200 import Tensor
+    rng = np.random.default_rng(101)
+    cols = 1024
+    for rows, cut in ((1000, 496), (1002, 499)):          # aligned slices / a slice that starts on an odd row
+        t = Tensor("q4_k", (rows, cols), oracle.quantize("q4_k", (0.02 * rng.standard_normal((rows, cols))).astype(np.float32)))
+        shards = [(0, cut, dev.upload(t.slice_rows(0, cut))), (cut, rows, dev.upload(t.slice_rows(cut, rows)))]
+        for n in (3, 40, 300):
+            x = rng.standard_normal((n, cols)).astype(np.float32)
+            want = oracle.matmul("q4_k", t.data, rows, cols, x)
+            copies = [dev.shared_alloc(n * rows)[0] for _ in range(2)]
+            for r in range(2):
+                dev.shared_connect_local(copies[r], 2, r, copies)
+            xb = dev.buffer(x)
+            for r, (b, e, w) in enumerate(shards):
+                dev.matmul_gather(copies[r], w, xb, b, rows)
+            for r in range(2):
+                assert max_rel_err(dev.read(copies[r]), want) <= 2e-5, (rows, n, r)
+
+
 def test_activation_precision_f16(dev, oracle):
     """f32 activations as one f16 column on request (the reference device's own precision, `halves`,
     gpu/cuda/mod.rs:313-384): it passes the reference's gate for that device (rms error below 1e-3 of
