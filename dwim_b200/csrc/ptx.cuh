@@ -170,14 +170,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int 
 }
 
 // 2-D tiled tensor copy shared -> global (the box as it lies in shared memory, outer index slowest),
-// then: close the group of copies issued so far, and wait until the group has been written.
+// then: close the group of copies issued so far, and wait until the group's shared memory has
+// been read (the writes themselves complete with the kernel: a CTA that waited for them kept its
+// SM idle for the links' latency).
 __device__ __forceinline__ void tma_store_2d(const void *tmap, int c0, int c1, uint32_t src) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(c0), "r"(c1),
                  "r"(src)
                  : "memory");
 }
 __device__ __forceinline__ void tma_store_commit_wait() {
-    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.bulk.commit_group;\n\tcp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 }  // namespace dwim
