@@ -175,10 +175,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 //   [0,14) address >> 4   [16,30) leading byte offset >> 4   [32,46) stride
 //   byte offset >> 4   [46,48) version 1   [61,64) layout
 // 128-byte swizzle: rows are 128 bytes (64 f16), eight-row groups 1024 bytes
-// apart (stride offset); the leading offset is not used.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    return (uint64_t)((addr & 0x3ffffu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
+// apart (stride offset); the leading offset is not used: (addr & 0x3ffff) >> 4 | 1 << 16 |
+// 64 << 32 | 1 << 46 | 2 << 61.  The kernels keep it as a low word per stage and the high word
+// all stages share (`desc_hi`), so that the MMA warp adds to 32-bit values only.
 // No swizzle: 8 rows x 16 bytes are contiguous (128 bytes); eight-row groups
 // 128 bytes apart (stride offset); the second 8 of K `lbo` bytes further on.
 __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo) {

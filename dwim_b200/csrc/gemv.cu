@@ -44,7 +44,6 @@ struct GemvArgs {
     const uint8_t *panels;   // [units][i8_unit_bytes(ncols)]: the activations' digit planes (prologue.cu)
     int xunit;               // bytes of one unit's panels for this launch
     int xsrc_stride;         // bytes between units in the panel array
-    int ctas_per_sm;         // 0: one
     // SwiGLU in one launch (int8 routine): `w` is the gate matrix, these the quants and scales of
     // the up matrix of the same shape; a CTA takes a row tile of the one, then of the other, and
     // writes silu(gate . x) * (up . x).  Null: an ordinary product.
@@ -612,9 +611,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
     constexpr int BASE = base_of(FMT);
     constexpr int RED_BYTES = KS > 1 ? ((2 * KS * RT * 4 * 32 * 4 + 127) & ~127) : 0;
     constexpr int SMEM_LIMIT = 227 * 1024;
-    // CTAs per SM: two smaller CTAs overlap one's fill and drain with the other's steady state
-    const int cps = a.ctas_per_sm > 0 ? a.ctas_per_sm : 1;
-    const int SMEM_MAX = cps > 1 ? (228 * 1024) / cps - 1024 : SMEM_LIMIT;
+    const int SMEM_MAX = SMEM_LIMIT;   // one CTA per SM
     const int fixed = 256 + RED_BYTES;
     // The digit planes stay resident in shared memory when they are small next to the ring, or
     // when two stages of whole rows still fit beside them (the planes of five tokens of a
@@ -667,7 +664,7 @@ static int launch(dwim_b200_ctx *ctx, GemvArgs &a) {
         DWIM_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
         configured[ctx->device & 63] = true;
     }
-    int grid = a.n_tiles < cps * ctx->sm_count ? a.n_tiles : cps * ctx->sm_count;
+    int grid = a.n_tiles < ctx->sm_count ? a.n_tiles : ctx->sm_count;
     const int nwarps = RT * KS + 1;
     const bool dependent = !ctx->weights_written;   // see dwim_b200_ctx::weights_written
     ctx->weights_written = false;

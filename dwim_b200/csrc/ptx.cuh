@@ -146,16 +146,6 @@ __device__ __forceinline__ uint32_t hsub2(uint32_t a, uint32_t b) {
 __device__ __forceinline__ float h2f_lo(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v & 0xffff))); }
 __device__ __forceinline__ float h2f_hi(uint32_t v) { return __half2float(__ushort_as_half((uint16_t)(v >> 16))); }
 
-// D += A (16 rows x 16 k, f16) * B (16 k x 8 columns, f16), fp32.
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-
 // ---- sm_100 tensor-memory and UMMA wrappers ------------------------------------
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
